@@ -1,0 +1,154 @@
+/* C ABI of libtensor_b200_gguf.so: B200 (sm_100a) GGUF dequant-fused GEMV / GEMM.
+ *
+ * This is the drop-in boundary for the one path the reference runs through
+ * benchmarks/kernels/showcase/kernels.py:114-119 (`gguf(m, n, k, encoding)`:
+ * `gemv_packed` for m == 1, `_packed` for m > 1), whose device kernels present the
+ * signature `kernel(x, w, out)` with flat, 64-byte aligned buffers to the runtime
+ * (src/tensor/runtime/executable.py:87-149 -> src/tensor/providers/cuda/device.py:211-229).
+ *
+ * Two layers are exported:
+ *   1. plain-pointer entry points (device pointers, sizes, a CUstream as void*);
+ *   2. `*_v1` entry points with the reference's C calling convention
+ *      `int32_t fn(const TensorCallV1*, TensorErrorV1*)` (src/tensor/include/tensor/abi.h:141),
+ *      which validate the descriptors before touching memory, as the reference's CPU image
+ *      wrappers do (src/tensor/compiler/cpu.py:60-155), and then call layer 1.
+ *
+ * The structs below re-declare the reference's frozen ABI 1.3 layouts
+ * (src/tensor/include/tensor/abi.h:37-85: 48 / 64 / 16 / 72 / 512 bytes); the library
+ * static-asserts the sizes.  Status codes are abi.h:20-23.  Nothing is allocated by the
+ * library on these paths: scratch memory is an explicit argument (the reference's ABI allows no
+ * hidden workspace, src/tensor/runtime/abi.py:135-152).  All work is enqueued on the given
+ * stream and returns without synchronising.  There is no CPU fallback.
+ */
+#ifndef TENSOR_B200_GGUF_H
+#define TENSOR_B200_GGUF_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- reference ABI 1.3 layouts (abi.h:10-85) ---------------------------------------------- */
+#ifndef TENSOR_ABI_H
+#define TENSOR_ABI_VERSION 1u
+#define TENSOR_DEVICE_CUDA 2u
+#define TENSOR_ARG_BUFFER 1u
+#define TENSOR_ARG_SCALAR 2u
+#define TENSOR_OK 0
+#define TENSOR_ERROR_ABI 1
+#define TENSOR_ERROR_ARGUMENT 2
+#define TENSOR_ERROR_PROVIDER 3
+#define TENSOR_UINT8 3
+#define TENSOR_INT32 6
+#define TENSOR_INT64 8
+#define TENSOR_FLOAT16 10
+#define TENSOR_FLOAT32 11
+#define TENSOR_BFLOAT16 13
+
+typedef struct TensorBufferV1 {
+  uint64_t address;
+  uint64_t byte_size;
+  const int64_t *shape;
+  const int64_t *strides; /* bytes */
+  uint32_t rank;
+  uint32_t dtype;
+  uint32_t device_type;
+  int32_t device_ordinal;
+} TensorBufferV1;
+
+typedef struct TensorArgumentV1 {
+  uint32_t kind;
+  uint32_t dtype;
+  TensorBufferV1 buffer;
+  uint64_t scalar;
+} TensorArgumentV1;
+
+typedef struct TensorStreamV1 {
+  uint32_t device_type;
+  int32_t device_ordinal;
+  uint64_t handle; /* CUstream */
+} TensorStreamV1;
+
+typedef struct TensorCallV1 {
+  uint32_t abi_version;
+  uint32_t struct_size;
+  const TensorArgumentV1 *arguments;
+  uint32_t argument_count;
+  uint32_t flags;
+  uint32_t grid[3];  /* ignored: the library sizes its own launches */
+  uint32_t block[3]; /* ignored */
+  uint64_t shared_memory_bytes; /* ignored */
+  TensorStreamV1 stream;
+} TensorCallV1;
+
+typedef struct TensorErrorV1 {
+  int32_t code;
+  char message[508];
+} TensorErrorV1;
+#endif /* TENSOR_ABI_H */
+
+/* ---- block formats: GGML type ids, the `encoding` of showcase/benchmark.py:122 ------------- */
+#define TB200_Q4_0 2
+#define TB200_Q8_0 8
+#define TB200_Q4_K 12
+#define TB200_Q6_K 14
+
+/* kernel selection: 0 lets the library choose */
+#define TB200_VARIANT_AUTO 0
+#define TB200_VARIANT_SIMPLE 1 /* SIMT fp32 kernels, any shape */
+#define TB200_VARIANT_FAST 2   /* GEMV: bulk-copy pipeline + mma.sync; GEMM: tcgen05 / TMEM */
+
+/* Library / ABI version: (major << 16) | minor. */
+int32_t tb200_gguf_version(void);
+
+/* Bytes of an [n, k] weight in `format`; -1 if k is not a multiple of the block size or the
+ * format id is unknown.  Row stride is k / block * bytes (triton_kernels.py:136,144,164). */
+int64_t tb200_gguf_weight_bytes(int32_t format, int64_t n, int64_t k);
+
+/* Scratch bytes the GEMV may use for its split-K partial sums at this shape on the current
+ * device (0 when the chosen kernel never splits K).  Passing less (or NULL) is legal: the
+ * library then picks a kernel that needs none. */
+int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int64_t k);
+
+/* Synchronises the current device and reads the sticky status words of the pipelined kernels.
+ * Every device-side wait in this library is bounded (about two seconds); a wait that gives up
+ * records a code there and the kernel returns instead of hanging.  Returns TENSOR_OK and
+ * *status == 0 when nothing was recorded; the words are cleared by the call.  No counterpart in
+ * the reference (its generated kernels do not wait on anything). */
+int32_t tb200_gguf_device_status(uint32_t *status, TensorErrorV1 *error);
+
+/* out[n, k] (fp32) = dequant(w).  Replaces the decode the reference states in
+ * benchmarks/kernels/showcase/triton_kernels.py:133-181; results are bit-identical to it. */
+int32_t tb200_gguf_dequant(int32_t format, const void *w, float *out, int64_t n, int64_t k,
+                           void *stream, TensorErrorV1 *error);
+
+/* Decode GEMV: out[m, n] (fp32) = x[m, k] . dequant(w[n, k])^T with fp32 weights and fp32
+ * accumulation, 1 <= m.  Replaces `gemv_packed` (showcase/kernels.py:116-119; contract
+ * showcase/benchmark.py:468-470, triton_kernels.py:213-222).  x_dtype is TENSOR_FLOAT16,
+ * TENSOR_BFLOAT16 or TENSOR_FLOAT32.  If scratch is used, it must start zeroed before the first
+ * call; every call leaves it zeroed again.  Calls that share scratch must not overlap. */
+int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
+                        int64_t m, int64_t n, int64_t k, void *scratch, int64_t scratch_bytes,
+                        int32_t variant, void *stream, TensorErrorV1 *error);
+
+/* Prefill GEMM: out[m, n] (fp32) = x[m, k] . dequant(w[n, k])^T with both operands rounded to
+ * bf16 and fp32 accumulation.  Replaces `_packed` (showcase/kernels.py:116-119; contract
+ * showcase/benchmark.py:471-477, triton_kernels.py:184-210, there with fp16 operands).
+ * x_dtype must be TENSOR_BFLOAT16. */
+int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
+                        int64_t m, int64_t n, int64_t k, int32_t variant, void *stream,
+                        TensorErrorV1 *error);
+
+/* Descriptor forms (reference convention, abi.h:141).  Arguments, in order:
+ *   dequant: buffers w (uint8), out (float32); scalars n, k, format.
+ *   gemv:    buffers x, w (uint8), out (float32)[, scratch (uint8)]; scalars m, n, k, format[, variant].
+ *   gemm:    buffers x (bfloat16), w (uint8), out (float32); scalars m, n, k, format[, variant].
+ * Scalars are TENSOR_INT32 or TENSOR_INT64.  call->stream.handle is the CUstream. */
+int32_t tb200_gguf_dequant_v1(const TensorCallV1 *call, TensorErrorV1 *error);
+int32_t tb200_gguf_gemv_v1(const TensorCallV1 *call, TensorErrorV1 *error);
+int32_t tb200_gguf_gemm_v1(const TensorCallV1 *call, TensorErrorV1 *error);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

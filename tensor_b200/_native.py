@@ -1,0 +1,84 @@
+"""Loader of the in-tree CUDA library.  There is no fallback: if ``libtensor_b200_gguf.so`` is
+missing or does not load, every operation of this package raises."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import abi
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libtensor_b200_gguf.so")
+
+#: every symbol include/tensor_b200_gguf.h declares
+EXPORTS = (
+    "tb200_gguf_version", "tb200_gguf_weight_bytes", "tb200_gguf_gemv_scratch_bytes",
+    "tb200_gguf_device_status", "tb200_gguf_dequant", "tb200_gguf_gemv", "tb200_gguf_gemm",
+    "tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1",
+)
+
+
+class TensorRuntimeError(RuntimeError):
+    """Provider-side failure (status 3), like the reference's ``TensorRuntimeError``
+    (src/tensor/providers/cuda/driver.py:11-16)."""
+
+    def __init__(self, message: str, code: int = abi.ERROR_PROVIDER):
+        super().__init__(message)
+        self.code = code
+
+
+class AbiError(TensorRuntimeError):
+    """The call descriptor itself was malformed (status 1)."""
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise TensorRuntimeError(
+            f"{LIB_PATH} is missing: build the CUDA extension first (python -m tensor_b200.build). "
+            "This package has no CPU or PyTorch fallback.")
+    handle = ctypes.CDLL(LIB_PATH)
+    missing = [name for name in EXPORTS if not hasattr(handle, name)]
+    if missing:
+        raise TensorRuntimeError(f"{LIB_PATH} does not export {missing}; rebuild it")
+    i32, i64, vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
+    err = ctypes.POINTER(abi.TensorErrorV1)
+    call = ctypes.POINTER(abi.TensorCallV1)
+    handle.tb200_gguf_version.restype = i32
+    handle.tb200_gguf_weight_bytes.restype = i64
+    handle.tb200_gguf_weight_bytes.argtypes = [i32, i64, i64]
+    handle.tb200_gguf_gemv_scratch_bytes.restype = i64
+    handle.tb200_gguf_gemv_scratch_bytes.argtypes = [i32, i64, i64, i64]
+    handle.tb200_gguf_device_status.restype = i32
+    handle.tb200_gguf_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), err]
+    handle.tb200_gguf_dequant.restype = i32
+    handle.tb200_gguf_dequant.argtypes = [i32, vp, vp, i64, i64, vp, err]
+    handle.tb200_gguf_gemv.restype = i32
+    handle.tb200_gguf_gemv.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, vp, i64, i32, vp, err]
+    handle.tb200_gguf_gemm.restype = i32
+    handle.tb200_gguf_gemm.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, i32, vp, err]
+    for name in ("tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1"):
+        fn = getattr(handle, name)
+        fn.restype = i32
+        fn.argtypes = [call, err]
+    _lib = handle
+    return _lib
+
+
+def raise_for_status(status: int, error: abi.TensorErrorV1) -> None:
+    """Map the C status codes onto the exception types the reference raises for the same
+    conditions: binding problems are ValueError (src/tensor/runtime/executable.py:93-148),
+    provider failures a RuntimeError subclass carrying ``.code``."""
+    if status == abi.OK:
+        return
+    message = error.message.decode("utf-8", "replace")
+    if status == abi.ERROR_ARGUMENT:
+        raise ValueError(message)
+    if status == abi.ERROR_ABI:
+        raise AbiError(message, status)
+    raise TensorRuntimeError(message, status)

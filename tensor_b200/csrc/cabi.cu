@@ -1,0 +1,393 @@
+// C-ABI entry points of libtensor_b200_gguf.so (declared in include/tensor_b200_gguf.h).
+//
+// Layer 1: plain device pointers + sizes + stream.  Layer 2 (`*_v1`): the reference's
+// `int32_t fn(const TensorCallV1*, TensorErrorV1*)` convention (src/tensor/include/tensor/abi.h:141),
+// validated the way the reference's CPU image wrappers validate a call before touching data
+// (src/tensor/compiler/cpu.py:60-155): abi version, struct size, argument count / kind / dtype,
+// byte sizes, alignment, device.  Errors are status codes + a message, never C++ exceptions
+// (abi.h:135-141).  There is no CPU fallback: every path below ends in a CUDA launch or an error.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/tensor_b200_gguf.h"
+#include "common.cuh"
+#include "kernels.h"
+
+static_assert(sizeof(TensorBufferV1) == 48, "TensorBufferV1 layout");
+static_assert(sizeof(TensorArgumentV1) == 64, "TensorArgumentV1 layout");
+static_assert(sizeof(TensorStreamV1) == 16, "TensorStreamV1 layout");
+static_assert(sizeof(TensorCallV1) == 72, "TensorCallV1 layout");
+static_assert(sizeof(TensorErrorV1) == 512, "TensorErrorV1 layout");
+
+namespace tb200 {
+
+const DeviceInfo* device_info(cudaError_t* err) {
+  static DeviceInfo table[64];
+  static std::mutex lock;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && (dev < 0 || dev >= 64)) e = cudaErrorInvalidDevice;
+  if (e != cudaSuccess) {
+    if (err) *err = e;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> guard(lock);
+  DeviceInfo& d = table[dev];
+  if (d.ordinal != dev) {
+    int sm = 0, smem = 0, major = 0, minor = 0;
+    if ((e = cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev)) != cudaSuccess) {
+      if (err) *err = e;
+      return nullptr;
+    }
+    d.sm_count = sm;
+    d.max_smem_optin = smem;
+    d.cc_major = major;
+    d.cc_minor = minor;
+    d.ordinal = dev;
+  }
+  if (err) *err = cudaSuccess;
+  return &d;
+}
+
+}  // namespace tb200
+
+namespace {
+
+using namespace tb200;
+
+int32_t fail(TensorErrorV1* error, int32_t code, const char* fmt, ...) {
+  if (error) {
+    error->code = code;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error->message, sizeof(error->message), fmt, ap);
+    va_end(ap);
+    error->message[sizeof(error->message) - 1] = 0;
+  }
+  return code;
+}
+
+int32_t ok(TensorErrorV1* error) {
+  if (error) {
+    error->code = TENSOR_OK;
+    error->message[0] = 0;
+  }
+  return TENSOR_OK;
+}
+
+int32_t cuda_fail(TensorErrorV1* error, const char* what, cudaError_t e) {
+  return fail(error, TENSOR_ERROR_PROVIDER, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+// The kernels are sm_100a-only; refuse anything else before a launch can fail obscurely.
+int32_t require_device(TensorErrorV1* error, const DeviceInfo** out) {
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return cuda_fail(error, "no usable CUDA device", e);
+  if (dev->cc_major != 10)
+    return fail(error, TENSOR_ERROR_PROVIDER,
+                "device %d has compute capability %d.%d; this library is built for sm_100a only", dev->ordinal,
+                dev->cc_major, dev->cc_minor);
+  *out = dev;
+  return TENSOR_OK;
+}
+
+int32_t check_shape(TensorErrorV1* error, int32_t format, int64_t m, int64_t n, int64_t k) {
+  if (!valid_format(format))
+    return fail(error, TENSOR_ERROR_ARGUMENT, "unknown GGUF format id %d (expected 2, 8, 12 or 14)", format);
+  if (m < 0 || n < 0 || k < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative extent m=%lld n=%lld k=%lld",
+                                           (long long)m, (long long)n, (long long)k);
+  if (k % block_weights(format))
+    return fail(error, TENSOR_ERROR_ARGUMENT, "K=%lld is not a multiple of the block size %d of format %d",
+                (long long)k, block_weights(format), format);
+  if (k > (1ll << 30) || n > (1ll << 31) || m > (1ll << 24))
+    return fail(error, TENSOR_ERROR_ARGUMENT, "extent too large: m=%lld n=%lld k=%lld", (long long)m,
+                (long long)n, (long long)k);
+  return TENSOR_OK;
+}
+
+int32_t check_pointer(TensorErrorV1* error, const char* name, const void* p, size_t alignment, bool needed) {
+  if (!p && needed) return fail(error, TENSOR_ERROR_ARGUMENT, "%s is NULL", name);
+  if (reinterpret_cast<uintptr_t>(p) % alignment)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "%s (%p) is not %zu-byte aligned", name, p, alignment);
+  return TENSOR_OK;
+}
+
+int dtype_bytes(int32_t dtype) {
+  switch (dtype) {
+    case TENSOR_FLOAT16:
+    case TENSOR_BFLOAT16: return 2;
+    case TENSOR_FLOAT32: return 4;
+    case TENSOR_UINT8: return 1;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t tb200_gguf_version(void) { return (1 << 16) | 0; }
+
+int64_t tb200_gguf_weight_bytes(int32_t format, int64_t n, int64_t k) {
+  if (!valid_format(format) || n < 0 || k < 0 || k % block_weights(format)) return -1;
+  return n * row_bytes(format, k);
+}
+
+int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int64_t k) {
+  if (!valid_format(format) || m < 1 || n < 1 || k < 0 || k % block_weights(format)) return 0;
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return 0;
+  // The plan does not depend on the 2-byte activation type.
+  GemvPlan plan = plan_gemv_fast(format, kBF16, m, n, k, (long long)1 << 40, *dev);
+  return plan.supported ? plan.scratch_bytes : 0;
+}
+
+int32_t tb200_gguf_device_status(uint32_t* status, TensorErrorV1* error) {
+  unsigned int a = 0, b = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(error, "cudaDeviceSynchronize", e);
+  if ((e = read_gemv_status(&a, true)) != cudaSuccess) return cuda_fail(error, "reading GEMV status", e);
+  if ((e = read_gemm_status(&b, true)) != cudaSuccess) return cuda_fail(error, "reading GEMM status", e);
+  if (status) *status = a ? a : b;
+  if (a || b)
+    return fail(error, TENSOR_ERROR_PROVIDER, "a bounded device-side wait gave up (gemv 0x%x, gemm 0x%x)", a, b);
+  return ok(error);
+}
+
+int32_t tb200_gguf_dequant(int32_t format, const void* w, float* out, int64_t n, int64_t k, void* stream,
+                           TensorErrorV1* error) {
+  if (int32_t s = check_shape(error, format, 0, n, k)) return s;
+  if (n == 0 || k == 0) return ok(error);
+  if (int32_t s = check_pointer(error, "w", w, 2, true)) return s;
+  if (int32_t s = check_pointer(error, "out", out, 16, true)) return s;
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaError_t e = launch_dequant(format, static_cast<const uint8_t*>(w), out, n, k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(error, "dequant launch", e);
+  return ok(error);
+}
+
+int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
+                        int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
+                        TensorErrorV1* error) {
+  if (int32_t s = check_shape(error, format, m, n, k)) return s;
+  if (x_dtype != TENSOR_FLOAT16 && x_dtype != TENSOR_BFLOAT16 && x_dtype != TENSOR_FLOAT32)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "activation dtype %d is not float16, bfloat16 or float32", x_dtype);
+  if (variant < 0 || variant > 2) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (m == 0 || n == 0) return ok(error);
+  if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
+  if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
+  if (int32_t s = check_pointer(error, "out", out, 4, true)) return s;
+  if (int32_t s = check_pointer(error, "scratch", scratch, 256, false)) return s;
+  if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* wp = static_cast<const uint8_t*>(w);
+  if (variant != TB200_VARIANT_SIMPLE) {
+    GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
+    if (plan.supported) {
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st);
+      if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch", e);
+      return ok(error);
+    }
+    if (variant == TB200_VARIANT_FAST)
+      return fail(error, TENSOR_ERROR_ARGUMENT,
+                  "the pipelined GEMV does not cover format %d, dtype %d, m=%lld, n=%lld, k=%lld", format, x_dtype,
+                  (long long)m, (long long)n, (long long)k);
+  }
+  cudaError_t e = launch_gemv_simple(format, x_dtype, x, wp, out, m, n, k, false, st);
+  if (e != cudaSuccess) return cuda_fail(error, "GEMV launch", e);
+  return ok(error);
+}
+
+int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
+                        int64_t n, int64_t k, int32_t variant, void* stream, TensorErrorV1* error) {
+  if (int32_t s = check_shape(error, format, m, n, k)) return s;
+  if (x_dtype != TENSOR_BFLOAT16)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "the GEMM takes bfloat16 activations (dtype 13), got %d", x_dtype);
+  if (variant < 0 || variant > 2) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (m == 0 || n == 0) return ok(error);
+  if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
+  if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
+  if (int32_t s = check_pointer(error, "out", out, 16, true)) return s;
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* wp = static_cast<const uint8_t*>(w);
+  if (variant != TB200_VARIANT_SIMPLE) {
+    if (gemm_fast_supported(format, m, n, k, *dev)) {
+      const char* detail = "";
+      cudaError_t e = launch_gemm_fast(format, x, wp, out, m, n, k, st, &detail);
+      if (e != cudaSuccess) return cuda_fail(error, detail && *detail ? detail : "tcgen05 GEMM launch", e);
+      return ok(error);
+    }
+    if (variant == TB200_VARIANT_FAST)
+      return fail(error, TENSOR_ERROR_ARGUMENT, "the tcgen05 GEMM does not cover format %d, m=%lld, n=%lld, k=%lld",
+                  format, (long long)m, (long long)n, (long long)k);
+  }
+  cudaError_t e = launch_gemv_simple(format, x_dtype, x, wp, out, m, n, k, true, st);
+  if (e != cudaSuccess) return cuda_fail(error, "GEMM launch", e);
+  return ok(error);
+}
+
+// ---- descriptor forms ----------------------------------------------------------------------------
+
+}  // extern "C"
+
+namespace {
+
+struct Parsed {
+  const TensorBufferV1* buffers[4] = {nullptr, nullptr, nullptr, nullptr};
+  int buffer_count = 0;
+  int64_t scalars[5] = {0, 0, 0, 0, 0};
+  int scalar_count = 0;
+};
+
+int32_t parse_call(const TensorCallV1* call, TensorErrorV1* error, int min_buffers, int max_buffers,
+                   int min_scalars, int max_scalars, Parsed* out) {
+  if (!call) return fail(error, TENSOR_ERROR_ABI, "call descriptor is NULL");
+  if (call->abi_version != TENSOR_ABI_VERSION)
+    return fail(error, TENSOR_ERROR_ABI, "unsupported ABI version %u (expected %u)", call->abi_version,
+                TENSOR_ABI_VERSION);
+  if (call->struct_size != sizeof(TensorCallV1))
+    return fail(error, TENSOR_ERROR_ABI, "TensorCallV1 struct_size %u, expected %zu", call->struct_size,
+                sizeof(TensorCallV1));
+  if (call->flags != 0) return fail(error, TENSOR_ERROR_ABI, "call flags must be zero");
+  if (call->stream.device_type != TENSOR_DEVICE_CUDA)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "stream device type %u is not CUDA", call->stream.device_type);
+  if (!call->arguments && call->argument_count)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "argument array is NULL");
+  for (uint32_t i = 0; i < call->argument_count; ++i) {
+    const TensorArgumentV1& a = call->arguments[i];
+    if (a.kind == TENSOR_ARG_BUFFER) {
+      if (out->scalar_count) return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: buffers must precede scalars", i);
+      if (out->buffer_count == max_buffers) return fail(error, TENSOR_ERROR_ARGUMENT, "too many buffer arguments");
+      if (a.buffer.device_type != TENSOR_DEVICE_CUDA)
+        return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: buffer is not on a CUDA device", i);
+      if (a.buffer.device_ordinal != call->stream.device_ordinal)
+        return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: buffer on device %d, stream on device %d", i,
+                    a.buffer.device_ordinal, call->stream.device_ordinal);
+      if (a.dtype != a.buffer.dtype)
+        return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: dtype %u does not match its buffer's %u", i, a.dtype,
+                    a.buffer.dtype);
+      if (a.scalar != 0) return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: buffer with a scalar payload", i);
+      out->buffers[out->buffer_count++] = &a.buffer;
+    } else if (a.kind == TENSOR_ARG_SCALAR) {
+      if (out->scalar_count == max_scalars) return fail(error, TENSOR_ERROR_ARGUMENT, "too many scalar arguments");
+      int64_t v;
+      if (a.dtype == TENSOR_INT32) {
+        int32_t t;
+        memcpy(&t, &a.scalar, 4);
+        v = t;
+      } else if (a.dtype == TENSOR_INT64) {
+        memcpy(&v, &a.scalar, 8);
+      } else {
+        return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: scalar dtype %u is not int32 or int64", i, a.dtype);
+      }
+      out->scalars[out->scalar_count++] = v;
+    } else {
+      return fail(error, TENSOR_ERROR_ARGUMENT, "argument %u: unsupported kind %u", i, a.kind);
+    }
+  }
+  if (out->buffer_count < min_buffers || out->scalar_count < min_scalars)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "expected at least %d buffers and %d scalars, got %d and %d", min_buffers,
+                min_scalars, out->buffer_count, out->scalar_count);
+  return TENSOR_OK;
+}
+
+int32_t check_buffer(TensorErrorV1* error, const char* name, const TensorBufferV1* b, int32_t dtype_a,
+                     int32_t dtype_b, int64_t elements) {
+  if ((int32_t)b->dtype != dtype_a && (int32_t)b->dtype != dtype_b)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "%s has dtype %u", name, b->dtype);
+  const int64_t need = elements * dtype_bytes((int32_t)b->dtype);
+  if ((int64_t)b->byte_size != need)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "%s holds %llu bytes, the shape needs %lld", name,
+                (unsigned long long)b->byte_size, (long long)need);
+  if (!b->address && need) return fail(error, TENSOR_ERROR_ARGUMENT, "%s has a NULL address", name);
+  return TENSOR_OK;
+}
+
+// Run on the stream's device, restoring the caller's current device afterwards.
+struct DeviceScope {
+  int previous = -1;
+  cudaError_t status;
+  explicit DeviceScope(int ordinal) {
+    status = cudaGetDevice(&previous);
+    if (status == cudaSuccess && previous != ordinal) status = cudaSetDevice(ordinal);
+  }
+  ~DeviceScope() {
+    if (previous >= 0) cudaSetDevice(previous);
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+int32_t tb200_gguf_dequant_v1(const TensorCallV1* call, TensorErrorV1* error) {
+  Parsed p;
+  if (int32_t s = parse_call(call, error, 2, 2, 3, 3, &p)) return s;
+  const int64_t n = p.scalars[0], k = p.scalars[1];
+  const int32_t format = (int32_t)p.scalars[2];
+  if (int32_t s = check_shape(error, format, 0, n, k)) return s;
+  if (int32_t s = check_buffer(error, "w", p.buffers[0], TENSOR_UINT8, TENSOR_UINT8, n * row_bytes(format, k))) return s;
+  if (int32_t s = check_buffer(error, "out", p.buffers[1], TENSOR_FLOAT32, TENSOR_FLOAT32, n * k)) return s;
+  DeviceScope scope(call->stream.device_ordinal);
+  if (scope.status != cudaSuccess) return cuda_fail(error, "selecting the stream's device", scope.status);
+  return tb200_gguf_dequant(format, (const void*)p.buffers[0]->address, (float*)p.buffers[1]->address, n, k,
+                            (void*)call->stream.handle, error);
+}
+
+int32_t tb200_gguf_gemv_v1(const TensorCallV1* call, TensorErrorV1* error) {
+  Parsed p;
+  if (int32_t s = parse_call(call, error, 3, 4, 4, 5, &p)) return s;
+  const int64_t m = p.scalars[0], n = p.scalars[1], k = p.scalars[2];
+  const int32_t format = (int32_t)p.scalars[3];
+  const int32_t variant = p.scalar_count > 4 ? (int32_t)p.scalars[4] : 0;
+  if (int32_t s = check_shape(error, format, m, n, k)) return s;
+  const TensorBufferV1* x = p.buffers[0];
+  if (x->dtype != TENSOR_FLOAT16 && x->dtype != TENSOR_BFLOAT16 && x->dtype != TENSOR_FLOAT32)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "x has dtype %u; expected float16, bfloat16 or float32", x->dtype);
+  if (int32_t s = check_buffer(error, "x", x, (int32_t)x->dtype, (int32_t)x->dtype, m * k)) return s;
+  if (int32_t s = check_buffer(error, "w", p.buffers[1], TENSOR_UINT8, TENSOR_UINT8, n * row_bytes(format, k))) return s;
+  if (int32_t s = check_buffer(error, "out", p.buffers[2], TENSOR_FLOAT32, TENSOR_FLOAT32, m * n)) return s;
+  void* scratch = nullptr;
+  int64_t scratch_bytes = 0;
+  if (p.buffer_count == 4) {
+    if (p.buffers[3]->dtype != TENSOR_UINT8) return fail(error, TENSOR_ERROR_ARGUMENT, "scratch must be uint8");
+    scratch = (void*)p.buffers[3]->address;
+    scratch_bytes = (int64_t)p.buffers[3]->byte_size;
+  }
+  DeviceScope scope(call->stream.device_ordinal);
+  if (scope.status != cudaSuccess) return cuda_fail(error, "selecting the stream's device", scope.status);
+  return tb200_gguf_gemv(format, (int32_t)x->dtype, (const void*)x->address, (const void*)p.buffers[1]->address,
+                         (float*)p.buffers[2]->address, m, n, k, scratch, scratch_bytes, variant,
+                         (void*)call->stream.handle, error);
+}
+
+int32_t tb200_gguf_gemm_v1(const TensorCallV1* call, TensorErrorV1* error) {
+  Parsed p;
+  if (int32_t s = parse_call(call, error, 3, 3, 4, 5, &p)) return s;
+  const int64_t m = p.scalars[0], n = p.scalars[1], k = p.scalars[2];
+  const int32_t format = (int32_t)p.scalars[3];
+  const int32_t variant = p.scalar_count > 4 ? (int32_t)p.scalars[4] : 0;
+  if (int32_t s = check_shape(error, format, m, n, k)) return s;
+  if (int32_t s = check_buffer(error, "x", p.buffers[0], TENSOR_BFLOAT16, TENSOR_BFLOAT16, m * k)) return s;
+  if (int32_t s = check_buffer(error, "w", p.buffers[1], TENSOR_UINT8, TENSOR_UINT8, n * row_bytes(format, k))) return s;
+  if (int32_t s = check_buffer(error, "out", p.buffers[2], TENSOR_FLOAT32, TENSOR_FLOAT32, m * n)) return s;
+  DeviceScope scope(call->stream.device_ordinal);
+  if (scope.status != cudaSuccess) return cuda_fail(error, "selecting the stream's device", scope.status);
+  return tb200_gguf_gemm(format, TENSOR_BFLOAT16, (const void*)p.buffers[0]->address,
+                         (const void*)p.buffers[1]->address, (float*)p.buffers[2]->address, m, n, k, variant,
+                         (void*)call->stream.handle, error);
+}
+
+}  // extern "C"

@@ -1,0 +1,354 @@
+// Prefill GEMM on sm_100a: out[m, n] (fp32) = x[m, k] (bf16) . dequant(w[n, k])^T, weights rounded
+// to bf16 (round-to-nearest-even of the exact fp32 decode), fp32 accumulation in tensor memory.
+//
+// Replaces the reference's `_packed` kernel (benchmarks/kernels/showcase/kernels.py:116-119),
+// which decodes GGML blocks to 16-bit operands in shared memory and runs `mma.sync`
+// (benchmarks/kernels/showcase/benchmark.py:471-477, showcase/README.md:105-108).
+//
+// Orientation: the 128 weight rows of a tile sit on the MMA M axis (TMEM lanes), up to 256 tokens
+// on the MMA N axis (TMEM columns), so one decoded weight tile is reused by 256 tokens.
+//
+// One CTA = one 128 x 256 output tile, 10 warps:
+//   warp 0      TMA producer: activation tiles [256 tokens x 64 k] bf16, 128-byte swizzle
+//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits to mbarriers
+//   warps 2..9  decode raw GGUF blocks -> bf16, store the weight tile [128 x 64] into shared
+//               memory in the same swizzled K-major layout TMA would produce, then drain the
+//               accumulator (tcgen05.ld) and store fp32 results
+// Two CTAs are resident per SM (256 TMEM columns and ~97 KB shared memory each), so one CTA's
+// decode / epilogue overlaps the other's MMAs.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kTileN = 128;    // weight rows per tile (MMA M)
+constexpr int kTileTok = 256;  // tokens per tile (MMA N)
+constexpr int kBlockK = 64;    // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kStages = 2;
+constexpr int kDecodeWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kABytes = kTileN * kBlockK * 2;    // 16 KB
+constexpr int kBBytes = kTileTok * kBlockK * 2;  // 32 KB
+constexpr int kTmemCols = 256;
+constexpr int kSmemBytes = kStages * (kABytes + kBBytes) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+// tcgen05 shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 bytes, eight
+// rows form a 1024-byte swizzle atom (stride byte offset), version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                    // descriptor version
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileTok >> 3) << 17) |
+                                ((uint32_t)(kTileN >> 4) << 24);
+
+// 2^23 + v for byte j of `bytes`
+__device__ __forceinline__ float byte_magic(uint32_t bytes, int j) {
+  return __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7540u | (uint32_t)j));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// 32-bit load from a 2-byte aligned address (Q6_K blocks are 210 bytes).
+__device__ __forceinline__ uint32_t load_u32_a2(const uint8_t* p) {
+  if ((reinterpret_cast<uintptr_t>(p) & 2) == 0) return __ldg(reinterpret_cast<const uint32_t*>(p));
+  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(p - 2));
+  const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(p + 2));
+  return __funnelshift_r(lo, hi, 16);
+}
+
+// Store 32 consecutive bf16 of row `r` (k offset 32*h within the 64-wide stage) as four 16-byte
+// chunks at their swizzled positions: chunk c of row r lives at r*128 + ((c ^ (r & 7)) * 16).
+__device__ __forceinline__ void store_row_half(uint8_t* a_tile, int r, int h, const uint32_t (&v)[16]) {
+  uint8_t* row = a_tile + r * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int chunk = (4 * h + c) ^ (r & 7);
+    *reinterpret_cast<uint4*>(row + chunk * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  }
+}
+
+// ---- per-format decode of 32 weights: row `wrow`, k-block kb (64 wide), half h -> 16 bf16x2 -------
+
+template <int FMT> struct Decoder;
+
+template <> struct Decoder<kQ4_K> {
+  // k-block kb: super-block kb/4, group pair p = kb%4; half h is group 2p+h (low / high nibbles
+  // of quant bytes 32p .. 32p+31).
+  __device__ static __forceinline__ void run(const uint8_t* wrow, int kb, int h, uint32_t (&v)[16]) {
+    const uint8_t* blk = wrow + (kb >> 2) * 144;
+    const int p = kb & 3, g = 2 * p + h;
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * p));
+    const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * p));
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const int j = g & 3, sh = 8 * j;
+    uint32_t sc, mn;
+    if (g < 4) {
+      sc = (hdr.y >> sh) & 63u;
+      mn = (hdr.z >> sh) & 63u;
+    } else {
+      sc = ((hdr.w >> sh) & 15u) | (((hdr.y >> (sh + 6)) & 3u) << 4);
+      mn = ((hdr.w >> (sh + 4)) & 15u) | (((hdr.z >> (sh + 6)) & 3u) << 4);
+    }
+    const float dsc = d * (float)sc;
+    const float dm = dmin * (float)mn;
+    const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t nib = (words[i] >> (4 * h)) & 0x0F0F0F0Fu;
+      float f[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) f[b] = fmaf(dsc, byte_magic(nib, b) - 8388608.f, -dm);
+      v[2 * i] = pack_bf16(f[0], f[1]);
+      v[2 * i + 1] = pack_bf16(f[2], f[3]);
+    }
+  }
+};
+
+template <> struct Decoder<kQ6_K> {
+  // k-block kb: super-block kb/4, j = kb%4 covers weights 64j .. 64j+63: half-block j/2, quarters
+  // 2(j%2)+h; ql bytes 64(j/2) + 32h + lane, nibble j%2; qh bytes 32(j/2) + lane, bit pair 2(j%2)+h.
+  __device__ static __forceinline__ void run(const uint8_t* wrow, int kb, int h, uint32_t (&v)[16]) {
+    const uint8_t* blk = wrow + (kb >> 2) * 210;
+    const int j = kb & 3, half = j >> 1, quarter = 2 * (j & 1) + h;
+    const uint8_t* ql = blk + 64 * half + 32 * h;
+    const uint8_t* qh = blk + 128 + 32 * half;
+    const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(blk + 208))));
+    const unsigned short scp = __ldg(reinterpret_cast<const unsigned short*>(blk + 192 + 4 * j + 2 * h));
+    const float ds0 = d * (float)(int)(int8_t)(scp & 0xFF);
+    const float ds1 = d * (float)(int)(int8_t)(scp >> 8);
+    const int lsh = 4 * (j & 1), hsh = 2 * quarter;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t lw = load_u32_a2(ql + 4 * i);
+      const uint32_t hw = load_u32_a2(qh + 4 * i);
+      const uint32_t q = ((lw >> lsh) & 0x0F0F0F0Fu) | (((hw >> hsh) & 0x03030303u) << 4);
+      const float ds = i < 4 ? ds0 : ds1;
+      float f[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) f[b] = (byte_magic(q, b) - 8388640.f) * ds;  // 2^23 + 32
+      v[2 * i] = pack_bf16(f[0], f[1]);
+      v[2 * i + 1] = pack_bf16(f[2], f[3]);
+    }
+  }
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 2)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ w,
+                        float* __restrict__ out, int M, int N, int K, long long row_bytes_) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle needs 1024-byte aligned tiles
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* a_tiles = smem;
+  uint8_t* b_tiles = smem + kStages * kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (kABytes + kBBytes));
+  uint64_t* full_a = bars;               // decode warps -> MMA
+  uint64_t* full_b = bars + kStages;     // TMA -> MMA
+  uint64_t* empty = bars + 2 * kStages;  // MMA -> producers
+  uint64_t* acc_full = bars + 3 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kTileTok;
+  const int n0 = blockIdx.y * kTileN;
+  const int k_blocks = K / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full_a[s], kDecodeThreads);
+      ptx::mbar_init(&full_b[s], 1);
+      ptx::mbar_init(&empty[s], 1);
+    }
+    ptx::mbar_init(acc_full, 1);
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmap_x);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: activations ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % kStages;
+        if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+          report_timeout(0x10000u | (unsigned)kb);
+          break;
+        }
+        ptx::mbar_arrive_expect_tx(&full_b[s], kBBytes);
+        ptx::tma_load_2d(b_tiles + s * kBBytes, &tmap_x, kb * kBlockK, m0, &full_b[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t parity = (kb / kStages) & 1;
+        if (!ptx::mbar_wait(&full_a[s], parity) || !ptx::mbar_wait(&full_b[s], parity)) {
+          report_timeout(0x20000u | (unsigned)kb);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint64_t a_desc = smem_desc_sw128(ptx::smem_addr(a_tiles + s * kABytes));
+        const uint64_t b_desc = smem_desc_sw128(ptx::smem_addr(b_tiles + s * kBBytes));
+#pragma unroll
+        for (int i = 0; i < kBlockK / 16; ++i)  // advance 16 bf16 = 32 bytes = 2 descriptor units
+          ptx::umma_f16(tmem_base, a_desc + 2 * i, b_desc + 2 * i, kInstrDesc, (kb | i) ? 1u : 0u);
+        ptx::umma_commit(&empty[s]);
+      }
+      ptx::umma_commit(acc_full);
+    }
+  } else {
+    // ---------------- decode warps, then epilogue ----------------
+    const int t = threadIdx.x - 64;
+    const int r = t >> 1, h = t & 1;
+    const int grow = min(n0 + r, N - 1);  // rows past N are decoded from the last row and dropped
+    const uint8_t* wrow = w + (long long)grow * row_bytes_;
+    bool ok = true;
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      const int s = kb % kStages;
+      uint32_t v[16];
+      Decoder<FMT>::run(wrow, kb, h, v);
+      if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+        report_timeout(0x30000u | (unsigned)kb);
+        ok = false;
+        break;
+      }
+      store_row_half(a_tiles + s * kABytes, r, h, v);
+      ptx::fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
+      ptx::mbar_arrive(&full_a[s]);
+    }
+    if (ok) {
+      if (!ptx::mbar_wait(acc_full, 0)) {
+        report_timeout(0x40000u);
+        ok = false;
+      }
+    }
+    if (ok) {
+      ptx::tc_fence_after();
+      const int quarter = warp & 3;            // TMEM lanes this warp may read
+      const int col_half = (warp - 2) >> 2;    // warps 2..5 take tokens 0..127, warps 6..9 128..255
+      const int n = n0 + quarter * 32 + lane;  // output column (weight row) of this thread
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        const int col0 = col_half * 128 + c * 32;
+        if (m0 + col0 >= M) break;
+        uint32_t acc[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col0, acc);
+        ptx::tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = m0 + col0 + j;
+            if (tok < M) out[(long long)tok * N + n] = __uint_as_float(acc[j]);
+          }
+        }
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+template <int FMT>
+cudaError_t launch_fmt(const CUtensorMap& tmap, const uint8_t* w, float* out, long long m, long long n,
+                       long long k, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<FMT>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((unsigned)((m + kTileTok - 1) / kTileTok), (unsigned)((n + kTileN - 1) / kTileN));
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, w, out, (int)m, (int)n, (int)k, row_bytes(FMT, k));
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+TB200_DEFINE_STATUS_READER(read_gemm_status)
+
+bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const DeviceInfo& dev) {
+  if (fmt != kQ4_K && fmt != kQ6_K) return false;
+  if (m < 1 || n < 1 || k < 256 || k % 256) return false;
+  if (m > (1 << 24) || n > (1 << 24) || k > (1 << 24)) return false;
+  if ((n + kTileN - 1) / kTileN > 65535) return false;
+  if (row_bytes(fmt, k) % 16) return false;  // 16-byte vector loads (Q4_K) / 4-byte pairs (Q6_K)
+  return dev.max_smem_optin >= kSmemBytes;
+}
+
+cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m, long long n,
+                             long long k, cudaStream_t stream, const char** detail) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) {
+    if (detail) *detail = "cuTensorMapEncodeTiled is not available from the driver";
+    return cudaErrorNotSupported;
+  }
+  // x as a 2-D tensor [m rows, k columns] of bf16; box = 64 columns (128 bytes) x 256 rows,
+  // 128-byte swizzle, rows past m read as zero.
+  CUtensorMap tmap;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)kTileTok};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (detail) *detail = "cuTensorMapEncodeTiled rejected the activation layout";
+    return cudaErrorInvalidValue;
+  }
+  switch (fmt) {
+    case kQ4_K: return launch_fmt<kQ4_K>(tmap, w, out, m, n, k, stream);
+    case kQ6_K: return launch_fmt<kQ6_K>(tmap, w, out, m, n, k, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace tb200

@@ -1,0 +1,547 @@
+// Decode GEMV for batch 1..16 on sm_100a: out[m, n] = x[m, k] . dequant(w[n, k])^T.
+//
+// Replaces the reference's `gemv_packed` (benchmarks/kernels/showcase/kernels.py:116-119) with
+// its fp32-weight x fp32-activation contract (benchmarks/kernels/showcase/benchmark.py:468-470).
+//
+// Regime: HBM-bound.  B200 streams about 43 GB/s per SM, i.e. ~23 raw bytes per SM clock, which
+// leaves ~3 issue slots per 4-bit weight.  A SIMT decode + FMA does not fit in that budget, so:
+//
+//  * a producer warp streams raw super-blocks into a shared-memory ring with 1-D bulk async
+//    copies (cp.async.bulk + mbarrier), one copy per weight row of a 16-row tile, so tens of KB
+//    per SM are in flight without holding registers;
+//  * consumer warps never form fp32 weights.  The 4-bit (or 6-bit) integers are turned into
+//    bf16/fp16 values `offset + q` by one logic op per pair (0x4300|q = 128+q in bf16), which is
+//    exact, and fed to warp-level tensor-core MMAs (m16n8k16, fp32 accumulate) against the staged
+//    activations.  The block scales are applied to the 32-weight partial sums in fp32:
+//        sum_k (d*sc*q - dmin*mn) x = d*sc*(S - offset*Sx) - dmin*mn*Sx,   S = sum (offset+q) x
+//    with Sx = sum of x over the group (computed once per CTA).  Operands are exact, so the result
+//    differs from the fp32 oracle only by summation order.
+//  * m == 1 puts the 8 scale groups of a super-block on the 8 MMA columns (x masked per group),
+//    so scales are applied once per super-block and every lane owns distinct (row, group) pairs;
+//    1 < m <= 16 puts the batch on the columns and applies scales per 32-weight group.
+//  * the K range of a CTA is fixed for its lifetime (x is staged once); row tiles are strided
+//    over CTAs; if K is split across CTAs, partial sums go to caller-provided scratch and the
+//    last CTA to arrive for a row tile adds them in a fixed order (deterministic).
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kTileRows = 16;
+constexpr int kMaxStages = 8;
+constexpr int kSclRowFloats = 18;  // 8 x (scale, offset) pairs + 2 floats of padding (bank spread)
+
+struct GemvArgs {
+  const void* x;
+  const uint8_t* w;
+  float* out;
+  float* partials;
+  unsigned int* counters;
+  int m;
+  long long n;
+  int k;
+  long long row_bytes;
+  int nsb;           // 256-weight super-blocks per row
+  int sb_per_split;  // super-blocks per K range
+  int k_splits;
+  int row_groups;
+  int row_tiles;
+  int stages;
+  int stride_s;   // shared-memory bytes between the rows of a stage
+  int xs_stride;  // shared-memory bytes between staged activation rows
+  int off_stage, off_xs, off_sx, off_red, off_scl;
+};
+
+template <bool F16> struct Magic {
+  static constexpr uint32_t kOr = F16 ? 0x64006400u : 0x43004300u;
+  static constexpr float kOffset = F16 ? 1024.f : 128.f;
+};
+
+// byte j of v as an exact float: 0x4B0000vv is 2^23 + vv.
+__device__ __forceinline__ float byte_to_float(uint32_t v, int j) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540u | (uint32_t)j)) - 8388608.f;
+}
+
+template <bool F16>
+__device__ __forceinline__ float sum8(uint4 v) {
+  float s = 0.f;
+  const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (F16) {
+      float2 f = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
+      s += f.x;
+      s += f.y;
+    } else {
+      s += __uint_as_float(words[i] << 16);
+      s += __uint_as_float(words[i] & 0xFFFF0000u);
+    }
+  }
+  return s;
+}
+
+// Stage the activations of this CTA's K range: rows b < NTB (zero beyond m), each aligned group
+// of four values stored as [x0, x2, x1, x3] so that an MMA B fragment is one contiguous load.
+// Also the per-32-group sums Sx[g][b] in fp32.
+template <bool F16, int NTB>
+__device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
+                                                  int klen) {
+  const int chunks = klen >> 3;  // 8 values (16 bytes) each; a multiple of 32
+  const int total = NTB * chunks;
+  uint8_t* xs = smem + a.off_xs;
+  float* sx = reinterpret_cast<float*>(smem + a.off_sx);
+  const uint16_t* xg = static_cast<const uint16_t*>(a.x);
+  for (int base = 0; base < total; base += kConsumerThreads) {
+    const int idx = base + ctid;
+    const bool valid = idx < total;
+    const int b = valid ? idx / chunks : 0;
+    const int c = valid ? idx - b * chunks : 0;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (valid && b < a.m)
+      v = *reinterpret_cast<const uint4*>(xg + (long long)b * a.k + k0 + (c << 3));
+    float s = sum8<F16>(v);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (valid) {
+      uint4 p;
+      p.x = __byte_perm(v.x, v.y, 0x5410);
+      p.y = __byte_perm(v.x, v.y, 0x7632);
+      p.z = __byte_perm(v.z, v.w, 0x5410);
+      p.w = __byte_perm(v.z, v.w, 0x7632);
+      *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = p;
+      if ((c & 3) == 0) sx[(c >> 2) * NTB + b] = s;
+    }
+  }
+}
+
+// ---- Q4_K, batch on the MMA columns (1 < m <= 16) ------------------------------------------------
+template <bool F16, int NT>
+__device__ __forceinline__ void q4k_item_batch(const GemvArgs& a, const uint8_t* stage, const uint8_t* smem,
+                                               float* scl, int sbl, int lane, float (&acc)[NT][4]) {
+  constexpr int NTB = NT * 8;
+  constexpr uint32_t kOr = Magic<F16>::kOr;
+  const int gid = lane >> 2, tig = lane & 3;
+  const uint8_t* xs = smem + a.off_xs;
+  const float* sx = reinterpret_cast<const float*>(smem + a.off_sx);
+  __syncwarp();
+  {  // scale preparation: lane -> (row, half of the groups)
+    const int r = lane >> 1, hf = lane & 1;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(stage + r * a.stride_s + sbl * 144);
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
+    const uint32_t mnv =
+        hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
+    float2* dst = reinterpret_cast<float2*>(scl + r * kSclRowFloats + hf * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float dsc = d * byte_to_float(scv, j);
+      const float e = fmaf(Magic<F16>::kOffset, dsc, dmin * byte_to_float(mnv, j));
+      dst[j] = make_float2(dsc, e);
+    }
+  }
+  __syncwarp();
+  const uint8_t* rowA = stage + gid * a.stride_s + sbl * 144 + 16 + tig * 8;
+  const uint8_t* rowB = rowA + 8 * a.stride_s;
+  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint2 wa = *reinterpret_cast<const uint2*>(rowA + p * 32);
+    const uint2 wb = *reinterpret_cast<const uint2*>(rowB + p * 32);
+#pragma unroll
+    for (int nib = 0; nib < 2; ++nib) {
+      const int g = 2 * p + nib;
+      const int sh = 4 * nib;
+      const uint32_t a0 = ((wa.x >> sh) & 0x000F000Fu) | kOr, a1 = ((wb.x >> sh) & 0x000F000Fu) | kOr;
+      const uint32_t a2 = ((wa.x >> (sh + 8)) & 0x000F000Fu) | kOr, a3 = ((wb.x >> (sh + 8)) & 0x000F000Fu) | kOr;
+      const uint32_t a4 = ((wa.y >> sh) & 0x000F000Fu) | kOr, a5 = ((wb.y >> sh) & 0x000F000Fu) | kOr;
+      const uint32_t a6 = ((wa.y >> (sh + 8)) & 0x000F000Fu) | kOr, a7 = ((wb.y >> (sh + 8)) & 0x000F000Fu) | kOr;
+      const float2 sA = *reinterpret_cast<const float2*>(scl + gid * kSclRowFloats + g * 2);
+      const float2 sB = *reinterpret_cast<const float2*>(scl + (gid + 8) * kSclRowFloats + g * 2);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint4 xb = *reinterpret_cast<const uint4*>(xs + (size_t)(gid + 8 * t) * a.xs_stride +
+                                                         ((sbl * 256 + 32 * g + 8 * tig) << 1));
+        float c[4];
+        ptx::mma16816<F16>(c, a0, a1, a2, a3, xb.x, xb.y, zero);
+        ptx::mma16816<F16>(c, a4, a5, a6, a7, xb.z, xb.w, c);
+        const float2 sxv = *reinterpret_cast<const float2*>(sx + (sbl * 8 + g) * NTB + 8 * t + 2 * tig);
+        acc[t][0] = fmaf(sA.x, c[0], acc[t][0]);
+        acc[t][1] = fmaf(sA.x, c[1], acc[t][1]);
+        acc[t][2] = fmaf(sB.x, c[2], acc[t][2]);
+        acc[t][3] = fmaf(sB.x, c[3], acc[t][3]);
+        acc[t][0] = fmaf(-sA.y, sxv.x, acc[t][0]);
+        acc[t][1] = fmaf(-sA.y, sxv.y, acc[t][1]);
+        acc[t][2] = fmaf(-sB.y, sxv.x, acc[t][2]);
+        acc[t][3] = fmaf(-sB.y, sxv.y, acc[t][3]);
+      }
+    }
+  }
+}
+
+// ---- Q4_K, scale groups on the MMA columns (m == 1) ----------------------------------------------
+// Lane (gid, tig) holds the weights of rows gid and gid+8 that sit in 16-byte chunks tig and tig+4
+// of the 128 quant bytes; chunk c belongs to group pair c/2, so in one MMA different lanes may feed
+// different groups.  Column j of the MMA collects group j: the B fragment of lane (gid, tig) is its
+// slice of x when the lane's weights are in group gid, else zero.
+template <bool F16>
+__device__ __forceinline__ void q4k_item_groups(const GemvArgs& a, const uint8_t* stage, const uint8_t* smem,
+                                                int sbl, int lane, const uint32_t (&mask)[2][2],
+                                                float& accA, float& accB) {
+  constexpr uint32_t kOr = Magic<F16>::kOr;
+  const int gid = lane >> 2, tig = lane & 3;
+  const uint8_t* xs = smem + a.off_xs;
+  const float* sx = reinterpret_cast<const float*>(smem + a.off_sx);
+  const uint8_t* blkA = stage + gid * a.stride_s + sbl * 144;
+  const uint8_t* blkB = blkA + 8 * a.stride_s;
+  // this lane's slice of x: group gid, 16 values starting at 16*(tig&1)
+  const uint8_t* xp = xs + ((sbl * 256 + 32 * gid + 16 * (tig & 1)) << 1);
+  const uint4 x0 = *reinterpret_cast<const uint4*>(xp);
+  const uint4 x1 = *reinterpret_cast<const uint4*>(xp + 16);
+  const uint32_t xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int ci = 0; ci < 2; ++ci) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(blkA + 16 + 16 * (tig + 4 * ci));
+    const uint4 qb = *reinterpret_cast<const uint4*>(blkB + 16 + 16 * (tig + 4 * ci));
+    const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
+    const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int nib = 0; nib < 2; ++nib) {
+        const int sh = 4 * nib;
+        const uint32_t a0 = ((wa[i] >> sh) & 0x000F000Fu) | kOr, a1 = ((wb[i] >> sh) & 0x000F000Fu) | kOr;
+        const uint32_t a2 = ((wa[i] >> (sh + 8)) & 0x000F000Fu) | kOr;
+        const uint32_t a3 = ((wb[i] >> (sh + 8)) & 0x000F000Fu) | kOr;
+        ptx::mma16816<F16>(c, a0, a1, a2, a3, xr[2 * i] & mask[ci][nib], xr[2 * i + 1] & mask[ci][nib], c);
+      }
+    }
+  }
+  // c[0], c[1]: row gid, groups 2*tig, 2*tig+1; c[2], c[3]: row gid+8, same groups.
+  const float2 sxv = *reinterpret_cast<const float2*>(sx + sbl * 8 + 2 * tig);
+  const int sel = (tig & 1) * 16;
+  const bool upper = tig >= 2;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const uint4 hdr = *reinterpret_cast<const uint4*>(rr ? blkB : blkA);
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const uint32_t h0 = hdr.y >> sel, h1 = hdr.z >> sel, h2 = hdr.w >> sel;
+    const uint32_t scp = upper ? ((h2 & 0x0F0Fu) | ((h0 >> 2) & 0x3030u)) : (h0 & 0x3F3Fu);
+    const uint32_t mnp = upper ? (((h2 >> 4) & 0x0F0Fu) | ((h1 >> 2) & 0x3030u)) : (h1 & 0x3F3Fu);
+    const float dsc0 = d * byte_to_float(scp, 0), dsc1 = d * byte_to_float(scp, 1);
+    const float e0 = fmaf(Magic<F16>::kOffset, dsc0, dmin * byte_to_float(mnp, 0));
+    const float e1 = fmaf(Magic<F16>::kOffset, dsc1, dmin * byte_to_float(mnp, 1));
+    float v = rr ? accB : accA;
+    v = fmaf(dsc0, c[2 * rr], v);
+    v = fmaf(dsc1, c[2 * rr + 1], v);
+    v = fmaf(-e0, sxv.x, v);
+    v = fmaf(-e1, sxv.y, v);
+    if (rr) accB = v; else accA = v;
+  }
+}
+
+template <int FMT, bool F16, int NT, bool GROUPS>
+__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a) {
+  static_assert(FMT == kQ4_K, "only Q4_K is pipelined so far");
+  constexpr int NTB = GROUPS ? 1 : NT * 8;
+  constexpr int kBlockBytes = Fmt<FMT>::kBytes;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kMaxStages;
+  uint64_t* cbar = empty + kMaxStages;  // consumer-only barrier (bounded, unlike bar.sync)
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ks = blockIdx.x % a.k_splits;
+  const int rg = blockIdx.x / a.k_splits;
+  const int sb0 = ks * a.sb_per_split;
+  const int nsb_local = min(a.sb_per_split, a.nsb - sb0);
+  const uint32_t range_bytes = (uint32_t)nsb_local * kBlockBytes;
+  const int S = a.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], kConsumerWarps);
+    }
+    ptx::mbar_init(cbar, kConsumerWarps);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer: one bulk copy per weight row of the tile ----------------
+    const uint8_t* src0 = a.w + (long long)sb0 * kBlockBytes;
+    int i = 0;
+    for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
+      const int s = i % S;
+      if (i >= S && !ptx::mbar_wait(&empty[s], ((i / S) - 1) & 1)) {
+        report_timeout(0x10000u | (unsigned)s);
+        break;
+      }
+      const long long row0 = (long long)rt * kTileRows;
+      const int rows = (int)min((long long)kTileRows, a.n - row0);
+      if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
+      __syncwarp();
+      if (lane < rows)
+        ptx::bulk_g2s(smem + a.off_stage + (size_t)s * kTileRows * a.stride_s + (size_t)lane * a.stride_s,
+                      src0 + (row0 + lane) * a.row_bytes, range_bytes, &full[s]);
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  const int cw = warp;
+  const int ctid = threadIdx.x;
+  uint32_t cphase = 0;
+  // All consumer warps meet here; returns false if the (bounded) wait gave up.
+  auto consumer_sync = [&]() -> bool {
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(cbar);
+    const bool ok = ptx::mbar_wait(cbar, cphase & 1);
+    ++cphase;
+    if (!ok) report_timeout(0x30000u);
+    return ok;
+  };
+  stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256);
+  if (!consumer_sync()) return;
+
+  const int gid = lane >> 2, tig = lane & 3;
+  uint32_t mask[2][2] = {{0u, 0u}, {0u, 0u}};
+  if constexpr (GROUPS) {
+#pragma unroll
+    for (int ci = 0; ci < 2; ++ci)
+#pragma unroll
+      for (int nib = 0; nib < 2; ++nib)
+        mask[ci][nib] = (gid == 2 * (tig >> 1) + 4 * ci + nib) ? 0xFFFFFFFFu : 0u;
+  }
+  float* red = reinterpret_cast<float*>(smem + a.off_red);
+  float* scl = reinterpret_cast<float*>(smem + a.off_scl) + cw * (kTileRows * kSclRowFloats);
+  constexpr int kRedPerBuf = kConsumerWarps * NTB * kTileRows;
+
+  int i = 0;
+  for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
+    const int s = i % S;
+    if (!ptx::mbar_wait(&full[s], (i / S) & 1)) {
+      report_timeout(0x20000u | (unsigned)s);
+      return;
+    }
+    const uint8_t* stage = smem + a.off_stage + (size_t)s * kTileRows * a.stride_s;
+    float* redbuf = red + (i & 1) * kRedPerBuf;
+    if constexpr (GROUPS) {
+      float accA = 0.f, accB = 0.f;
+      for (int sbl = cw; sbl < nsb_local; sbl += kConsumerWarps)
+        q4k_item_groups<F16>(a, stage, smem, sbl, lane, mask, accA, accB);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty[s]);
+      accA += __shfl_xor_sync(0xffffffffu, accA, 1);
+      accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+      accB += __shfl_xor_sync(0xffffffffu, accB, 1);
+      accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+      if (tig == 0) {
+        redbuf[cw * kTileRows + gid] = accA;
+        redbuf[cw * kTileRows + gid + 8] = accB;
+      }
+    } else {
+      float acc[NT][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
+      for (int sbl = cw; sbl < nsb_local; sbl += kConsumerWarps)
+        q4k_item_batch<F16, NT>(a, stage, smem, scl, sbl, lane, acc);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty[s]);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int col = 8 * t + 2 * tig;
+        redbuf[(cw * NTB + col) * kTileRows + gid] = acc[t][0];
+        redbuf[(cw * NTB + col + 1) * kTileRows + gid] = acc[t][1];
+        redbuf[(cw * NTB + col) * kTileRows + gid + 8] = acc[t][2];
+        redbuf[(cw * NTB + col + 1) * kTileRows + gid + 8] = acc[t][3];
+      }
+    }
+    if (!consumer_sync()) return;
+    // cross-warp sum in warp order; thread e -> (column e / 16, row e % 16)
+    const int row = ctid & 15, col = ctid >> 4;
+    const long long grow = (long long)rt * kTileRows + row;
+    const bool mine = col < NTB && col < a.m && grow < a.n;
+    float v = 0.f;
+    if (col < NTB) {
+#pragma unroll
+      for (int w8 = 0; w8 < kConsumerWarps; ++w8) v += redbuf[(w8 * NTB + col) * kTileRows + row];
+    }
+    if (a.k_splits == 1) {
+      if (mine) a.out[(long long)col * a.n + grow] = v;
+    } else {
+      if (mine) a.partials[((long long)ks * a.m + col) * a.n + grow] = v;
+      __threadfence();
+      if (!consumer_sync()) return;
+      if (ctid == 0) {
+        const unsigned int old = atomicAdd(&a.counters[rt], 1u);
+        const int last = old == (unsigned)(a.k_splits - 1);
+        if (last) a.counters[rt] = 0u;  // every other K range has already arrived
+        s_last = last;
+      }
+      if (!consumer_sync()) return;
+      if (s_last) {
+        __threadfence();
+        if (mine) {
+          float total = 0.f;
+          for (int q = 0; q < a.k_splits; ++q)
+            total += __ldcg(&a.partials[((long long)q * a.m + col) * a.n + grow]);
+          a.out[(long long)col * a.n + grow] = total;
+        }
+      }
+    }
+  }
+}
+
+inline int round_up(int v, int to) { return (v + to - 1) / to * to; }
+
+// smallest s >= bytes with s % 128 == want (want a multiple of 16)
+inline int pad_stride(int bytes, int want) {
+  int s = round_up(bytes, 16);
+  while (s % 128 != want) s += 16;
+  return s;
+}
+
+struct Layout {
+  int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, total;
+};
+
+Layout make_layout(int fmt, int m, int sb_per_split, int stages) {
+  const bool groups = m == 1;
+  const int ntb = groups ? 1 : (m <= 8 ? 8 : 16);
+  Layout L;
+  L.stride_s = pad_stride(sb_per_split * block_bytes(fmt), groups ? 64 : 32);
+  L.xs_stride = pad_stride(sb_per_split * 512, 64);
+  L.stage_bytes = kTileRows * L.stride_s;
+  int off = 256;  // mbarriers: full[8], empty[8], consumer barrier
+  L.off_stage = off;
+  off += stages * L.stage_bytes;
+  L.off_xs = off;
+  off += ntb * L.xs_stride;
+  L.off_sx = off;
+  off += round_up(sb_per_split * 8 * ntb * 4, 128);
+  L.off_red = off;
+  off += 2 * kConsumerWarps * ntb * kTileRows * 4;
+  L.off_scl = off;
+  off += groups ? 0 : kConsumerWarps * kTileRows * kSclRowFloats * 4;
+  L.total = round_up(off, 128);
+  return L;
+}
+
+}  // namespace
+
+TB200_DEFINE_STATUS_READER(read_gemv_status)
+
+GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
+                        long long scratch_bytes_available, const DeviceInfo& dev) {
+  GemvPlan best;
+  if (fmt != kQ4_K) return best;
+  if (xt != kBF16 && xt != kF16) return best;
+  if (m < 1 || m > 16 || n < 1 || k < 256 || k % 256 || k > (1 << 24)) return best;
+  const long long rb = row_bytes(fmt, k);
+  if (rb % 16) return best;
+  const int nsb = (int)(k / 256);
+  const long long row_tiles = (n + kTileRows - 1) / kTileRows;
+  if (row_tiles > 0x7fffffffLL) return best;
+  const int slots = dev.sm_count;  // one CTA per SM
+  double best_cost = 1e300;
+  for (int splits = 1; splits <= nsb && splits <= 64; ++splits) {
+    const int per = (nsb + splits - 1) / splits;
+    if ((splits - 1) * per >= nsb) continue;  // an empty K range
+    const long long need =
+        splits > 1 ? ((row_tiles * 4 + 255) / 256 * 256 + (long long)splits * m * n * 4) : 0;
+    if (need > scratch_bytes_available) continue;
+    int stages = 0;
+    Layout L{};
+    for (int s = kMaxStages; s >= 2; --s) {
+      L = make_layout(fmt, (int)m, per, s);
+      if (L.total <= dev.max_smem_optin) { stages = s; break; }
+    }
+    if (!stages) continue;
+    // splitting K so finely that the ring holds little data cannot keep HBM busy
+    if (splits > 1 && (long long)stages * L.stage_bytes < 64 * 1024) continue;
+    int groups = (int)((long long)slots / splits < row_tiles ? slots / splits : row_tiles);
+    if (groups < 1) continue;
+    const long long tiles_per_cta = (row_tiles + groups - 1) / groups;
+    // time ~ bytes the slowest CTA streams, plus the partial-sum traffic of a split
+    double cost = (double)tiles_per_cta * per * block_bytes(fmt) * kTileRows;
+    if (splits > 1) cost += (double)tiles_per_cta * kTileRows * m * 4 * 2 + 2000.0 * tiles_per_cta;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best.supported = true;
+      best.k_splits = splits;
+      best.row_groups = groups;
+      best.sb_per_split = per;
+      best.stages = stages;
+      best.stage_bytes = L.stage_bytes;
+      best.smem_bytes = L.total;
+      best.scratch_bytes = need;
+    }
+  }
+  return best;
+}
+
+template <int FMT, bool F16, int NT, bool GROUPS>
+static cudaError_t launch_variant(const GemvArgs& a, int grid, int smem, cudaStream_t stream) {
+  auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  kernel<<<grid, kThreads, smem, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
+                             float* out, long long m, long long n, long long k, void* scratch,
+                             cudaStream_t stream) {
+  if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
+  GemvArgs a{};
+  a.x = x;
+  a.w = w;
+  a.out = out;
+  a.m = (int)m;
+  a.n = n;
+  a.k = (int)k;
+  a.row_bytes = row_bytes(fmt, k);
+  a.nsb = (int)(k / 256);
+  a.sb_per_split = plan.sb_per_split;
+  a.k_splits = plan.k_splits;
+  a.row_groups = plan.row_groups;
+  a.row_tiles = (int)((n + kTileRows - 1) / kTileRows);
+  a.stages = plan.stages;
+  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages);
+  a.stride_s = L.stride_s;
+  a.xs_stride = L.xs_stride;
+  a.off_stage = L.off_stage;
+  a.off_xs = L.off_xs;
+  a.off_sx = L.off_sx;
+  a.off_red = L.off_red;
+  a.off_scl = L.off_scl;
+  if (plan.k_splits > 1) {
+    if (!scratch) return cudaErrorInvalidValue;
+    a.counters = static_cast<unsigned int*>(scratch);
+    a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + ((a.row_tiles * 4 + 255) / 256) * 256);
+  }
+  const int grid = plan.k_splits * plan.row_groups;
+  const bool f16 = xt == kF16;
+  if (m == 1)
+    return f16 ? launch_variant<kQ4_K, true, 1, true>(a, grid, L.total, stream)
+               : launch_variant<kQ4_K, false, 1, true>(a, grid, L.total, stream);
+  if (m <= 8)
+    return f16 ? launch_variant<kQ4_K, true, 1, false>(a, grid, L.total, stream)
+               : launch_variant<kQ4_K, false, 1, false>(a, grid, L.total, stream);
+  return f16 ? launch_variant<kQ4_K, true, 2, false>(a, grid, L.total, stream)
+             : launch_variant<kQ4_K, false, 2, false>(a, grid, L.total, stream);
+}
+
+}  // namespace tb200

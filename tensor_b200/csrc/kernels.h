@@ -1,0 +1,52 @@
+// Internal launch interface between the C-ABI layer (cabi.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb200 {
+
+struct DeviceInfo {
+  int ordinal = -1;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int cc_major = 0, cc_minor = 0;
+};
+// Properties of the current device (cached per ordinal).  Returns nullptr on a CUDA error.
+const DeviceInfo* device_info(cudaError_t* err);
+
+cudaError_t launch_dequant(int fmt, const uint8_t* w, float* out, long long n, long long k,
+                           cudaStream_t stream);
+
+// SIMT fallback: any m, any K that is a multiple of the block size.  weights_bf16 rounds each
+// decoded weight to bf16 first (the GEMM operand contract).
+cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w, float* out,
+                               long long m, long long n, long long k, bool weights_bf16,
+                               cudaStream_t stream);
+
+// Bulk-copy pipeline + mma.sync GEMV for m <= 16.
+struct GemvPlan {
+  bool supported = false;
+  int k_splits = 1;        // CTAs along K per row tile
+  int row_groups = 0;      // CTAs along N
+  int sb_per_split = 0;    // 256-weight super-blocks per K range (last may be shorter)
+  int stages = 0;
+  int stage_bytes = 0;
+  int smem_bytes = 0;
+  long long scratch_bytes = 0;
+};
+GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
+                        long long scratch_bytes_available, const DeviceInfo& dev);
+cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
+                             float* out, long long m, long long n, long long k, void* scratch,
+                             cudaStream_t stream);
+
+// tcgen05 / TMEM prefill GEMM (bf16 operands, fp32 accumulate).
+bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const DeviceInfo& dev);
+cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m,
+                             long long n, long long k, cudaStream_t stream, const char** detail);
+
+// Sticky status words of the pipelined kernels (bounded waits that gave up); these synchronise.
+cudaError_t read_gemv_status(unsigned int* value, bool clear);
+cudaError_t read_gemm_status(unsigned int* value, bool clear);
+
+}  // namespace tb200

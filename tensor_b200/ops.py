@@ -1,0 +1,158 @@
+"""Host-side operators over torch CUDA tensors.  PyTorch supplies device memory and streams; the
+arithmetic is entirely in the C library (``tensor_b200/csrc``), reached through the reference's
+descriptor calling convention (``*_v1`` entry points of include/tensor_b200_gguf.h)."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import abi
+from ._native import lib, raise_for_status
+from .formats import get_format
+
+_TORCH_DTYPE_IDS = {torch.uint8: 3, torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
+_VARIANTS = {"auto": 0, "simple": 1, "fast": 2, 0: 0, 1: 1, 2: 2}
+
+
+def _require_cuda(name: str, t: torch.Tensor) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must live on a CUDA device (this path has no CPU fallback)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _buffer(name: str, t: torch.Tensor, shape=None) -> abi.TensorArgumentV1:
+    try:
+        dtype = _TORCH_DTYPE_IDS[t.dtype]
+    except KeyError:
+        raise ValueError(f"{name} has unsupported dtype {t.dtype}") from None
+    return abi.buffer_argument(t.data_ptr(), t.numel() * t.element_size(), dtype, t.device.index,
+                               shape if shape is not None else tuple(t.shape))
+
+
+def _stream_handle(device: torch.device, stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream(device).cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+def _same_device(*tensors) -> torch.device:
+    device = tensors[0].device
+    for t in tensors[1:]:
+        if t is not None and t.device != device:
+            raise ValueError("all buffers of a call must live on the same device")
+    return device
+
+
+def _invoke(fn, arguments, device, stream) -> None:
+    call, keep = abi.make_call(arguments, device.index, _stream_handle(device, stream))
+    error = abi.TensorErrorV1()
+    status = fn(ctypes.byref(call), ctypes.byref(error))
+    del keep
+    raise_for_status(status, error)
+
+
+def weight_bytes(encoding, n: int, k: int) -> int:
+    return get_format(encoding).weight_bytes(n, k)
+
+
+def gemv_scratch_bytes(encoding, m: int, n: int, k: int) -> int:
+    """Scratch the GEMV can use at this shape on the current device (0: never splits K)."""
+    return int(lib().tb200_gguf_gemv_scratch_bytes(get_format(encoding).type_id, m, n, k))
+
+
+def device_status() -> int:
+    """Synchronise and return the sticky device status word (0 = no bounded wait gave up)."""
+    word = ctypes.c_uint32(0)
+    error = abi.TensorErrorV1()
+    status = lib().tb200_gguf_device_status(ctypes.byref(word), ctypes.byref(error))
+    raise_for_status(status, error)
+    return int(word.value)
+
+
+def dequantize(w: torch.Tensor, encoding, n: int, k: int, out: torch.Tensor | None = None,
+               stream=None) -> torch.Tensor:
+    """fp32 ``[n, k]`` decode of raw GGUF bytes; bit-identical to the reference's ``decode_ggml``
+    (benchmarks/kernels/showcase/triton_kernels.py:133-181)."""
+    fmt = get_format(encoding)
+    _require_cuda("w", w)
+    if w.dtype != torch.uint8:
+        raise ValueError(f"w must be uint8 raw blocks, got {w.dtype}")
+    if w.numel() != fmt.weight_bytes(n, k):
+        raise ValueError(f"w holds {w.numel()} bytes; [{n}, {k}] in {fmt.name} needs {fmt.weight_bytes(n, k)}")
+    if out is None:
+        out = torch.empty((n, k), dtype=torch.float32, device=w.device)
+    _require_cuda("out", out)
+    device = _same_device(w, out)
+    args = [_buffer("w", w, (w.numel(),)), _buffer("out", out, (n, k)),
+            abi.scalar_argument(n), abi.scalar_argument(k), abi.scalar_argument(fmt.type_id)]
+    _invoke(lib().tb200_gguf_dequant_v1, args, device, stream)
+    return out
+
+
+def _matmul_args(x, w, out, fmt, m, n, k):
+    _require_cuda("x", x)
+    _require_cuda("w", w)
+    _require_cuda("out", out)
+    if w.dtype != torch.uint8:
+        raise ValueError(f"w must be uint8 raw blocks, got {w.dtype}")
+    if x.numel() != m * k:
+        raise ValueError(f"x holds {x.numel()} elements; [{m}, {k}] needs {m * k}")
+    if w.numel() != fmt.weight_bytes(n, k):
+        raise ValueError(f"w holds {w.numel()} bytes; [{n}, {k}] in {fmt.name} needs {fmt.weight_bytes(n, k)}")
+    if out.dtype != torch.float32 or out.numel() != m * n:
+        raise ValueError(f"out must be float32 with {m * n} elements")
+    return [_buffer("x", x, (m, k)), _buffer("w", w, (w.numel(),)), _buffer("out", out, (m, n))]
+
+
+def _infer_m(x: torch.Tensor, k: int) -> int:
+    if k <= 0 or x.numel() % k:
+        raise ValueError(f"x with {x.numel()} elements is not a whole number of rows of K={k}")
+    return x.numel() // k
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out: torch.Tensor | None = None,
+         scratch: torch.Tensor | None = None, variant="auto", stream=None) -> torch.Tensor:
+    """Decode GEMV ``out[m, n] = x[m, k] . dequant(w)^T`` (fp32 weights, fp32 accumulate).
+
+    ``scratch`` (uint8, zero-initialised once, reused across calls on one stream) lets the kernel
+    split K across CTAs for short-and-wide weights; without it a non-splitting kernel is used.
+    """
+    fmt = get_format(encoding)
+    m = _infer_m(x, k)
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    args = _matmul_args(x, w, out, fmt, m, n, k)
+    device = _same_device(x, w, out, scratch)
+    if scratch is not None:
+        _require_cuda("scratch", scratch)
+        if scratch.dtype != torch.uint8:
+            raise ValueError("scratch must be uint8")
+        args.append(_buffer("scratch", scratch, (scratch.numel(),)))
+    args += [abi.scalar_argument(m), abi.scalar_argument(n), abi.scalar_argument(k),
+             abi.scalar_argument(fmt.type_id), abi.scalar_argument(_VARIANTS[variant])]
+    _invoke(lib().tb200_gguf_gemv_v1, args, device, stream)
+    return out
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out: torch.Tensor | None = None,
+         variant="auto", stream=None) -> torch.Tensor:
+    """Prefill GEMM ``out[m, n] = x[m, k] . dequant(w)^T`` with bf16 operands, fp32 accumulate."""
+    fmt = get_format(encoding)
+    m = _infer_m(x, k)
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"the GEMM takes bfloat16 activations, got {x.dtype}")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    args = _matmul_args(x, w, out, fmt, m, n, k)
+    device = _same_device(x, w, out)
+    args += [abi.scalar_argument(m), abi.scalar_argument(n), abi.scalar_argument(k),
+             abi.scalar_argument(fmt.type_id), abi.scalar_argument(_VARIANTS[variant])]
+    _invoke(lib().tb200_gguf_gemm_v1, args, device, stream)
+    return out
