@@ -319,7 +319,8 @@ bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const D
   if (m < 1 || n < 1 || k < 256 || k % 256) return false;
   if (m > (1 << 24) || n > (1 << 24) || k > (1 << 24)) return false;
   if ((n + kTileN - 1) / kTileN > 65535) return false;
-  if (row_bytes(fmt, k) % 16) return false;  // 16-byte vector loads (Q4_K) / 4-byte pairs (Q6_K)
+  // Q4_K rows are always multiples of 16 bytes (16-byte vector loads); Q6_K rows are only
+  // 2-byte aligned in general and are read with 4-byte loads realigned in registers.
   return dev.max_smem_optin >= kSmemBytes;
 }
 

@@ -22,6 +22,8 @@
 //  * the K range of a CTA is fixed for its lifetime (x is staged once); row tiles are strided
 //    over CTAs; if K is split across CTAs, partial sums go to caller-provided scratch and the
 //    last CTA to arrive for a row tile adds them in a fixed order (deterministic).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -54,48 +56,98 @@ struct GemvArgs {
   int stages;
   int stride_s;   // shared-memory bytes between the rows of a stage
   int xs_stride;  // shared-memory bytes between staged activation rows
-  int off_stage, off_xs, off_sx, off_red, off_scl;
+  int off_stage, off_xs, off_sx, off_red, off_scl, off_zero;
+  int debug;  // TEMP experiment switch
+  int contiguous;  // one bulk copy per tile (K not split): stage rows are packed like global rows
 };
 
-template <bool F16> struct Magic {
-  static constexpr uint32_t kOr = F16 ? 0x64006400u : 0x43004300u;
-  static constexpr float kOffset = F16 ? 1024.f : 128.f;
-};
+// All MMAs run in fp16: q | 0x6400 is the fp16 number 1024 + q for q < 1024, and a nibble that
+// sits in bits 4..7 gives 1024 + 16 q without a shift (the factor 16 is folded into the scale).
+constexpr uint32_t kOr = 0x64006400u;
+constexpr float kOffset = 1024.f;
 
 // byte j of v as an exact float: 0x4B0000vv is 2^23 + vv.
 __device__ __forceinline__ float byte_to_float(uint32_t v, int j) {
   return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540u | (uint32_t)j)) - 8388608.f;
 }
 
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// 8 activations (16 bytes) -> 4 fp16x2 words, multiplied by `scale` (a power of two) when the
+// source is bf16; fp16 sources pass through.
 template <bool F16>
-__device__ __forceinline__ float sum8(uint4 v) {
+__device__ __forceinline__ uint4 to_f16x8(uint4 v, float scale) {
+  if constexpr (F16) {
+    return v;
+  } else {
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[i] = pack_f16(__uint_as_float(w[i] << 16) * scale, __uint_as_float(w[i] & 0xFFFF0000u) * scale);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+__device__ __forceinline__ float sum_f16x8(uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   float s = 0.f;
-  const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    if constexpr (F16) {
-      float2 f = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
-      s += f.x;
-      s += f.y;
-    } else {
-      s += __uint_as_float(words[i] << 16);
-      s += __uint_as_float(words[i] & 0xFFFF0000u);
-    }
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    s += f.x;
+    s += f.y;
   }
   return s;
 }
 
-// Stage the activations of this CTA's K range: rows b < NTB (zero beyond m), each aligned group
-// of four values stored as [x0, x2, x1, x3] so that an MMA B fragment is one contiguous load.
-// Also the per-32-group sums Sx[g][b] in fp32.
-template <bool F16, int NTB>
-__device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
-                                                  int klen) {
+// Stage the activations of this CTA's K range as fp16: rows b < NTB (zero beyond m), each aligned
+// group of four values stored as [x0, x2, x1, x3] so that an MMA B fragment is one contiguous
+// load, plus the per-32-group sums Sx[g][b] of the staged values in fp32.  bf16 inputs are scaled
+// by one power of two per CTA so that the largest magnitude lands in [2^14, 2^15): the conversion
+// is then exact for every value within 2^-32 of the largest, and the result is scaled back at the
+// end.  Returns the factor that undoes the scaling.
+template <bool F16, int NTB, typename Sync>
+__device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
+                                                   int klen, Sync&& consumer_sync, bool& ok) {
   const int chunks = klen >> 3;  // 8 values (16 bytes) each; a multiple of 32
   const int total = NTB * chunks;
   uint8_t* xs = smem + a.off_xs;
   float* sx = reinterpret_cast<float*>(smem + a.off_sx);
+  uint32_t* wmax = reinterpret_cast<uint32_t*>(smem + a.off_red);  // reused before the main loop
   const uint16_t* xg = static_cast<const uint16_t*>(a.x);
+  float scale = 1.f, unscale = 1.f;
+  if constexpr (!F16) {
+    uint32_t mx = 0;
+    for (int idx = ctid; idx < total; idx += kConsumerThreads) {
+      const int b = idx / chunks, c = idx - b * chunks;
+      if (b < a.m) {
+        const uint4 v = *reinterpret_cast<const uint4*>(xg + (long long)b * a.k + k0 + (c << 3));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((ctid & 31) == 0) wmax[ctid >> 5] = mx;
+    ok = consumer_sync();
+    if (!ok) return 1.f;
+#pragma unroll
+    for (int i = 0; i < kConsumerWarps; ++i) mx = max(mx, wmax[i]);
+    const int e = (int)(mx >> 7);  // biased bf16 exponent of the largest magnitude
+    if (e > 0 && e < 255) {
+      int sh = 141 - e;  // largest -> [2^14, 2^15)
+      sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+      scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+      unscale = __uint_as_float((uint32_t)(127 - sh) << 23);
+    }
+    ok = consumer_sync();  // wmax is free again
+    if (!ok) return 1.f;
+  }
   for (int base = 0; base < total; base += kConsumerThreads) {
     const int idx = base + ctid;
     const bool valid = idx < total;
@@ -103,8 +155,8 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* sm
     const int c = valid ? idx - b * chunks : 0;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (valid && b < a.m)
-      v = *reinterpret_cast<const uint4*>(xg + (long long)b * a.k + k0 + (c << 3));
-    float s = sum8<F16>(v);
+      v = to_f16x8<F16>(*reinterpret_cast<const uint4*>(xg + (long long)b * a.k + k0 + (c << 3)), scale);
+    float s = sum_f16x8(v);
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     if (valid) {
@@ -117,60 +169,105 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* sm
       if ((c & 3) == 0) sx[(c >> 2) * NTB + b] = s;
     }
   }
+  return unscale;
 }
 
+// (a & mask) | bits in ONE logic op.  The constants are handed over in registers: with two
+// immediates the compiler splits the expression into two LOP3s, and logic ops (half-rate ALU pipe)
+// are what bounds this kernel.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t bits) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(bits));
+  return d;
+}
+struct NibbleConsts {
+  uint32_t lo, hi, bits;  // 0x000F000F, 0x00F000F0, 0x64006400, kept in registers
+};
+__device__ __forceinline__ NibbleConsts nibble_consts() {
+  NibbleConsts c;
+  asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(c.lo));
+  asm volatile("mov.b32 %0, 0x00F000F0;" : "=r"(c.hi));
+  asm volatile("mov.b32 %0, 0x64006400;" : "=r"(c.bits));
+  return c;
+}
+
+// One 32-bit word of Q4_K quants (4 bytes = 4 low + 4 high nibbles) -> four fp16x2 registers:
+// lo02 / lo13 hold 1024 + low nibble of bytes (0,2) / (1,3); hi02 / hi13 hold 1024 + 16 * high
+// nibble.  Five logic ops for eight weights.
+struct Nibbles {
+  uint32_t lo02, hi02, lo13, hi13;
+};
+__device__ __forceinline__ Nibbles split_nibbles(uint32_t w, const NibbleConsts& k) {
+  Nibbles r;
+  const uint32_t w8 = w >> 8;
+  r.lo02 = and_or(w, k.lo, k.bits);
+  r.hi02 = and_or(w, k.hi, k.bits);
+  r.lo13 = and_or(w8, k.lo, k.bits);
+  r.hi13 = and_or(w8, k.hi, k.bits);
+  return r;
+}
+
+// Shared-memory addresses (32-bit, shared window) a consumer warp needs; computed once per CTA.
+struct SmemMap {
+  uint32_t xs, sx, scl;  // staged activations, group sums, this warp's scale scratch
+  int stride_s, xs_stride;
+  NibbleConsts nc;
+};
+
 // ---- Q4_K, batch on the MMA columns (1 < m <= 16) ------------------------------------------------
-template <bool F16, int NT>
-__device__ __forceinline__ void q4k_item_batch(const GemvArgs& a, const uint8_t* stage, const uint8_t* smem,
-                                               float* scl, int sbl, int lane, float (&acc)[NT][4]) {
+template <int NT>
+__device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage, int sbl, int lane,
+                                               float (&acc)[NT][4]) {
   constexpr int NTB = NT * 8;
-  constexpr uint32_t kOr = Magic<F16>::kOr;
   const int gid = lane >> 2, tig = lane & 3;
-  const uint8_t* xs = smem + a.off_xs;
-  const float* sx = reinterpret_cast<const float*>(smem + a.off_sx);
   __syncwarp();
   {  // scale preparation: lane -> (row, half of the groups)
     const int r = lane >> 1, hf = lane & 1;
-    const uint4 hdr = *reinterpret_cast<const uint4*>(stage + r * a.stride_s + sbl * 144);
+    const uint4 hdr = ptx::lds128(stage + r * sm.stride_s + sbl * 144);
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
     const uint32_t mnv =
         hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
-    float2* dst = reinterpret_cast<float2*>(scl + r * kSclRowFloats + hf * 8);
+    const uint32_t dst = sm.scl + (r * kSclRowFloats + hf * 8) * 4;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float dsc = d * byte_to_float(scv, j);
-      const float e = fmaf(Magic<F16>::kOffset, dsc, dmin * byte_to_float(mnv, j));
-      dst[j] = make_float2(dsc, e);
+      // odd groups are the high nibbles, which enter the MMA as 16 * q
+      const float dsc = d * byte_to_float(scv, j) * ((j & 1) ? 0.0625f : 1.f);
+      const float e = fmaf(kOffset, dsc, dmin * byte_to_float(mnv, j));
+      ptx::sts64f(dst + 8 * j, dsc, e);
     }
   }
   __syncwarp();
-  const uint8_t* rowA = stage + gid * a.stride_s + sbl * 144 + 16 + tig * 8;
-  const uint8_t* rowB = rowA + 8 * a.stride_s;
+  const uint32_t rowA = stage + gid * sm.stride_s + sbl * 144 + 16 + tig * 8;
+  const uint32_t rowB = rowA + 8 * sm.stride_s;
+  const uint32_t sclA = sm.scl + gid * (kSclRowFloats * 4), sclB = sclA + 8 * (kSclRowFloats * 4);
+  const uint32_t xrow = sm.xs + gid * sm.xs_stride + ((sbl * 256 + 8 * tig) << 1);
+  const uint32_t sxp = sm.sx + ((sbl * 8) * NTB + 2 * tig) * 4;
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    const uint2 wa = *reinterpret_cast<const uint2*>(rowA + p * 32);
-    const uint2 wb = *reinterpret_cast<const uint2*>(rowB + p * 32);
+    const uint2 wa = ptx::lds64(rowA + p * 32);
+    const uint2 wb = ptx::lds64(rowB + p * 32);
+    const Nibbles ax = split_nibbles(wa.x, sm.nc), ay = split_nibbles(wa.y, sm.nc);
+    const Nibbles bx = split_nibbles(wb.x, sm.nc), by = split_nibbles(wb.y, sm.nc);
 #pragma unroll
     for (int nib = 0; nib < 2; ++nib) {
       const int g = 2 * p + nib;
-      const int sh = 4 * nib;
-      const uint32_t a0 = ((wa.x >> sh) & 0x000F000Fu) | kOr, a1 = ((wb.x >> sh) & 0x000F000Fu) | kOr;
-      const uint32_t a2 = ((wa.x >> (sh + 8)) & 0x000F000Fu) | kOr, a3 = ((wb.x >> (sh + 8)) & 0x000F000Fu) | kOr;
-      const uint32_t a4 = ((wa.y >> sh) & 0x000F000Fu) | kOr, a5 = ((wb.y >> sh) & 0x000F000Fu) | kOr;
-      const uint32_t a6 = ((wa.y >> (sh + 8)) & 0x000F000Fu) | kOr, a7 = ((wb.y >> (sh + 8)) & 0x000F000Fu) | kOr;
-      const float2 sA = *reinterpret_cast<const float2*>(scl + gid * kSclRowFloats + g * 2);
-      const float2 sB = *reinterpret_cast<const float2*>(scl + (gid + 8) * kSclRowFloats + g * 2);
+      const float2 sA = ptx::lds64f(sclA + g * 8);
+      const float2 sB = ptx::lds64f(sclB + g * 8);
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint4 xb = *reinterpret_cast<const uint4*>(xs + (size_t)(gid + 8 * t) * a.xs_stride +
-                                                         ((sbl * 256 + 32 * g + 8 * tig) << 1));
+        const uint4 xb = ptx::lds128(xrow + 8 * t * sm.xs_stride + g * 64);
         float c[4];
-        ptx::mma16816<F16>(c, a0, a1, a2, a3, xb.x, xb.y, zero);
-        ptx::mma16816<F16>(c, a4, a5, a6, a7, xb.z, xb.w, c);
-        const float2 sxv = *reinterpret_cast<const float2*>(sx + (sbl * 8 + g) * NTB + 8 * t + 2 * tig);
+        if (nib == 0) {
+          ptx::mma16816<true>(c, ax.lo02, bx.lo02, ax.lo13, bx.lo13, xb.x, xb.y, zero);
+          ptx::mma16816<true>(c, ay.lo02, by.lo02, ay.lo13, by.lo13, xb.z, xb.w, c);
+        } else {
+          ptx::mma16816<true>(c, ax.hi02, bx.hi02, ax.hi13, bx.hi13, xb.x, xb.y, zero);
+          ptx::mma16816<true>(c, ay.hi02, by.hi02, ay.hi13, by.hi13, xb.z, xb.w, c);
+        }
+        const float2 sxv = ptx::lds64f(sxp + (g * NTB + 8 * t) * 4);
         acc[t][0] = fmaf(sA.x, c[0], acc[t][0]);
         acc[t][1] = fmaf(sA.x, c[1], acc[t][1]);
         acc[t][2] = fmaf(sB.x, c[2], acc[t][2]);
@@ -188,59 +285,60 @@ __device__ __forceinline__ void q4k_item_batch(const GemvArgs& a, const uint8_t*
 // Lane (gid, tig) holds the weights of rows gid and gid+8 that sit in 16-byte chunks tig and tig+4
 // of the 128 quant bytes; chunk c belongs to group pair c/2, so in one MMA different lanes may feed
 // different groups.  Column j of the MMA collects group j: the B fragment of lane (gid, tig) is its
-// slice of x when the lane's weights are in group gid, else zero.
-template <bool F16>
-__device__ __forceinline__ void q4k_item_groups(const GemvArgs& a, const uint8_t* stage, const uint8_t* smem,
-                                                int sbl, int lane, const uint32_t (&mask)[2][2],
-                                                float& accA, float& accB) {
-  constexpr uint32_t kOr = Magic<F16>::kOr;
+// slice of x when the lane's weights are in group gid, else zero.  For a lane that is true for one
+// of the four (chunk, nibble) combinations at most, so the four B fragments are loaded through
+// per-combination addresses that point at x for that one and at a block of zeros otherwise (loads
+// are cheap here; logic ops are the scarce resource).
+struct GroupLane {
+  uint32_t xbase[4];  // combination = 2 * chunk_index + nibble
+  int xstep[4];       // bytes per super-block: 512 for the live combination, 0 otherwise
+};
+
+__device__ __forceinline__ void q4k_item_groups(const SmemMap& sm, uint32_t stage, int sbl, int lane,
+                                                const GroupLane& gl, float& accA, float& accB) {
   const int gid = lane >> 2, tig = lane & 3;
-  const uint8_t* xs = smem + a.off_xs;
-  const float* sx = reinterpret_cast<const float*>(smem + a.off_sx);
-  const uint8_t* blkA = stage + gid * a.stride_s + sbl * 144;
-  const uint8_t* blkB = blkA + 8 * a.stride_s;
-  // this lane's slice of x: group gid, 16 values starting at 16*(tig&1)
-  const uint8_t* xp = xs + ((sbl * 256 + 32 * gid + 16 * (tig & 1)) << 1);
-  const uint4 x0 = *reinterpret_cast<const uint4*>(xp);
-  const uint4 x1 = *reinterpret_cast<const uint4*>(xp + 16);
-  const uint32_t xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t blkA = stage + gid * sm.stride_s + sbl * 144;
+  const uint32_t blkB = blkA + 8 * sm.stride_s;
+  float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};  // two independent MMA chains
 #pragma unroll
   for (int ci = 0; ci < 2; ++ci) {
-    const uint4 qa = *reinterpret_cast<const uint4*>(blkA + 16 + 16 * (tig + 4 * ci));
-    const uint4 qb = *reinterpret_cast<const uint4*>(blkB + 16 + 16 * (tig + 4 * ci));
+    const uint4 qa = ptx::lds128(blkA + 16 + 16 * (tig + 4 * ci));
+    const uint4 qb = ptx::lds128(blkB + 16 + 16 * (tig + 4 * ci));
     const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
     const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
+    const uint32_t pl = gl.xbase[2 * ci] + sbl * gl.xstep[2 * ci];
+    const uint32_t ph = gl.xbase[2 * ci + 1] + sbl * gl.xstep[2 * ci + 1];
+    const uint4 l0 = ptx::lds128(pl), l1 = ptx::lds128(pl + 16);
+    const uint4 h0 = ptx::lds128(ph), h1 = ptx::lds128(ph + 16);
+    const uint32_t xlo[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const uint32_t xhi[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-#pragma unroll
-      for (int nib = 0; nib < 2; ++nib) {
-        const int sh = 4 * nib;
-        const uint32_t a0 = ((wa[i] >> sh) & 0x000F000Fu) | kOr, a1 = ((wb[i] >> sh) & 0x000F000Fu) | kOr;
-        const uint32_t a2 = ((wa[i] >> (sh + 8)) & 0x000F000Fu) | kOr;
-        const uint32_t a3 = ((wb[i] >> (sh + 8)) & 0x000F000Fu) | kOr;
-        ptx::mma16816<F16>(c, a0, a1, a2, a3, xr[2 * i] & mask[ci][nib], xr[2 * i + 1] & mask[ci][nib], c);
-      }
+      const Nibbles na = split_nibbles(wa[i], sm.nc), nb = split_nibbles(wb[i], sm.nc);
+      ptx::mma16816<true>(c0, na.lo02, nb.lo02, na.lo13, nb.lo13, xlo[2 * i], xlo[2 * i + 1], c0);
+      ptx::mma16816<true>(c1, na.hi02, nb.hi02, na.hi13, nb.hi13, xhi[2 * i], xhi[2 * i + 1], c1);
     }
   }
-  // c[0], c[1]: row gid, groups 2*tig, 2*tig+1; c[2], c[3]: row gid+8, same groups.
-  const float2 sxv = *reinterpret_cast<const float2*>(sx + sbl * 8 + 2 * tig);
+  // c0 collects the even groups (columns 0, 2, 4, 6), c1 the odd ones.  c[0], c[1]: row gid,
+  // groups 2*tig, 2*tig+1; c[2], c[3]: row gid+8.
+  const float2 sxv = ptx::lds64f(sm.sx + (sbl * 8 + 2 * tig) * 4);
   const int sel = (tig & 1) * 16;
   const bool upper = tig >= 2;
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
-    const uint4 hdr = *reinterpret_cast<const uint4*>(rr ? blkB : blkA);
+    const uint4 hdr = ptx::lds128(rr ? blkB : blkA);
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     const uint32_t h0 = hdr.y >> sel, h1 = hdr.z >> sel, h2 = hdr.w >> sel;
     const uint32_t scp = upper ? ((h2 & 0x0F0Fu) | ((h0 >> 2) & 0x3030u)) : (h0 & 0x3F3Fu);
     const uint32_t mnp = upper ? (((h2 >> 4) & 0x0F0Fu) | ((h1 >> 2) & 0x3030u)) : (h1 & 0x3F3Fu);
-    const float dsc0 = d * byte_to_float(scp, 0), dsc1 = d * byte_to_float(scp, 1);
-    const float e0 = fmaf(Magic<F16>::kOffset, dsc0, dmin * byte_to_float(mnp, 0));
-    const float e1 = fmaf(Magic<F16>::kOffset, dsc1, dmin * byte_to_float(mnp, 1));
+    const float dsc0 = d * byte_to_float(scp, 0);             // even group: low nibbles
+    const float dsc1 = d * byte_to_float(scp, 1) * 0.0625f;   // odd group: 16 * high nibble
+    const float e0 = fmaf(kOffset, dsc0, dmin * byte_to_float(mnp, 0));
+    const float e1 = fmaf(kOffset, dsc1, dmin * byte_to_float(mnp, 1));
     float v = rr ? accB : accA;
-    v = fmaf(dsc0, c[2 * rr], v);
-    v = fmaf(dsc1, c[2 * rr + 1], v);
+    v = fmaf(dsc0, c0[2 * rr], v);      // even column: fed by the low-nibble MMAs only
+    v = fmaf(dsc1, c1[2 * rr + 1], v);  // odd column: fed by the high-nibble MMAs only
     v = fmaf(-e0, sxv.x, v);
     v = fmaf(-e1, sxv.y, v);
     if (rr) accB = v; else accA = v;
@@ -248,7 +346,7 @@ __device__ __forceinline__ void q4k_item_groups(const GemvArgs& a, const uint8_t
 }
 
 template <int FMT, bool F16, int NT, bool GROUPS>
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a) {
   static_assert(FMT == kQ4_K, "only Q4_K is pipelined so far");
   constexpr int NTB = GROUPS ? 1 : NT * 8;
   constexpr int kBlockBytes = Fmt<FMT>::kBytes;
@@ -274,11 +372,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a)
     ptx::mbar_init(cbar, kConsumerWarps);
     ptx::fence_mbar_init();
   }
+  if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(smem + a.off_zero)[threadIdx.x] = 0u;
   __syncthreads();
 
   if (warp == kConsumerWarps) {
     // ---------------- producer: one bulk copy per weight row of the tile ----------------
     const uint8_t* src0 = a.w + (long long)sb0 * kBlockBytes;
+    if (a.debug & 2) return;
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int s = i % S;
@@ -288,11 +388,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a)
       }
       const long long row0 = (long long)rt * kTileRows;
       const int rows = (int)min((long long)kTileRows, a.n - row0);
-      if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
-      __syncwarp();
-      if (lane < rows)
-        ptx::bulk_g2s(smem + a.off_stage + (size_t)s * kTileRows * a.stride_s + (size_t)lane * a.stride_s,
-                      src0 + (row0 + lane) * a.row_bytes, range_bytes, &full[s]);
+      uint8_t* dst = smem + a.off_stage + (size_t)s * kTileRows * a.stride_s;
+      if (a.contiguous) {
+        // the K range is the whole row and rows are packed back to back: one copy per tile
+        if (lane == 0) {
+          ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
+          ptx::bulk_g2s(dst, src0 + row0 * a.row_bytes, (uint32_t)rows * range_bytes, &full[s]);
+        }
+      } else {
+        if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
+        __syncwarp();
+        if (lane < rows)
+          ptx::bulk_g2s(dst + (size_t)lane * a.stride_s, src0 + (row0 + lane) * a.row_bytes, range_bytes, &full[s]);
+      }
     }
     return;
   }
@@ -310,35 +418,52 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a)
     if (!ok) report_timeout(0x30000u);
     return ok;
   };
-  stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256);
+  bool staged = true;
+  const float unscale =
+      stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, consumer_sync, staged);
+  if (!staged) return;
   if (!consumer_sync()) return;
 
   const int gid = lane >> 2, tig = lane & 3;
-  uint32_t mask[2][2] = {{0u, 0u}, {0u, 0u}};
+  const uint32_t smem_base = ptx::smem_addr(smem);
+  SmemMap sm;
+  sm.xs = smem_base + a.off_xs;
+  sm.sx = smem_base + a.off_sx;
+  sm.scl = smem_base + a.off_scl + cw * (kTileRows * kSclRowFloats * 4);
+  sm.stride_s = a.stride_s;
+  sm.xs_stride = a.xs_stride;
+  sm.nc = nibble_consts();
+  GroupLane gl;
   if constexpr (GROUPS) {
+    // this lane's slice of x: group gid, 16 values starting at 16 * (tig & 1)
+    const uint32_t mine = sm.xs + ((32 * gid + 16 * (tig & 1)) << 1);
+    const uint32_t zeros = smem_base + a.off_zero;
 #pragma unroll
     for (int ci = 0; ci < 2; ++ci)
 #pragma unroll
-      for (int nib = 0; nib < 2; ++nib)
-        mask[ci][nib] = (gid == 2 * (tig >> 1) + 4 * ci + nib) ? 0xFFFFFFFFu : 0u;
+      for (int nib = 0; nib < 2; ++nib) {
+        const bool live = gid == 2 * (tig >> 1) + 4 * ci + nib;
+        gl.xbase[2 * ci + nib] = live ? mine : zeros;
+        gl.xstep[2 * ci + nib] = live ? 512 : 0;
+      }
   }
   float* red = reinterpret_cast<float*>(smem + a.off_red);
-  float* scl = reinterpret_cast<float*>(smem + a.off_scl) + cw * (kTileRows * kSclRowFloats);
   constexpr int kRedPerBuf = kConsumerWarps * NTB * kTileRows;
 
   int i = 0;
   for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
     const int s = i % S;
-    if (!ptx::mbar_wait(&full[s], (i / S) & 1)) {
+    if (!(a.debug & 2) && !ptx::mbar_wait(&full[s], (i / S) & 1)) {
       report_timeout(0x20000u | (unsigned)s);
       return;
     }
-    const uint8_t* stage = smem + a.off_stage + (size_t)s * kTileRows * a.stride_s;
+    const uint32_t stage = smem_base + a.off_stage + s * kTileRows * a.stride_s;
     float* redbuf = red + (i & 1) * kRedPerBuf;
     if constexpr (GROUPS) {
       float accA = 0.f, accB = 0.f;
+      if (!(a.debug & 1))
       for (int sbl = cw; sbl < nsb_local; sbl += kConsumerWarps)
-        q4k_item_groups<F16>(a, stage, smem, sbl, lane, mask, accA, accB);
+        q4k_item_groups(sm, stage, sbl, lane, gl, accA, accB);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
       accA += __shfl_xor_sync(0xffffffffu, accA, 1);
@@ -356,7 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
       for (int sbl = cw; sbl < nsb_local; sbl += kConsumerWarps)
-        q4k_item_batch<F16, NT>(a, stage, smem, scl, sbl, lane, acc);
+        q4k_item_batch<NT>(sm, stage, sbl, lane, acc);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
 #pragma unroll
@@ -378,6 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a)
 #pragma unroll
       for (int w8 = 0; w8 < kConsumerWarps; ++w8) v += redbuf[(w8 * NTB + col) * kTileRows + row];
     }
+    v *= unscale;
     if (a.k_splits == 1) {
       if (mine) a.out[(long long)col * a.n + grow] = v;
     } else {
@@ -414,14 +540,15 @@ inline int pad_stride(int bytes, int want) {
 }
 
 struct Layout {
-  int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, total;
+  int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, off_zero, total;
 };
 
-Layout make_layout(int fmt, int m, int sb_per_split, int stages) {
+Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool contiguous) {
   const bool groups = m == 1;
   const int ntb = groups ? 1 : (m <= 8 ? 8 : 16);
   Layout L;
-  L.stride_s = pad_stride(sb_per_split * block_bytes(fmt), groups ? 64 : 32);
+  L.stride_s = contiguous ? sb_per_split * block_bytes(fmt)
+                          : pad_stride(sb_per_split * block_bytes(fmt), groups ? 64 : 32);
   L.xs_stride = pad_stride(sb_per_split * 512, 64);
   L.stage_bytes = kTileRows * L.stride_s;
   int off = 256;  // mbarriers: full[8], empty[8], consumer barrier
@@ -435,6 +562,8 @@ Layout make_layout(int fmt, int m, int sb_per_split, int stages) {
   off += 2 * kConsumerWarps * ntb * kTileRows * 4;
   L.off_scl = off;
   off += groups ? 0 : kConsumerWarps * kTileRows * kSclRowFloats * 4;
+  L.off_zero = off;  // 64 zero bytes: the B fragment of lanes whose weights feed another column
+  off += 64;
   L.total = round_up(off, 128);
   return L;
 }
@@ -454,39 +583,43 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
   const int nsb = (int)(k / 256);
   const long long row_tiles = (n + kTileRows - 1) / kTileRows;
   if (row_tiles > 0x7fffffffLL) return best;
-  const int slots = dev.sm_count;  // one CTA per SM
   double best_cost = 1e300;
-  for (int splits = 1; splits <= nsb && splits <= 64; ++splits) {
-    const int per = (nsb + splits - 1) / splits;
-    if ((splits - 1) * per >= nsb) continue;  // an empty K range
-    const long long need =
-        splits > 1 ? ((row_tiles * 4 + 255) / 256 * 256 + (long long)splits * m * n * 4) : 0;
-    if (need > scratch_bytes_available) continue;
-    int stages = 0;
-    Layout L{};
-    for (int s = kMaxStages; s >= 2; --s) {
-      L = make_layout(fmt, (int)m, per, s);
-      if (L.total <= dev.max_smem_optin) { stages = s; break; }
-    }
-    if (!stages) continue;
-    // splitting K so finely that the ring holds little data cannot keep HBM busy
-    if (splits > 1 && (long long)stages * L.stage_bytes < 64 * 1024) continue;
-    int groups = (int)((long long)slots / splits < row_tiles ? slots / splits : row_tiles);
-    if (groups < 1) continue;
-    const long long tiles_per_cta = (row_tiles + groups - 1) / groups;
-    // time ~ bytes the slowest CTA streams, plus the partial-sum traffic of a split
-    double cost = (double)tiles_per_cta * per * block_bytes(fmt) * kTileRows;
-    if (splits > 1) cost += (double)tiles_per_cta * kTileRows * m * 4 * 2 + 2000.0 * tiles_per_cta;
-    if (cost < best_cost) {
-      best_cost = cost;
-      best.supported = true;
-      best.k_splits = splits;
-      best.row_groups = groups;
-      best.sb_per_split = per;
-      best.stages = stages;
-      best.stage_bytes = L.stage_bytes;
-      best.smem_bytes = L.total;
-      best.scratch_bytes = need;
+  // Two CTAs per SM hide each other's barriers and reductions when the shared memory allows it.
+  for (int per_sm = 2; per_sm >= 1; --per_sm) {
+    const int slots = dev.sm_count * per_sm;
+    const int smem_limit = per_sm == 1 ? dev.max_smem_optin : (dev.max_smem_optin + 1024) / 2 - 1024;
+    for (int splits = 1; splits <= nsb && splits <= 64; ++splits) {
+      const int per = (nsb + splits - 1) / splits;
+      if ((splits - 1) * per >= nsb) continue;  // an empty K range
+      const long long need =
+          splits > 1 ? ((row_tiles * 4 + 255) / 256 * 256 + (long long)splits * m * n * 4) : 0;
+      if (need > scratch_bytes_available) continue;
+      int stages = 0;
+      Layout L{};
+      for (int s = kMaxStages; s >= 2; --s) {
+        L = make_layout(fmt, (int)m, per, s, splits == 1);
+        if (L.total <= smem_limit) { stages = s; break; }
+      }
+      if (!stages) continue;
+      // a ring that holds little data cannot keep HBM busy
+      if ((long long)stages * L.stage_bytes * per_sm < 96 * 1024 && stages < kMaxStages) continue;
+      int groups = (int)((long long)slots / splits < row_tiles ? slots / splits : row_tiles);
+      if (groups < 1) continue;
+      const long long tiles_per_cta = (row_tiles + groups - 1) / groups;
+      // time ~ bytes the busiest SM streams, plus the partial-sum traffic and sync of a split
+      double cost = (double)per_sm * tiles_per_cta * per * block_bytes(fmt) * kTileRows;
+      if (splits > 1) cost += per_sm * ((double)tiles_per_cta * kTileRows * m * 4 * 2 + 2000.0 * tiles_per_cta);
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.supported = true;
+        best.k_splits = splits;
+        best.row_groups = groups;
+        best.sb_per_split = per;
+        best.stages = stages;
+        best.stage_bytes = L.stage_bytes;
+        best.smem_bytes = L.total;
+        best.scratch_bytes = need;
+      }
     }
   }
   return best;
@@ -519,7 +652,9 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.row_groups = plan.row_groups;
   a.row_tiles = (int)((n + kTileRows - 1) / kTileRows);
   a.stages = plan.stages;
-  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages);
+  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages, plan.k_splits == 1);
+  a.contiguous = plan.k_splits == 1;
+  a.debug = getenv("TB200_GEMV_DEBUG") ? atoi(getenv("TB200_GEMV_DEBUG")) : 0;
   a.stride_s = L.stride_s;
   a.xs_stride = L.xs_stride;
   a.off_stage = L.off_stage;
@@ -527,6 +662,7 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.off_sx = L.off_sx;
   a.off_red = L.off_red;
   a.off_scl = L.off_scl;
+  a.off_zero = L.off_zero;
   if (plan.k_splits > 1) {
     if (!scratch) return cudaErrorInvalidValue;
     a.counters = static_cast<unsigned int*>(scratch);
