@@ -22,8 +22,6 @@
 //  * the K range of a CTA is fixed for its lifetime (x is staged once); row tiles are strided
 //    over CTAs; if K is split across CTAs, partial sums go to caller-provided scratch and the
 //    last CTA to arrive for a row tile adds them in a fixed order (deterministic).
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -31,9 +29,10 @@
 namespace tb200 {
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxConsumerWarps = 8;
+constexpr int kProducerWarp = kMaxConsumerWarps;     // streams weights into the ring
+constexpr int kReducerWarp = kMaxConsumerWarps + 1;  // adds the consumer warps' partial sums, writes out
+constexpr int kThreads = (kMaxConsumerWarps + 2) * 32;
 constexpr int kTileRows = 16;
 constexpr int kMaxStages = 8;
 constexpr int kSclRowFloats = 18;  // 8 x (scale, offset) pairs + 2 floats of padding (bank spread)
@@ -56,8 +55,8 @@ struct GemvArgs {
   int stages;
   int stride_s;   // shared-memory bytes between the rows of a stage
   int xs_stride;  // shared-memory bytes between staged activation rows
-  int off_stage, off_xs, off_sx, off_red, off_scl, off_zero;
-  int debug;  // TEMP experiment switch
+  int off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc;
+  int consumer_warps;  // warps that decode (<= 8), chosen to divide the super-blocks of a K range evenly
   int contiguous;  // one bulk copy per tile (K not split): stage rows are packed like global rows
 };
 
@@ -113,6 +112,7 @@ __device__ __forceinline__ float sum_f16x8(uint4 v) {
 template <bool F16, int NTB, typename Sync>
 __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
                                                    int klen, Sync&& consumer_sync, bool& ok) {
+  const int kConsumerThreads = a.consumer_warps * 32;
   const int chunks = klen >> 3;  // 8 values (16 bytes) each; a multiple of 32
   const int total = NTB * chunks;
   uint8_t* xs = smem + a.off_xs;
@@ -137,7 +137,7 @@ __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* s
     ok = consumer_sync();
     if (!ok) return 1.f;
 #pragma unroll
-    for (int i = 0; i < kConsumerWarps; ++i) mx = max(mx, wmax[i]);
+    for (int i = 0; i < a.consumer_warps; ++i) mx = max(mx, wmax[i]);
     const int e = (int)(mx >> 7);  // biased bf16 exponent of the largest magnitude
     if (e > 0 && e < 255) {
       int sh = 141 - e;  // largest -> [2^14, 2^15)
@@ -170,6 +170,54 @@ __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* s
     }
   }
   return unscale;
+}
+
+// m == 1 staging: one pass, no CTA-wide reduction.  Each 32-value scale group gets its own power of
+// two (its largest magnitude lands in [2^14, 2^15)), so bf16 -> fp16 is exact for every value within
+// 2^-32 of the group's largest; the factor that undoes it rides along with the group sum:
+// sxu[g] = {sum of the staged fp16 values of group g, unscale of group g}.
+template <bool F16>
+__device__ __forceinline__ void stage_activations_groups(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
+                                                         int klen) {
+  const int chunks = klen >> 3;  // 8 values each; four consecutive chunks (lanes) form a group
+  const int threads = a.consumer_warps * 32;
+  uint8_t* xs = smem + a.off_xs;
+  float2* sxu = reinterpret_cast<float2*>(smem + a.off_sx);
+  const uint16_t* xg = static_cast<const uint16_t*>(a.x);
+  for (int base = 0; base < chunks; base += threads) {
+    const int c = base + ctid;  // chunks is a multiple of 32: a warp is all-valid or all-invalid
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (c < chunks) v = *reinterpret_cast<const uint4*>(xg + k0 + (c << 3));
+    float scale = 1.f, unscale = 1.f;
+    if constexpr (!F16) {
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t mx = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const int e = (int)(mx >> 7);  // biased bf16 exponent of the group's largest magnitude
+      if (e > 0 && e < 255) {
+        int sh = 141 - e;
+        sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+        scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+        unscale = __uint_as_float((uint32_t)(127 - sh) << 23);
+      }
+    }
+    v = to_f16x8<F16>(v, scale);
+    float sum = sum_f16x8(v);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (c < chunks) {
+      uint4 p;
+      p.x = __byte_perm(v.x, v.y, 0x5410);
+      p.y = __byte_perm(v.x, v.y, 0x7632);
+      p.z = __byte_perm(v.z, v.w, 0x5410);
+      p.w = __byte_perm(v.z, v.w, 0x7632);
+      *reinterpret_cast<uint4*>(xs + (c << 4)) = p;
+      if ((c & 3) == 0) sxu[c >> 2] = make_float2(sum, unscale);
+    }
+  }
 }
 
 // (a & mask) | bits in ONE logic op.  The constants are handed over in registers: with two
@@ -292,18 +340,32 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
 struct GroupLane {
   uint32_t xbase[4];  // combination = 2 * chunk_index + nibble
   int xstep[4];       // bytes per super-block: 512 for the live combination, 0 otherwise
+  uint32_t row_off;   // gid * stride: this lane's first weight row inside a stage
+  uint32_t row8;      // 8 * stride: distance to its second row
+  uint32_t quant_off; // 16 + 16 * tig: first quant chunk of the lane inside a super-block
+  uint32_t sxu;       // shared address of {group sum, unscale} for group 2 * tig of super-block 0
+  // scale extraction, fixed per lane: groups 2*tig, 2*tig+1 sit in bytes 2*(tig&1), +1 of the
+  // packed words; lanes with tig >= 2 (groups 4..7) splice low 4 bits and high 2 bits
+  uint32_t m_lo, m_hi;      // 0x3F3F3F3F / 0 for groups 0..3, 0x0F0F0F0F / 0x30303030 for groups 4..7
+  uint32_t sel0, sel1;      // PRMT selectors that turn byte 2*(tig&1) (+1) into the float 2^23 + byte
+  bool upper;
 };
 
-__device__ __forceinline__ void q4k_item_groups(const SmemMap& sm, uint32_t stage, int sbl, int lane,
+__device__ __forceinline__ float prmt_float(uint32_t v, uint32_t selector) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, selector)) - 8388608.f;
+}
+
+__device__ __forceinline__ void q4k_item_groups(const SmemMap& sm, uint32_t stage, int sbl,
                                                 const GroupLane& gl, float& accA, float& accB) {
-  const int gid = lane >> 2, tig = lane & 3;
-  const uint32_t blkA = stage + gid * sm.stride_s + sbl * 144;
-  const uint32_t blkB = blkA + 8 * sm.stride_s;
+  const uint32_t blkA = stage + gl.row_off + sbl * 144;
+  const uint32_t blkB = blkA + gl.row8;
+  const uint4 hdrA = ptx::lds128(blkA), hdrB = ptx::lds128(blkB);
+  const uint4 su = ptx::lds128(gl.sxu + sbl * 64);  // {Sx, u} of groups 2*tig and 2*tig+1
   float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};  // two independent MMA chains
 #pragma unroll
   for (int ci = 0; ci < 2; ++ci) {
-    const uint4 qa = ptx::lds128(blkA + 16 + 16 * (tig + 4 * ci));
-    const uint4 qb = ptx::lds128(blkB + 16 + 16 * (tig + 4 * ci));
+    const uint4 qa = ptx::lds128(blkA + gl.quant_off + 64 * ci);
+    const uint4 qb = ptx::lds128(blkB + gl.quant_off + 64 * ci);
     const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
     const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
     const uint32_t pl = gl.xbase[2 * ci] + sbl * gl.xstep[2 * ci];
@@ -321,26 +383,26 @@ __device__ __forceinline__ void q4k_item_groups(const SmemMap& sm, uint32_t stag
   }
   // c0 collects the even groups (columns 0, 2, 4, 6), c1 the odd ones.  c[0], c[1]: row gid,
   // groups 2*tig, 2*tig+1; c[2], c[3]: row gid+8.
-  const float2 sxv = ptx::lds64f(sm.sx + (sbl * 8 + 2 * tig) * 4);
-  const int sel = (tig & 1) * 16;
-  const bool upper = tig >= 2;
+  const float sx0 = __uint_as_float(su.x), u0 = __uint_as_float(su.y);
+  const float sx1 = __uint_as_float(su.z), u1 = __uint_as_float(su.w);
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
-    const uint4 hdr = ptx::lds128(rr ? blkB : blkA);
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
-    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-    const uint32_t h0 = hdr.y >> sel, h1 = hdr.z >> sel, h2 = hdr.w >> sel;
-    const uint32_t scp = upper ? ((h2 & 0x0F0Fu) | ((h0 >> 2) & 0x3030u)) : (h0 & 0x3F3Fu);
-    const uint32_t mnp = upper ? (((h2 >> 4) & 0x0F0Fu) | ((h1 >> 2) & 0x3030u)) : (h1 & 0x3F3Fu);
-    const float dsc0 = d * byte_to_float(scp, 0);             // even group: low nibbles
-    const float dsc1 = d * byte_to_float(scp, 1) * 0.0625f;   // odd group: 16 * high nibble
-    const float e0 = fmaf(kOffset, dsc0, dmin * byte_to_float(mnp, 0));
-    const float e1 = fmaf(kOffset, dsc1, dmin * byte_to_float(mnp, 1));
+    const uint4 hdr = rr ? hdrB : hdrA;
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // d, dmin
+    // 6-bit scales / mins of the lane's two groups, all four packed bytes at once
+    const uint32_t sc_src = gl.upper ? hdr.w : hdr.y;
+    const uint32_t mn_src = gl.upper ? (hdr.w >> 4) : hdr.z;
+    const uint32_t scv = and_or(sc_src, gl.m_lo, (hdr.y >> 2) & gl.m_hi);
+    const uint32_t mnv = and_or(mn_src, gl.m_lo, (hdr.z >> 2) & gl.m_hi);
+    const float dsc0 = dd.x * prmt_float(scv, gl.sel0);              // even group: low nibbles
+    const float dsc1 = dd.x * 0.0625f * prmt_float(scv, gl.sel1);    // odd group: 16 * high nibble
+    const float e0 = fmaf(kOffset, dsc0, dd.y * prmt_float(mnv, gl.sel0));
+    const float e1 = fmaf(kOffset, dsc1, dd.y * prmt_float(mnv, gl.sel1));
+    const float t0 = fmaf(dsc0, c0[2 * rr], -e0 * sx0);      // even column: low-nibble MMAs only
+    const float t1 = fmaf(dsc1, c1[2 * rr + 1], -e1 * sx1);  // odd column: high-nibble MMAs only
     float v = rr ? accB : accA;
-    v = fmaf(dsc0, c0[2 * rr], v);      // even column: fed by the low-nibble MMAs only
-    v = fmaf(dsc1, c1[2 * rr + 1], v);  // odd column: fed by the high-nibble MMAs only
-    v = fmaf(-e0, sxv.x, v);
-    v = fmaf(-e1, sxv.y, v);
+    v = fmaf(u0, t0, v);
+    v = fmaf(u1, t1, v);
     if (rr) accB = v; else accA = v;
   }
 }
@@ -353,32 +415,41 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + kMaxStages;
-  uint64_t* cbar = empty + kMaxStages;  // consumer-only barrier (bounded, unlike bar.sync)
-  __shared__ int s_last;
+  uint64_t* cbar = empty + kMaxStages;  // consumer-only barrier for the staging phase (bounded)
+  uint64_t* red_full = cbar + 1;        // [2] consumers -> reducer: partial sums of a tile are in place
+  uint64_t* red_empty = red_full + 2;   // [2] reducer -> consumers: buffer may be overwritten
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int W = a.consumer_warps;
   const int ks = blockIdx.x % a.k_splits;
   const int rg = blockIdx.x / a.k_splits;
   const int sb0 = ks * a.sb_per_split;
   const int nsb_local = min(a.sb_per_split, a.nsb - sb0);
   const uint32_t range_bytes = (uint32_t)nsb_local * kBlockBytes;
   const int S = a.stages;
+  float* red = reinterpret_cast<float*>(smem + a.off_red);
+  constexpr int kRedPerWarp = NTB * kTileRows;
+  const int red_per_buf = W * kRedPerWarp;
+  volatile float* unscale_slot = reinterpret_cast<volatile float*>(smem + a.off_misc);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(&full[s], 1);
-      ptx::mbar_init(&empty[s], kConsumerWarps);
+      ptx::mbar_init(&empty[s], W);
     }
-    ptx::mbar_init(cbar, kConsumerWarps);
+    ptx::mbar_init(cbar, W);
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&red_full[b], W);
+      ptx::mbar_init(&red_empty[b], 1);
+    }
     ptx::fence_mbar_init();
   }
   if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(smem + a.off_zero)[threadIdx.x] = 0u;
   __syncthreads();
 
-  if (warp == kConsumerWarps) {
-    // ---------------- producer: one bulk copy per weight row of the tile ----------------
+  if (warp == kProducerWarp) {
+    // ---------------- producer: bulk copies of the tile's weight rows ----------------
     const uint8_t* src0 = a.w + (long long)sb0 * kBlockBytes;
-    if (a.debug & 2) return;
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int s = i % S;
@@ -405,8 +476,71 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
     return;
   }
 
+  if (warp == kReducerWarp) {
+    // ---------------- reducer: sum the consumer warps' partials in warp order, write out ----------------
+    int i = 0;
+    for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
+      const int b = i & 1;
+      if (!ptx::mbar_wait(&red_full[b], (i >> 1) & 1)) {
+        report_timeout(0x40000u | (unsigned)b);
+        return;
+      }
+      const float unscale = *unscale_slot;
+      const float* buf = red + b * red_per_buf;
+      float vals[kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1];
+      bool mine[kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1];
+      long long gidx[kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1];
+      constexpr int kPerLane = kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1;
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        const int e = lane + 32 * j;  // (column e / 16, row e % 16)
+        const int row = e & 15, col = e >> 4;
+        const long long grow = (long long)rt * kTileRows + row;
+        mine[j] = e < kRedPerWarp && col < a.m && grow < a.n;
+        gidx[j] = (long long)col * a.n + grow;
+        float v = 0.f;
+        if (e < kRedPerWarp)
+          for (int w8 = 0; w8 < W; ++w8) v += buf[w8 * kRedPerWarp + e];
+        vals[j] = v * unscale;
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&red_empty[b]);  // partials are in registers now
+      if (a.k_splits == 1) {
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j)
+          if (mine[j]) a.out[gidx[j]] = vals[j];
+      } else {
+        const long long plane = (long long)a.m * a.n;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j)
+          if (mine[j]) a.partials[ks * plane + gidx[j]] = vals[j];
+        __threadfence();
+        __syncwarp();
+        unsigned int last = 0;
+        if (lane == 0) {
+          const unsigned int old = atomicAdd(&a.counters[rt], 1u);
+          last = old == (unsigned)(a.k_splits - 1);
+          if (last) a.counters[rt] = 0u;  // every other K range has already arrived
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+#pragma unroll
+          for (int j = 0; j < kPerLane; ++j)
+            if (mine[j]) {
+              float total = 0.f;
+              for (int q = 0; q < a.k_splits; ++q) total += __ldcg(&a.partials[q * plane + gidx[j]]);
+              a.out[gidx[j]] = total;
+            }
+        }
+      }
+    }
+    return;
+  }
+
   // ---------------- consumers ----------------
   const int cw = warp;
+  if (cw >= W) return;
   const int ctid = threadIdx.x;
   uint32_t cphase = 0;
   // All consumer warps meet here; returns false if the (bounded) wait gave up.
@@ -418,10 +552,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
     if (!ok) report_timeout(0x30000u);
     return ok;
   };
-  bool staged = true;
-  const float unscale =
-      stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, consumer_sync, staged);
-  if (!staged) return;
+  if constexpr (GROUPS) {
+    stage_activations_groups<F16>(a, smem, ctid, sb0 * 256, nsb_local * 256);
+    if (ctid == 0) *unscale_slot = 1.f;  // scaling is undone per group inside the item
+  } else {
+    bool staged = true;
+    const float unscale =
+        stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, consumer_sync, staged);
+    if (!staged) return;
+    if (ctid == 0) *unscale_slot = unscale;
+  }
   if (!consumer_sync()) return;
 
   const int gid = lane >> 2, tig = lane & 3;
@@ -446,33 +586,44 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
         gl.xbase[2 * ci + nib] = live ? mine : zeros;
         gl.xstep[2 * ci + nib] = live ? 512 : 0;
       }
+    gl.row_off = gid * a.stride_s;
+    gl.row8 = 8 * a.stride_s;
+    gl.quant_off = 16 + 16 * tig;
+    gl.sxu = sm.sx + 2 * tig * 8;
+    gl.upper = tig >= 2;
+    gl.m_lo = gl.upper ? 0x0F0F0F0Fu : 0x3F3F3F3Fu;
+    gl.m_hi = gl.upper ? 0x30303030u : 0u;
+    gl.sel0 = 0x7540u | (uint32_t)(2 * (tig & 1));
+    gl.sel1 = gl.sel0 + 1;
   }
-  float* red = reinterpret_cast<float*>(smem + a.off_red);
-  constexpr int kRedPerBuf = kConsumerWarps * NTB * kTileRows;
 
   int i = 0;
   for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
     const int s = i % S;
-    if (!(a.debug & 2) && !ptx::mbar_wait(&full[s], (i / S) & 1)) {
+    if (!ptx::mbar_wait(&full[s], (i / S) & 1)) {
       report_timeout(0x20000u | (unsigned)s);
       return;
     }
     const uint32_t stage = smem_base + a.off_stage + s * kTileRows * a.stride_s;
-    float* redbuf = red + (i & 1) * kRedPerBuf;
+    float* redbuf = red + (i & 1) * red_per_buf + cw * kRedPerWarp;
     if constexpr (GROUPS) {
       float accA = 0.f, accB = 0.f;
-      if (!(a.debug & 1))
-      for (int sbl = cw; sbl < nsb_local; sbl += kConsumerWarps)
-        q4k_item_groups(sm, stage, sbl, lane, gl, accA, accB);
+      for (int sbl = cw; sbl < nsb_local; sbl += W)
+        q4k_item_groups(sm, stage, sbl, gl, accA, accB);
+
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
       accA += __shfl_xor_sync(0xffffffffu, accA, 1);
       accA += __shfl_xor_sync(0xffffffffu, accA, 2);
       accB += __shfl_xor_sync(0xffffffffu, accB, 1);
       accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+      if (i >= 2 && !ptx::mbar_wait(&red_empty[i & 1], ((i >> 1) - 1) & 1)) {
+        report_timeout(0x50000u);
+        return;
+      }
       if (tig == 0) {
-        redbuf[cw * kTileRows + gid] = accA;
-        redbuf[cw * kTileRows + gid + 8] = accB;
+        redbuf[gid] = accA;
+        redbuf[gid + 8] = accB;
       }
     } else {
       float acc[NT][4];
@@ -480,53 +631,25 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
       for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
-      for (int sbl = cw; sbl < nsb_local; sbl += kConsumerWarps)
+      for (int sbl = cw; sbl < nsb_local; sbl += W)
         q4k_item_batch<NT>(sm, stage, sbl, lane, acc);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
+      if (i >= 2 && !ptx::mbar_wait(&red_empty[i & 1], ((i >> 1) - 1) & 1)) {
+        report_timeout(0x50000u);
+        return;
+      }
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         const int col = 8 * t + 2 * tig;
-        redbuf[(cw * NTB + col) * kTileRows + gid] = acc[t][0];
-        redbuf[(cw * NTB + col + 1) * kTileRows + gid] = acc[t][1];
-        redbuf[(cw * NTB + col) * kTileRows + gid + 8] = acc[t][2];
-        redbuf[(cw * NTB + col + 1) * kTileRows + gid + 8] = acc[t][3];
+        redbuf[col * kTileRows + gid] = acc[t][0];
+        redbuf[(col + 1) * kTileRows + gid] = acc[t][1];
+        redbuf[col * kTileRows + gid + 8] = acc[t][2];
+        redbuf[(col + 1) * kTileRows + gid + 8] = acc[t][3];
       }
     }
-    if (!consumer_sync()) return;
-    // cross-warp sum in warp order; thread e -> (column e / 16, row e % 16)
-    const int row = ctid & 15, col = ctid >> 4;
-    const long long grow = (long long)rt * kTileRows + row;
-    const bool mine = col < NTB && col < a.m && grow < a.n;
-    float v = 0.f;
-    if (col < NTB) {
-#pragma unroll
-      for (int w8 = 0; w8 < kConsumerWarps; ++w8) v += redbuf[(w8 * NTB + col) * kTileRows + row];
-    }
-    v *= unscale;
-    if (a.k_splits == 1) {
-      if (mine) a.out[(long long)col * a.n + grow] = v;
-    } else {
-      if (mine) a.partials[((long long)ks * a.m + col) * a.n + grow] = v;
-      __threadfence();
-      if (!consumer_sync()) return;
-      if (ctid == 0) {
-        const unsigned int old = atomicAdd(&a.counters[rt], 1u);
-        const int last = old == (unsigned)(a.k_splits - 1);
-        if (last) a.counters[rt] = 0u;  // every other K range has already arrived
-        s_last = last;
-      }
-      if (!consumer_sync()) return;
-      if (s_last) {
-        __threadfence();
-        if (mine) {
-          float total = 0.f;
-          for (int q = 0; q < a.k_splits; ++q)
-            total += __ldcg(&a.partials[((long long)q * a.m + col) * a.n + grow]);
-          a.out[(long long)col * a.n + grow] = total;
-        }
-      }
-    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&red_full[i & 1]);
   }
 }
 
@@ -540,7 +663,7 @@ inline int pad_stride(int bytes, int want) {
 }
 
 struct Layout {
-  int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, off_zero, total;
+  int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc, total;
 };
 
 Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool contiguous) {
@@ -551,18 +674,20 @@ Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool contiguous
                           : pad_stride(sb_per_split * block_bytes(fmt), groups ? 64 : 32);
   L.xs_stride = pad_stride(sb_per_split * 512, 64);
   L.stage_bytes = kTileRows * L.stride_s;
-  int off = 256;  // mbarriers: full[8], empty[8], consumer barrier
+  int off = 256;  // mbarriers: full[8], empty[8], consumer barrier, red_full[2], red_empty[2]
   L.off_stage = off;
   off += stages * L.stage_bytes;
   L.off_xs = off;
   off += ntb * L.xs_stride;
   L.off_sx = off;
-  off += round_up(sb_per_split * 8 * ntb * 4, 128);
+  off += round_up(sb_per_split * 8 * (groups ? 2 : ntb) * 4, 128);
   L.off_red = off;
-  off += 2 * kConsumerWarps * ntb * kTileRows * 4;
+  off += 2 * kMaxConsumerWarps * ntb * kTileRows * 4;
   L.off_scl = off;
-  off += groups ? 0 : kConsumerWarps * kTileRows * kSclRowFloats * 4;
+  off += groups ? 0 : kMaxConsumerWarps * kTileRows * kSclRowFloats * 4;
   L.off_zero = off;  // 64 zero bytes: the B fragment of lanes whose weights feed another column
+  off += 64;
+  L.off_misc = off;  // the factor that undoes the activation scaling
   off += 64;
   L.total = round_up(off, 128);
   return L;
@@ -654,7 +779,6 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.stages = plan.stages;
   const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages, plan.k_splits == 1);
   a.contiguous = plan.k_splits == 1;
-  a.debug = getenv("TB200_GEMV_DEBUG") ? atoi(getenv("TB200_GEMV_DEBUG")) : 0;
   a.stride_s = L.stride_s;
   a.xs_stride = L.xs_stride;
   a.off_stage = L.off_stage;
@@ -663,6 +787,18 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.off_red = L.off_red;
   a.off_scl = L.off_scl;
   a.off_zero = L.off_zero;
+  a.off_misc = L.off_misc;
+  {
+    // as many decode warps as divide the super-blocks of a K range most evenly (ties: more warps)
+    int best_w = kMaxConsumerWarps;
+    double best_eff = 0;
+    for (int w = kMaxConsumerWarps; w >= 4; --w) {
+      const int rounds = (plan.sb_per_split + w - 1) / w;
+      const double eff = (double)plan.sb_per_split / (rounds * w) * (0.9 + 0.1 * w / kMaxConsumerWarps);
+      if (eff > best_eff + 1e-9) { best_eff = eff; best_w = w; }
+    }
+    a.consumer_warps = best_w;
+  }
   if (plan.k_splits > 1) {
     if (!scratch) return cudaErrorInvalidValue;
     a.counters = static_cast<unsigned int*>(scratch);
