@@ -110,6 +110,15 @@ int64_t tb200_gguf_weight_bytes(int32_t format, int64_t n, int64_t k);
  * library then picks a kernel that needs none. */
 int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int64_t k);
 
+/* The launch plan the pipelined GEMV would use with `scratch_bytes` of scratch available:
+ * plan_out[0..7] = {covered by the pipelined kernel (0/1), CTAs along K, CTAs along N,
+ * 256-weight super-blocks per K range, ring stages, dynamic shared memory bytes, scratch bytes
+ * needed, CTAs per SM}.  Without a CUDA device the plan is made for a B200 (148 SMs).  Plays the
+ * role of the reference's schedule dictionaries (src/tensor/compiler/cuda/schedules.py:3-52),
+ * except that the schedule is derived from the shape instead of searched. */
+int32_t tb200_gguf_gemv_plan(int32_t format, int64_t m, int64_t n, int64_t k, int64_t scratch_bytes,
+                             int32_t *plan_out);
+
 /* Synchronises the current device and reads the sticky status words of the pipelined kernels.
  * Every device-side wait in this library is bounded (about two seconds); a wait that gives up
  * records a code there and the kernel returns instead of hanging.  Returns TENSOR_OK and

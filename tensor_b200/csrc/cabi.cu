@@ -149,6 +149,34 @@ int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int6
   return plan.supported ? plan.scratch_bytes : 0;
 }
 
+int32_t tb200_gguf_gemv_plan(int32_t format, int64_t m, int64_t n, int64_t k, int64_t scratch_bytes,
+                             int32_t* plan_out) {
+  if (!plan_out) return TENSOR_ERROR_ARGUMENT;
+  for (int i = 0; i < 8; ++i) plan_out[i] = 0;
+  if (!valid_format(format) || m < 1 || n < 1 || k < 0 || k % block_weights(format)) return TENSOR_ERROR_ARGUMENT;
+  DeviceInfo b200;  // without a device, plan for a B200: 148 SMs, 227 KB of opt-in shared memory
+  b200.ordinal = 0;
+  b200.sm_count = 148;
+  b200.max_smem_optin = 232448;
+  b200.cc_major = 10;
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) {
+    cudaGetLastError();
+    dev = &b200;
+  }
+  GemvPlan plan = plan_gemv_fast(format, kBF16, m, n, k, scratch_bytes, *dev);
+  plan_out[0] = plan.supported ? 1 : 0;
+  plan_out[1] = plan.k_splits;
+  plan_out[2] = plan.row_groups;
+  plan_out[3] = plan.sb_per_split;
+  plan_out[4] = plan.stages;
+  plan_out[5] = plan.smem_bytes;
+  plan_out[6] = (int32_t)(plan.scratch_bytes > 0x7fffffff ? 0x7fffffff : plan.scratch_bytes);
+  plan_out[7] = plan.ctas_per_sm;
+  return TENSOR_OK;
+}
+
 int32_t tb200_gguf_device_status(uint32_t* status, TensorErrorV1* error) {
   unsigned int a = 0, b = 0;
   cudaError_t e = cudaDeviceSynchronize();

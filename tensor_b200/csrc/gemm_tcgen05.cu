@@ -283,22 +283,6 @@ __global__ void __launch_bounds__(kThreads, 2)
 
 // ---- host side -------------------------------------------------------------------------------------
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
 template <int FMT>
 cudaError_t launch_fmt(const CUtensorMap& tmap, const uint8_t* w, float* out, long long m, long long n,
                        long long k, cudaStream_t stream) {
@@ -326,24 +310,13 @@ bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const D
 
 cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m, long long n,
                              long long k, cudaStream_t stream, const char** detail) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (!encode) {
-    if (detail) *detail = "cuTensorMapEncodeTiled is not available from the driver";
-    return cudaErrorNotSupported;
-  }
   // x as a 2-D tensor [m rows, k columns] of bf16; box = 64 columns (128 bytes) x 256 rows,
   // 128-byte swizzle, rows past m read as zero.
-  CUtensorMap tmap;
-  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
-  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)kTileTok};
-  const cuuint32_t elem[2] = {1, 1};
-  CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    if (detail) *detail = "cuTensorMapEncodeTiled rejected the activation layout";
-    return cudaErrorInvalidValue;
+  alignas(64) CUtensorMap tmap;
+  if (!make_tensor_map_2d(&tmap, TmaType::kBF16, x, (unsigned long long)k, (unsigned long long)m,
+                          (unsigned long long)k * 2, kBlockK, kTileTok, true)) {
+    if (detail) *detail = "cuTensorMapEncodeTiled is unavailable or rejected the activation layout";
+    return cudaErrorNotSupported;
   }
   switch (fmt) {
     case kQ4_K: return launch_fmt<kQ4_K>(tmap, w, out, m, n, k, stream);

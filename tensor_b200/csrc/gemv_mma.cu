@@ -22,6 +22,10 @@
 //  * the K range of a CTA is fixed for its lifetime (x is staged once); row tiles are strided
 //    over CTAs; if K is split across CTAs, partial sums go to caller-provided scratch and the
 //    last CTA to arrive for a row tile adds them in a fixed order (deterministic).
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -35,6 +39,7 @@ constexpr int kReducerWarp = kMaxConsumerWarps + 1;  // adds the consumer warps'
 constexpr int kThreads = (kMaxConsumerWarps + 2) * 32;
 constexpr int kTileRows = 16;
 constexpr int kMaxStages = 8;
+constexpr int kCounterBytes = 4096;  // one arrival counter per group of CTAs that share row tiles (<= 1024)
 constexpr int kSclRowFloats = 18;  // 8 x (scale, offset) pairs + 2 floats of padding (bank spread)
 
 struct GemvArgs {
@@ -58,6 +63,7 @@ struct GemvArgs {
   int off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc;
   int consumer_warps;  // warps that decode (<= 8), chosen to divide the super-blocks of a K range evenly
   int contiguous;  // one bulk copy per tile (K not split): stage rows are packed like global rows
+  int use_tma;     // K split: one 2-D tiled TMA copy per tile (16 rows x the K range)
 };
 
 // All MMAs run in fp16: q | 0x6400 is the fp16 number 1024 + q for q < 1024, and a nibble that
@@ -103,15 +109,16 @@ __device__ __forceinline__ float sum_f16x8(uint4 v) {
   return s;
 }
 
-// Stage the activations of this CTA's K range as fp16: rows b < NTB (zero beyond m), each aligned
-// group of four values stored as [x0, x2, x1, x3] so that an MMA B fragment is one contiguous
-// load, plus the per-32-group sums Sx[g][b] of the staged values in fp32.  bf16 inputs are scaled
-// by one power of two per CTA so that the largest magnitude lands in [2^14, 2^15): the conversion
-// is then exact for every value within 2^-32 of the largest, and the result is scaled back at the
-// end.  Returns the factor that undoes the scaling.
+// Batch staging (1 < m <= 16): the activation rows of this CTA's K range are fetched with bulk
+// async copies (one per row, a single round trip to L2 / HBM), then converted in place to fp16:
+// each aligned group of four values is stored as [x0, x2, x1, x3] so that an MMA B fragment is one
+// contiguous load, and the per-32-group sums Sx[g][b] of the staged values are kept in fp32.  bf16
+// inputs are scaled by one power of two per CTA so that the largest magnitude lands in
+// [2^14, 2^15): the conversion is then exact for every value within 2^-32 of the largest, and the
+// result is scaled back at the end.  Returns the factor that undoes the scaling.
 template <bool F16, int NTB, typename Sync>
 __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
-                                                   int klen, Sync&& consumer_sync, bool& ok) {
+                                                   int klen, uint64_t* xbar, Sync&& consumer_sync, bool& ok) {
   const int kConsumerThreads = a.consumer_warps * 32;
   const int chunks = klen >> 3;  // 8 values (16 bytes) each; a multiple of 32
   const int total = NTB * chunks;
@@ -119,17 +126,29 @@ __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* s
   float* sx = reinterpret_cast<float*>(smem + a.off_sx);
   uint32_t* wmax = reinterpret_cast<uint32_t*>(smem + a.off_red);  // reused before the main loop
   const uint16_t* xg = static_cast<const uint16_t*>(a.x);
+  const uint32_t row_bytes_x = (uint32_t)klen * 2;
+  if (ctid == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * row_bytes_x);
+  __syncwarp();
+  if (ctid < a.m) ptx::bulk_g2s(xs + (size_t)ctid * a.xs_stride, xg + (long long)ctid * a.k + k0, row_bytes_x, xbar);
+  // rows beyond m are zero
+  for (int idx = a.m * chunks + ctid; idx < total; idx += kConsumerThreads) {
+    const int b = idx / chunks, c = idx - b * chunks;
+    *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = make_uint4(0, 0, 0, 0);
+  }
+  if (!ptx::mbar_wait(xbar, 0)) {
+    report_timeout(0x60000u);
+    ok = false;
+    return 1.f;
+  }
   float scale = 1.f, unscale = 1.f;
   if constexpr (!F16) {
     uint32_t mx = 0;
-    for (int idx = ctid; idx < total; idx += kConsumerThreads) {
+    for (int idx = ctid; idx < a.m * chunks; idx += kConsumerThreads) {
       const int b = idx / chunks, c = idx - b * chunks;
-      if (b < a.m) {
-        const uint4 v = *reinterpret_cast<const uint4*>(xg + (long long)b * a.k + k0 + (c << 3));
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      const uint4 v = *reinterpret_cast<const uint4*>(xs + (size_t)b * a.xs_stride + (c << 4));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
-      }
+      for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -137,7 +156,8 @@ __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* s
     ok = consumer_sync();
     if (!ok) return 1.f;
 #pragma unroll
-    for (int i = 0; i < a.consumer_warps; ++i) mx = max(mx, wmax[i]);
+    for (int i = 0; i < kMaxConsumerWarps; ++i)
+      if (i < a.consumer_warps) mx = max(mx, wmax[i]);
     const int e = (int)(mx >> 7);  // biased bf16 exponent of the largest magnitude
     if (e > 0 && e < 255) {
       int sh = 141 - e;  // largest -> [2^14, 2^15)
@@ -153,9 +173,9 @@ __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* s
     const bool valid = idx < total;
     const int b = valid ? idx / chunks : 0;
     const int c = valid ? idx - b * chunks : 0;
+    uint4* slot = reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4));
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (valid && b < a.m)
-      v = to_f16x8<F16>(*reinterpret_cast<const uint4*>(xg + (long long)b * a.k + k0 + (c << 3)), scale);
+    if (valid) v = to_f16x8<F16>(*slot, scale);
     float s = sum_f16x8(v);
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -165,7 +185,7 @@ __device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* s
       p.y = __byte_perm(v.x, v.y, 0x7632);
       p.z = __byte_perm(v.z, v.w, 0x5410);
       p.w = __byte_perm(v.z, v.w, 0x7632);
-      *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = p;
+      *slot = p;
       if ((c & 3) == 0) sx[(c >> 2) * NTB + b] = s;
     }
   }
@@ -219,6 +239,16 @@ __device__ __forceinline__ void stage_activations_groups(const GemvArgs& a, uint
     }
   }
 }
+
+// Pin a value in a register.  Kernel parameters live in the constant bank and the compiler likes
+// to re-load them inside hot loops instead of spending a register; those loads sit on the long
+// scoreboard and stall an otherwise short dependency chain.
+__device__ __forceinline__ uint32_t pin(uint32_t v) {
+  uint32_t r;
+  asm volatile("mov.b32 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ int pin(int v) { return (int)pin((uint32_t)v); }
 
 // (a & mask) | bits in ONE logic op.  The constants are handed over in registers: with two
 // immediates the compiler splits the expression into two LOP3s, and logic ops (half-rate ALU pipe)
@@ -408,7 +438,8 @@ __device__ __forceinline__ void q4k_item_groups(const SmemMap& sm, uint32_t stag
 }
 
 template <int FMT, bool F16, int NT, bool GROUPS>
-__global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(kThreads, 2)
+    gemv_mma_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap) {
   static_assert(FMT == kQ4_K, "only Q4_K is pipelined so far");
   constexpr int NTB = GROUPS ? 1 : NT * 8;
   constexpr int kBlockBytes = Fmt<FMT>::kBytes;
@@ -418,6 +449,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
   uint64_t* cbar = empty + kMaxStages;  // consumer-only barrier for the staging phase (bounded)
   uint64_t* red_full = cbar + 1;        // [2] consumers -> reducer: partial sums of a tile are in place
   uint64_t* red_empty = red_full + 2;   // [2] reducer -> consumers: buffer may be overwritten
+  uint64_t* xbar = red_empty + 2;       // activation rows have landed in shared memory
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int W = a.consumer_warps;
@@ -438,6 +470,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
       ptx::mbar_init(&empty[s], W);
     }
     ptx::mbar_init(cbar, W);
+    ptx::mbar_init(xbar, 1);
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&red_full[b], W);
       ptx::mbar_init(&red_empty[b], 1);
@@ -465,6 +498,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
           ptx::bulk_g2s(dst, src0 + row0 * a.row_bytes, (uint32_t)rows * range_bytes, &full[s]);
+        }
+      } else if (a.use_tma) {
+        // K is split: one tiled copy fetches the K range of all 16 rows (rows past N and
+        // super-blocks past K arrive as zeros, and count towards the transaction bytes)
+        if (lane == 0) {
+          ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)(kTileRows * a.stride_s));
+          ptx::tma_load_2d(dst, &wmap, sb0 * (kBlockBytes / 8), (int)row0, &full[s]);
         }
       } else {
         if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
@@ -514,24 +554,52 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
 #pragma unroll
         for (int j = 0; j < kPerLane; ++j)
           if (mine[j]) a.partials[ks * plane + gidx[j]] = vals[j];
+      }
+    }
+    if (a.k_splits > 1) {
+      // K is split over CTAs: the CTAs that share this set of row tiles count themselves in; the
+      // last one to arrive adds everybody's partial sums in K order (deterministic) and writes out.
+      __threadfence();
+      __syncwarp();
+      unsigned int last = 0;
+      if (lane == 0) {
+        const unsigned int old = atomicAdd(&a.counters[rg], 1u);
+        last = old == (unsigned)(a.k_splits - 1);
+        if (last) a.counters[rg] = 0u;  // every other K range has already arrived: ready for the next call
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
         __threadfence();
-        __syncwarp();
-        unsigned int last = 0;
-        if (lane == 0) {
-          const unsigned int old = atomicAdd(&a.counters[rt], 1u);
-          last = old == (unsigned)(a.k_splits - 1);
-          if (last) a.counters[rt] = 0u;  // every other K range has already arrived
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-#pragma unroll
-          for (int j = 0; j < kPerLane; ++j)
-            if (mine[j]) {
-              float total = 0.f;
-              for (int q = 0; q < a.k_splits; ++q) total += __ldcg(&a.partials[q * plane + gidx[j]]);
-              a.out[gidx[j]] = total;
+        // Work items = (row tile of this CTA group, column, 4 consecutive rows), spread over the
+        // lanes so that many independent 16-byte loads are in flight; each adds the K ranges in order.
+        const long long plane = (long long)a.m * a.n;
+        const int my_tiles = (a.row_tiles - rg + a.row_groups - 1) / a.row_groups;
+        const int per_tile = a.m * 4;
+        const bool vec = (a.n & 3) == 0;
+        for (int item = lane; item < my_tiles * per_tile; item += 32) {
+          const int t = item / per_tile, rem = item - t * per_tile;
+          const int col = rem >> 2, r4 = (rem & 3) * 4;
+          const long long grow = ((long long)rg + (long long)t * a.row_groups) * kTileRows + r4;
+          if (grow >= a.n) continue;
+          const long long idx = (long long)col * a.n + grow;
+          if (vec) {
+            float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int q = 0; q < a.k_splits; ++q) {
+              const float4 p = __ldcg(reinterpret_cast<const float4*>(&a.partials[q * plane + idx]));
+              tot.x += p.x;
+              tot.y += p.y;
+              tot.z += p.z;
+              tot.w += p.w;
             }
+            *reinterpret_cast<float4*>(&a.out[idx]) = tot;
+          } else {
+            for (int r = 0; r < 4 && grow + r < a.n; ++r) {
+              float total = 0.f;
+              for (int q = 0; q < a.k_splits; ++q) total += __ldcg(&a.partials[q * plane + idx + r]);
+              a.out[idx + r] = total;
+            }
+          }
         }
       }
     }
@@ -558,7 +626,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
   } else {
     bool staged = true;
     const float unscale =
-        stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, consumer_sync, staged);
+        stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, xbar, consumer_sync, staged);
     if (!staged) return;
     if (ctid == 0) *unscale_slot = unscale;
   }
@@ -567,11 +635,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
   const int gid = lane >> 2, tig = lane & 3;
   const uint32_t smem_base = ptx::smem_addr(smem);
   SmemMap sm;
-  sm.xs = smem_base + a.off_xs;
-  sm.sx = smem_base + a.off_sx;
-  sm.scl = smem_base + a.off_scl + cw * (kTileRows * kSclRowFloats * 4);
-  sm.stride_s = a.stride_s;
-  sm.xs_stride = a.xs_stride;
+  sm.xs = pin(smem_base + a.off_xs);
+  sm.sx = pin(smem_base + a.off_sx);
+  sm.scl = pin(smem_base + a.off_scl + cw * (kTileRows * kSclRowFloats * 4));
+  sm.stride_s = pin(a.stride_s);
+  sm.xs_stride = pin(a.xs_stride);
   sm.nc = nibble_consts();
   GroupLane gl;
   if constexpr (GROUPS) {
@@ -583,13 +651,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
 #pragma unroll
       for (int nib = 0; nib < 2; ++nib) {
         const bool live = gid == 2 * (tig >> 1) + 4 * ci + nib;
-        gl.xbase[2 * ci + nib] = live ? mine : zeros;
-        gl.xstep[2 * ci + nib] = live ? 512 : 0;
+        gl.xbase[2 * ci + nib] = pin(live ? mine : zeros);
+        gl.xstep[2 * ci + nib] = pin(live ? 512 : 0);
       }
-    gl.row_off = gid * a.stride_s;
-    gl.row8 = 8 * a.stride_s;
-    gl.quant_off = 16 + 16 * tig;
-    gl.sxu = sm.sx + 2 * tig * 8;
+    gl.row_off = pin((uint32_t)(gid * a.stride_s));
+    gl.row8 = pin((uint32_t)(8 * a.stride_s));
+    gl.quant_off = pin((uint32_t)(16 + 16 * tig));
+    gl.sxu = pin(sm.sx + 2 * tig * 8);
     gl.upper = tig >= 2;
     gl.m_lo = gl.upper ? 0x0F0F0F0Fu : 0x3F3F3F3Fu;
     gl.m_hi = gl.upper ? 0x30303030u : 0u;
@@ -597,18 +665,21 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
     gl.sel1 = gl.sel0 + 1;
   }
 
-  int i = 0;
-  for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
-    const int s = i % S;
-    if (!ptx::mbar_wait(&full[s], (i / S) & 1)) {
+  const uint32_t stage0 = pin(smem_base + a.off_stage);
+  const uint32_t stage_step = pin((uint32_t)(kTileRows * a.stride_s));
+  const int row_tiles = pin(a.row_tiles), row_groups = pin(a.row_groups);
+  const int nsb_l = pin(nsb_local), Wp = pin(W), Sp = pin(S);
+  int i = 0, s = 0, phase = 0;
+  for (int rt = rg; rt < row_tiles; rt += row_groups, ++i) {
+    if (!ptx::mbar_wait(&full[s], phase)) {
       report_timeout(0x20000u | (unsigned)s);
       return;
     }
-    const uint32_t stage = smem_base + a.off_stage + s * kTileRows * a.stride_s;
+    const uint32_t stage = stage0 + s * stage_step;
     float* redbuf = red + (i & 1) * red_per_buf + cw * kRedPerWarp;
     if constexpr (GROUPS) {
       float accA = 0.f, accB = 0.f;
-      for (int sbl = cw; sbl < nsb_local; sbl += W)
+      for (int sbl = cw; sbl < nsb_l; sbl += Wp)
         q4k_item_groups(sm, stage, sbl, gl, accA, accB);
 
       __syncwarp();
@@ -631,7 +702,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
       for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
-      for (int sbl = cw; sbl < nsb_local; sbl += W)
+      for (int sbl = cw; sbl < nsb_l; sbl += Wp)
         q4k_item_batch<NT>(sm, stage, sbl, lane, acc);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
@@ -650,10 +721,17 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvArgs a)
     }
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(&red_full[i & 1]);
+    if (++s == Sp) {
+      s = 0;
+      phase ^= 1;
+    }
   }
 }
 
 inline int round_up(int v, int to) { return (v + to - 1) / to * to; }
+inline int groups_limit(int slots, int splits) { return slots / splits; }
+// a tiled copy with 8-byte elements covers at most 256 elements = 2048 bytes per row
+inline bool tma_ok(int fmt, int sb_per_split) { return sb_per_split * block_bytes(fmt) <= 2048; }
 
 // smallest s >= bytes with s % 128 == want (want a multiple of 16)
 inline int pad_stride(int bytes, int want) {
@@ -666,11 +744,11 @@ struct Layout {
   int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc, total;
 };
 
-Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool contiguous) {
+Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed) {
   const bool groups = m == 1;
   const int ntb = groups ? 1 : (m <= 8 ? 8 : 16);
   Layout L;
-  L.stride_s = contiguous ? sb_per_split * block_bytes(fmt)
+  L.stride_s = packed ? sb_per_split * block_bytes(fmt)
                           : pad_stride(sb_per_split * block_bytes(fmt), groups ? 64 : 32);
   L.xs_stride = pad_stride(sb_per_split * 512, 64);
   L.stage_bytes = kTileRows * L.stride_s;
@@ -717,23 +795,28 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
       const int per = (nsb + splits - 1) / splits;
       if ((splits - 1) * per >= nsb) continue;  // an empty K range
       const long long need =
-          splits > 1 ? ((row_tiles * 4 + 255) / 256 * 256 + (long long)splits * m * n * 4) : 0;
+          splits > 1 ? (kCounterBytes + (long long)splits * m * n * 4) : 0;
       if (need > scratch_bytes_available) continue;
       int stages = 0;
       Layout L{};
       for (int s = kMaxStages; s >= 2; --s) {
-        L = make_layout(fmt, (int)m, per, s, splits == 1);
+        L = make_layout(fmt, (int)m, per, s, splits == 1 || tma_ok(fmt, per));
         if (L.total <= smem_limit) { stages = s; break; }
       }
       if (!stages) continue;
-      // a ring that holds little data cannot keep HBM busy
-      if ((long long)stages * L.stage_bytes * per_sm < 96 * 1024 && stages < kMaxStages) continue;
+      // splitting K so finely that the ring holds little data cannot keep HBM busy
+      if (splits > 1 && (long long)stages * L.stage_bytes * per_sm < 96 * 1024 && stages < kMaxStages) continue;
+      if (groups_limit(slots, splits) > 1024) continue;
       int groups = (int)((long long)slots / splits < row_tiles ? slots / splits : row_tiles);
       if (groups < 1) continue;
       const long long tiles_per_cta = (row_tiles + groups - 1) / groups;
       // time ~ bytes the busiest SM streams, plus the partial-sum traffic and sync of a split
       double cost = (double)per_sm * tiles_per_cta * per * block_bytes(fmt) * kTileRows;
       if (splits > 1) cost += per_sm * ((double)tiles_per_cta * kTileRows * m * 4 * 2 + 2000.0 * tiles_per_cta);
+      // per-row bulk copies of ~2 KB run far below HBM speed (each costs a few hundred cycles)
+      if (splits > 1 && !tma_ok(fmt, per)) cost *= 3.0;
+      // the decode warps are latency-bound: a second CTA on the SM is worth more than a perfect split
+      if (per_sm == 1 && m == 1) cost *= 1.3;
       if (cost < best_cost) {
         best_cost = cost;
         best.supported = true;
@@ -744,6 +827,7 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
         best.stage_bytes = L.stage_bytes;
         best.smem_bytes = L.total;
         best.scratch_bytes = need;
+        best.ctas_per_sm = per_sm;
       }
     }
   }
@@ -751,11 +835,20 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
 }
 
 template <int FMT, bool F16, int NT, bool GROUPS>
-static cudaError_t launch_variant(const GemvArgs& a, int grid, int smem, cudaStream_t stream) {
+static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t stream) {
   auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  kernel<<<grid, kThreads, smem, stream>>>(a);
+  alignas(64) CUtensorMap wmap;
+  memset(&wmap, 0, sizeof(wmap));
+  if (a.use_tma) {
+    // the weight as [n rows] x [row_bytes / 8] opaque 8-byte words; box = K range x 16 rows
+    const unsigned box_inner = (unsigned)(a.sb_per_split * Fmt<FMT>::kBytes / 8);
+    if (!make_tensor_map_2d(&wmap, TmaType::kU64, a.w, (unsigned long long)a.row_bytes / 8, (unsigned long long)a.n,
+                            (unsigned long long)a.row_bytes, box_inner, kTileRows, false))
+      return cudaErrorNotSupported;
+  }
+  kernel<<<grid, kThreads, smem, stream>>>(a, wmap);
   return cudaGetLastError();
 }
 
@@ -777,8 +870,10 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.row_groups = plan.row_groups;
   a.row_tiles = (int)((n + kTileRows - 1) / kTileRows);
   a.stages = plan.stages;
-  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages, plan.k_splits == 1);
+  const bool tma = plan.k_splits > 1 && tma_ok(fmt, plan.sb_per_split);
+  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages, plan.k_splits == 1 || tma);
   a.contiguous = plan.k_splits == 1;
+  a.use_tma = tma;
   a.stride_s = L.stride_s;
   a.xs_stride = L.xs_stride;
   a.off_stage = L.off_stage;
@@ -802,7 +897,7 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   if (plan.k_splits > 1) {
     if (!scratch) return cudaErrorInvalidValue;
     a.counters = static_cast<unsigned int*>(scratch);
-    a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + ((a.row_tiles * 4 + 255) / 256) * 256);
+    a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kCounterBytes);
   }
   const int grid = plan.k_splits * plan.row_groups;
   const bool f16 = xt == kF16;

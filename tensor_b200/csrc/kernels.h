@@ -33,6 +33,7 @@ struct GemvPlan {
   int stage_bytes = 0;
   int smem_bytes = 0;
   long long scratch_bytes = 0;
+  int ctas_per_sm = 1;
 };
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
                         long long scratch_bytes_available, const DeviceInfo& dev);
@@ -44,6 +45,13 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
 bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const DeviceInfo& dev);
 cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m,
                              long long n, long long k, cudaStream_t stream, const char** detail);
+
+// 2-D tiled TMA tensor map (128 bytes, 64-byte aligned) over a row-major matrix; elements are bf16
+// or opaque 8-byte words.  Returns false if the driver entry point is unavailable or rejects it.
+enum class TmaType { kBF16, kU64 };
+bool make_tensor_map_2d(void* map_out, TmaType type, const void* base, unsigned long long inner,
+                        unsigned long long outer, unsigned long long row_stride_bytes, unsigned box_inner,
+                        unsigned box_outer, bool swizzle_128b);
 
 // Sticky status words of the pipelined kernels (bounded waits that gave up); these synchronise.
 cudaError_t read_gemv_status(unsigned int* value, bool clear);

@@ -67,6 +67,19 @@ def gemv_scratch_bytes(encoding, m: int, n: int, k: int) -> int:
     return int(lib().tb200_gguf_gemv_scratch_bytes(get_format(encoding).type_id, m, n, k))
 
 
+def gemv_plan(encoding, m: int, n: int, k: int, scratch_bytes: int = 1 << 40) -> dict:
+    """The launch plan of the pipelined GEMV at this shape (see ``tb200_gguf_gemv_plan``)."""
+    out = (ctypes.c_int32 * 8)()
+    status = lib().tb200_gguf_gemv_plan(get_format(encoding).type_id, m, n, k, scratch_bytes, out)
+    if status:
+        raise ValueError(f"no plan for format {encoding!r}, m={m}, n={n}, k={k}")
+    keys = ("pipelined", "k_splits", "row_groups", "sb_per_split", "stages", "smem_bytes",
+            "scratch_bytes", "ctas_per_sm")
+    plan = dict(zip(keys, (int(v) for v in out)))
+    plan["pipelined"] = bool(plan["pipelined"])
+    return plan
+
+
 def device_status() -> int:
     """Synchronise and return the sticky device status word (0 = no bounded wait gave up)."""
     word = ctypes.c_uint32(0)
