@@ -40,6 +40,24 @@ def shard_weight_bytes(raw, encoding, n: int, k: int, rank: int, world: int):
     return flat[start * rb:stop * rb]
 
 
+def all_gather_columns(out_local: torch.Tensor, gathered: torch.Tensor, out: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather ``out_local[m, n_local]`` of every rank into ``out[m, world * n_local]``.
+
+    ``gathered`` is a ``[world, m, n_local]`` staging buffer (``all_gather_into_tensor`` concatenates
+    along dim 0); rank r's columns land at ``[r * n_local, (r + 1) * n_local)`` of every output row.
+    Works with any backend (NCCL on GPUs, gloo in the CPU tests).
+    """
+    import torch.distributed as dist
+
+    world, m, n_local = gathered.shape
+    dist.all_gather_into_tensor(gathered.view(world * m, n_local), out_local.view(m, n_local), group=group)
+    if m == 1:
+        out.view(-1).copy_(gathered.view(-1))
+    else:
+        out.view(m, world, n_local).copy_(gathered.permute(1, 0, 2))
+    return out
+
+
 class QuantLinear:
     """``y[m, N] = x[m, K] . dequant(W[N, K])^T`` for a fixed batch ``m``.
 
@@ -86,13 +104,7 @@ class QuantLinear:
         ``raw`` substitutes another weight of the same shape (e.g. the next layer's)."""
         self.kernel.launch(x, self.raw if raw is None else raw, self.out_local)
         if self.world > 1:
-            import torch.distributed as dist
-
-            dist.all_gather_into_tensor(self._gathered, self.out_local, group=self.group)
-            if self.m == 1:
-                self.out.view(-1).copy_(self._gathered.view(-1))
-            else:
-                self.out.view(self.m, self.world, self.n_local).copy_(self._gathered.permute(1, 0, 2))
+            all_gather_columns(self.out_local, self._gathered, self.out, group=self.group)
         return self.out
 
     __call__ = forward
@@ -125,4 +137,5 @@ class HostProjection:
         return self.y_host
 
 
-__all__ = ["GEMV_MAX_ROWS", "HostProjection", "QuantLinear", "shard_rows", "shard_weight_bytes"]
+__all__ = ["GEMV_MAX_ROWS", "HostProjection", "QuantLinear", "all_gather_columns", "shard_rows",
+           "shard_weight_bytes"]
