@@ -64,14 +64,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return r;
 }
 
-// 32-bit load from a 2-byte aligned address (Q6_K blocks are 210 bytes).
-__device__ __forceinline__ uint32_t load_u32_a2(const uint8_t* p) {
-  if ((reinterpret_cast<uintptr_t>(p) & 2) == 0) return __ldg(reinterpret_cast<const uint32_t*>(p));
-  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(p - 2));
-  const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(p + 2));
-  return __funnelshift_r(lo, hi, 16);
-}
-
 // Store 32 consecutive bf16 of row `r` (k offset 32*h within the 64-wide stage) as four 16-byte
 // chunks at their swizzled positions: chunk c of row r lives at r*128 + ((c ^ (r & 7)) * 16).
 __device__ __forceinline__ void store_row_half(uint8_t* a_tile, int r, int h, const uint32_t (&v)[16]) {
@@ -84,18 +76,29 @@ __device__ __forceinline__ void store_row_half(uint8_t* a_tile, int r, int h, co
 }
 
 // ---- per-format decode of 32 weights: row `wrow`, k-block kb (64 wide), half h -> 16 bf16x2 -------
+// Split into `fetch` (global loads into registers) and `decode`, so the loads of k-block kb+1 are
+// in flight while k-block kb is decoded.
 
 template <int FMT> struct Decoder;
 
 template <> struct Decoder<kQ4_K> {
+  struct Raw {
+    uint4 hdr, q0, q1;
+  };
   // k-block kb: super-block kb/4, group pair p = kb%4; half h is group 2p+h (low / high nibbles
   // of quant bytes 32p .. 32p+31).
-  __device__ static __forceinline__ void run(const uint8_t* wrow, int kb, int h, uint32_t (&v)[16]) {
+  __device__ static __forceinline__ Raw fetch(const uint8_t* wrow, int kb, int /*h*/) {
     const uint8_t* blk = wrow + (kb >> 2) * 144;
+    const int p = kb & 3;
+    Raw r;
+    r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+    r.q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * p));
+    r.q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * p));
+    return r;
+  }
+  __device__ static __forceinline__ void decode(const Raw& r, int kb, int h, uint32_t (&v)[16]) {
     const int p = kb & 3, g = 2 * p + h;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * p));
-    const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * p));
+    const uint4 hdr = r.hdr;
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     const int j = g & 3, sh = 8 * j;
@@ -109,7 +112,7 @@ template <> struct Decoder<kQ4_K> {
     }
     const float dsc = d * (float)sc;
     const float dm = dmin * (float)mn;
-    const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t words[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t nib = (words[i] >> (4 * h)) & 0x0F0F0F0Fu;
@@ -123,22 +126,43 @@ template <> struct Decoder<kQ4_K> {
 };
 
 template <> struct Decoder<kQ6_K> {
+  // Blocks are 210 bytes, so a row's blocks are only 2-byte aligned: 32-byte spans are read as nine
+  // aligned words and realigned with funnel shifts at decode time.
+  struct Raw {
+    uint32_t ql[9], qh[9];
+    uint32_t shift;  // 0 or 16: misalignment of the block in bits
+    unsigned short scales, d;
+  };
   // k-block kb: super-block kb/4, j = kb%4 covers weights 64j .. 64j+63: half-block j/2, quarters
   // 2(j%2)+h; ql bytes 64(j/2) + 32h + lane, nibble j%2; qh bytes 32(j/2) + lane, bit pair 2(j%2)+h.
-  __device__ static __forceinline__ void run(const uint8_t* wrow, int kb, int h, uint32_t (&v)[16]) {
+  __device__ static __forceinline__ Raw fetch(const uint8_t* wrow, int kb, int h) {
     const uint8_t* blk = wrow + (kb >> 2) * 210;
-    const int j = kb & 3, half = j >> 1, quarter = 2 * (j & 1) + h;
+    const int j = kb & 3, half = j >> 1;
     const uint8_t* ql = blk + 64 * half + 32 * h;
     const uint8_t* qh = blk + 128 + 32 * half;
-    const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(blk + 208))));
-    const unsigned short scp = __ldg(reinterpret_cast<const unsigned short*>(blk + 192 + 4 * j + 2 * h));
-    const float ds0 = d * (float)(int)(int8_t)(scp & 0xFF);
-    const float ds1 = d * (float)(int)(int8_t)(scp >> 8);
+    Raw r;
+    r.shift = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 2) * 8;
+    const uint32_t* lp = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(ql) & ~uintptr_t(3));
+    const uint32_t* hp = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(qh) & ~uintptr_t(3));
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+      r.ql[i] = __ldg(lp + i);
+      r.qh[i] = __ldg(hp + i);
+    }
+    r.scales = __ldg(reinterpret_cast<const unsigned short*>(blk + 192 + 4 * j + 2 * h));
+    r.d = __ldg(reinterpret_cast<const unsigned short*>(blk + 208));
+    return r;
+  }
+  __device__ static __forceinline__ void decode(const Raw& r, int kb, int h, uint32_t (&v)[16]) {
+    const int j = kb & 3, quarter = 2 * (j & 1) + h;
+    const float d = __half2float(__ushort_as_half(r.d));
+    const float ds0 = d * (float)(int)(int8_t)(r.scales & 0xFF);
+    const float ds1 = d * (float)(int)(int8_t)(r.scales >> 8);
     const int lsh = 4 * (j & 1), hsh = 2 * quarter;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t lw = load_u32_a2(ql + 4 * i);
-      const uint32_t hw = load_u32_a2(qh + 4 * i);
+      const uint32_t lw = __funnelshift_r(r.ql[i], r.ql[i + 1], r.shift);
+      const uint32_t hw = __funnelshift_r(r.qh[i], r.qh[i + 1], r.shift);
       const uint32_t q = ((lw >> lsh) & 0x0F0F0F0Fu) | (((hw >> hsh) & 0x03030303u) << 4);
       const float ds = i < 4 ? ds0 : ds1;
       float f[4];
@@ -232,10 +256,14 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int grow = min(n0 + r, N - 1);  // rows past N are decoded from the last row and dropped
     const uint8_t* wrow = w + (long long)grow * row_bytes_;
     bool ok = true;
+    typename Decoder<FMT>::Raw raw = Decoder<FMT>::fetch(wrow, 0, h);
     for (int kb = 0; kb < k_blocks; ++kb) {
       const int s = kb % kStages;
+      // start the loads of the next k-block before decoding this one (clamped on the last)
+      const typename Decoder<FMT>::Raw next = Decoder<FMT>::fetch(wrow, min(kb + 1, k_blocks - 1), h);
       uint32_t v[16];
-      Decoder<FMT>::run(wrow, kb, h, v);
+      Decoder<FMT>::decode(raw, kb, h, v);
+      raw = next;
       if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
         report_timeout(0x30000u | (unsigned)kb);
         ok = false;
