@@ -140,6 +140,18 @@ int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void *x, const vo
                         int64_t m, int64_t n, int64_t k, void *scratch, int64_t scratch_bytes,
                         int32_t variant, void *stream, TensorErrorV1 *error);
 
+/* The same GEMV for callers that may neither pass scratch nor let the library allocate: launch
+ * adapters that forward only an artifact's declared buffers, hosts that own all device memory in
+ * their own arena, code inside a stream capture.  The split-K scratch is a 4 MiB array built into
+ * the library image (held by every GPU that loads the library, until exit).  Shapes that want more
+ * are rejected with status 2.  The first call on a device resolves the array's address: make it
+ * outside any stream capture.  All calls on a device share the array, so calls must not overlap on
+ * the GPU; each call clears the counters it needs first.  Calls no allocator.  This entry point
+ * has no counterpart in the reference. */
+#define TB200_GEMV_STATIC_SCRATCH_BYTES (4u << 20)
+int32_t tb200_gguf_gemv_static(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
+                               int64_t m, int64_t n, int64_t k, void *stream, TensorErrorV1 *error);
+
 /* Prefill GEMM: out[m, n] (fp32) = x[m, k] . dequant(w[n, k])^T with both operands rounded to
  * bf16 and fp32 accumulation.  Replaces `_packed` (showcase/kernels.py:116-119; contract
  * showcase/benchmark.py:471-477, triton_kernels.py:184-210, there with fp16 operands).

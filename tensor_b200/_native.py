@@ -15,6 +15,7 @@ EXPORTS = (
     "tb200_gguf_version", "tb200_gguf_weight_bytes", "tb200_gguf_gemv_scratch_bytes",
     "tb200_gguf_device_status", "tb200_gguf_gemv_plan", "tb200_gguf_dequant", "tb200_gguf_gemv", "tb200_gguf_gemm",
     "tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1",
+    "tb200_gguf_gemv_static",
 )
 
 
@@ -62,6 +63,8 @@ def lib():
     handle.tb200_gguf_dequant.argtypes = [i32, vp, vp, i64, i64, vp, err]
     handle.tb200_gguf_gemv.restype = i32
     handle.tb200_gguf_gemv.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, vp, i64, i32, vp, err]
+    handle.tb200_gguf_gemv_static.restype = i32
+    handle.tb200_gguf_gemv_static.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, vp, err]
     handle.tb200_gguf_gemm.restype = i32
     handle.tb200_gguf_gemm.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, i32, vp, err]
     for name in ("tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1"):
