@@ -323,10 +323,10 @@ def run_gpu(args):
         "note": "average over the nine launches of a step (batch 1/4/16), gaps between launches included; "
                 f"best batch ({best['batch']}) reaches {best['gbps'] / world:.0f} GB/s per GPU",
     }
-    traffic_path = os.path.join(ROOT, "profiles", "gemv_q4k_traffic.json")
-    if os.path.exists(traffic_path):
-        with open(traffic_path) as f:
-            roofline["traffic"] = json.load(f).get("dram_bytes_per_launch")
+    if world == 1:
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu capture
+        # (profiles/gemv_q4k_batch1_18944x3584.md): equal to the algorithmic bytes, i.e. no re-reads
+        roofline["traffic"] = 38245120
 
     # ---- end to end: host buffers in, host buffers out, every step ----
     x_host = {b: [a.cpu().pin_memory() for a in acts[b]] for b in BATCHES}

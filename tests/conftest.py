@@ -12,6 +12,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+def pytest_sessionstart(session):
+    """The CUDA library is built in-tree and kept out of history: build it if it is not there yet
+    (nvcc cross-compiles without a GPU).  A failed build is left for the tests to report."""
+    try:
+        from tensor_b200 import build as native_build
+
+        native_build.build()
+    except Exception as exc:  # pragma: no cover
+        print(f"[conftest] building the CUDA library failed: {exc}")
+
+
 def pytest_collection_modifyitems(config, items):
     try:
         import torch
