@@ -119,6 +119,16 @@ int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int6
 int32_t tb200_gguf_gemv_plan(int32_t format, int64_t m, int64_t n, int64_t k, int64_t scratch_bytes,
                              int32_t *plan_out);
 
+/* Launch constants for packaging a static-shape kernel as a `.tbin` artifact of the reference
+ * (src/tensor/artifacts/format.py), planned for a B200: the reference's provider launches with the
+ * manifest's grid / block / shared memory and passes only the declared buffers, so the plan is baked
+ * into the cubin.  gemv: out32 = {grid, threads, smem, k_splits, row_groups, row_tiles, sb_per_split,
+ * nsb, stages, ring / staging layout ..., scratch bytes, CTAs per SM, counter bytes};
+ * gemm: out8 = {grid.x, grid.y, threads, smem, token tile, k per stage, 0, 0}. */
+int32_t tb200_gguf_gemv_launch_config(int32_t format, int32_t x_dtype, int64_t m, int64_t n, int64_t k,
+                                      int64_t scratch_bytes, int32_t *out32);
+int32_t tb200_gguf_gemm_launch_config(int32_t format, int64_t m, int64_t n, int64_t k, int32_t *out8);
+
 /* Synchronises the current device and reads the sticky status words of the pipelined kernels.
  * Every device-side wait in this library is bounded (about two seconds); a wait that gives up
  * records a code there and the kernel returns instead of hanging.  Returns TENSOR_OK and

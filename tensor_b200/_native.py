@@ -13,7 +13,8 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libt
 #: every symbol include/tensor_b200_gguf.h declares
 EXPORTS = (
     "tb200_gguf_version", "tb200_gguf_weight_bytes", "tb200_gguf_gemv_scratch_bytes",
-    "tb200_gguf_device_status", "tb200_gguf_gemv_plan", "tb200_gguf_dequant", "tb200_gguf_gemv", "tb200_gguf_gemm",
+    "tb200_gguf_device_status", "tb200_gguf_gemv_plan", "tb200_gguf_gemv_launch_config",
+    "tb200_gguf_gemm_launch_config", "tb200_gguf_dequant", "tb200_gguf_gemv", "tb200_gguf_gemm",
     "tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1",
     "tb200_gguf_gemv_static",
 )
@@ -57,6 +58,10 @@ def lib():
     handle.tb200_gguf_gemv_scratch_bytes.argtypes = [i32, i64, i64, i64]
     handle.tb200_gguf_gemv_plan.restype = i32
     handle.tb200_gguf_gemv_plan.argtypes = [i32, i64, i64, i64, i64, ctypes.POINTER(ctypes.c_int32)]
+    handle.tb200_gguf_gemv_launch_config.restype = i32
+    handle.tb200_gguf_gemv_launch_config.argtypes = [i32, i32, i64, i64, i64, i64, ctypes.POINTER(ctypes.c_int32)]
+    handle.tb200_gguf_gemm_launch_config.restype = i32
+    handle.tb200_gguf_gemm_launch_config.argtypes = [i32, i64, i64, i64, ctypes.POINTER(ctypes.c_int32)]
     handle.tb200_gguf_device_status.restype = i32
     handle.tb200_gguf_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32), err]
     handle.tb200_gguf_dequant.restype = i32

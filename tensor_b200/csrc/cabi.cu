@@ -177,6 +177,31 @@ int32_t tb200_gguf_gemv_plan(int32_t format, int64_t m, int64_t n, int64_t k, in
   return TENSOR_OK;
 }
 
+int32_t tb200_gguf_gemv_launch_config(int32_t format, int32_t x_dtype, int64_t m, int64_t n, int64_t k,
+                                      int64_t scratch_bytes, int32_t* out32) {
+  if (!out32) return TENSOR_ERROR_ARGUMENT;
+  if (!valid_format(format) || m < 1 || n < 1 || k < 0 || k % block_weights(format)) return TENSOR_ERROR_ARGUMENT;
+  DeviceInfo b200;  // packaging usually happens on a machine without a GPU: plan for a B200
+  b200.ordinal = 0;
+  b200.sm_count = 148;
+  b200.max_smem_optin = 232448;
+  b200.cc_major = 10;
+  GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch_bytes, b200);
+  return gemv_launch_config(plan, format, m, n, k, out32) ? TENSOR_OK : TENSOR_ERROR_ARGUMENT;
+}
+
+int32_t tb200_gguf_gemm_launch_config(int32_t format, int64_t m, int64_t n, int64_t k, int32_t* out8) {
+  if (!out8) return TENSOR_ERROR_ARGUMENT;
+  DeviceInfo b200;
+  b200.ordinal = 0;
+  b200.sm_count = 148;
+  b200.max_smem_optin = 232448;
+  b200.cc_major = 10;
+  if (!gemm_fast_supported(format, m, n, k, b200)) return TENSOR_ERROR_ARGUMENT;
+  gemm_launch_config(m, n, out8);
+  return TENSOR_OK;
+}
+
 int32_t tb200_gguf_device_status(uint32_t* status, TensorErrorV1* error) {
   unsigned int a = 0, b = 0;
   cudaError_t e = cudaDeviceSynchronize();

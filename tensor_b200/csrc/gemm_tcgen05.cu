@@ -175,9 +175,9 @@ template <> struct Decoder<kQ6_K> {
 };
 
 template <int FMT>
-__global__ void __launch_bounds__(kThreads, 2)
-    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ w,
-                        float* __restrict__ out, int M, int N, int K, long long row_bytes_) {
+__device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, const uint8_t* __restrict__ w,
+                                                  float* __restrict__ out, int M, int N, int K,
+                                                  long long row_bytes_) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -309,7 +309,15 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
 }
 
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 2)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ w,
+                        float* __restrict__ out, int M, int N, int K, long long row_bytes_) {
+  gemm_tcgen05_body<FMT>(tmap_x, w, out, M, N, K, row_bytes_);
+}
+
 // ---- host side -------------------------------------------------------------------------------------
+#ifndef TB200_TBIN_WRAPPER
 
 template <int FMT>
 cudaError_t launch_fmt(const CUtensorMap& tmap, const uint8_t* w, float* out, long long m, long long n,
@@ -322,9 +330,26 @@ cudaError_t launch_fmt(const CUtensorMap& tmap, const uint8_t* w, float* out, lo
   return cudaGetLastError();
 }
 
+#endif  // TB200_TBIN_WRAPPER
 }  // namespace
 
+// static-shape entry used by generated .tbin wrappers
+constexpr int kGemmThreads = kThreads;
+template <int FMT>
+__device__ __forceinline__ void gemm_static_entry(const CUtensorMap& x, const uint8_t* w, float* out, int m, int n,
+                                                  int k) {
+  gemm_tcgen05_body<FMT>(x, w, out, m, n, k, row_bytes(FMT, k));
+}
+
+#ifndef TB200_TBIN_WRAPPER
 TB200_DEFINE_STATUS_READER(read_gemm_status)
+
+void gemm_launch_config(long long m, long long n, int* out8) {
+  const int vals[8] = {(int)((m + kTileTok - 1) / kTileTok), (int)((n + kTileN - 1) / kTileN), kThreads, kSmemBytes,
+                       kTileTok, kBlockK, 0, 0};
+  for (int i = 0; i < 8; ++i) out8[i] = vals[i];
+}
+
 
 bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const DeviceInfo& dev) {
   if (fmt != kQ4_K && fmt != kQ6_K) return false;
@@ -352,5 +377,6 @@ cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* ou
   }
   return cudaErrorInvalidValue;
 }
+#endif  // TB200_TBIN_WRAPPER
 
 }  // namespace tb200

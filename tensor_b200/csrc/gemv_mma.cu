@@ -438,8 +438,7 @@ __device__ __forceinline__ void q4k_item_groups(const SmemMap& sm, uint32_t stag
 }
 
 template <int FMT, bool F16, int NT, bool GROUPS>
-__global__ void __launch_bounds__(kThreads, 2)
-    gemv_mma_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap) {
+__device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorMap* wmap) {
   static_assert(FMT == kQ4_K, "only Q4_K is pipelined so far");
   constexpr int NTB = GROUPS ? 1 : NT * 8;
   constexpr int kBlockBytes = Fmt<FMT>::kBytes;
@@ -504,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         // super-blocks past K arrive as zeros, and count towards the transaction bytes)
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)(kTileRows * a.stride_s));
-          ptx::tma_load_2d(dst, &wmap, sb0 * (kBlockBytes / 8), (int)row0, &full[s]);
+          ptx::tma_load_2d(dst, wmap, sb0 * (kBlockBytes / 8), (int)row0, &full[s]);
         }
       } else {
         if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
@@ -728,6 +727,12 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
 }
 
+template <int FMT, bool F16, int NT, bool GROUPS>
+__global__ void __launch_bounds__(kThreads, 2)
+    gemv_mma_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap) {
+  gemv_mma_body<FMT, F16, NT, GROUPS>(a, &wmap);
+}
+
 inline int round_up(int v, int to) { return (v + to - 1) / to * to; }
 inline int groups_limit(int slots, int splits) { return slots / splits; }
 // a tiled copy with 8-byte elements covers at most 256 elements = 2048 bytes per row
@@ -773,6 +778,50 @@ Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed) {
 
 }  // namespace
 
+// ---- static-shape entry used by generated .tbin wrappers ------------------------------------------
+// A .tbin kernel is launched by the reference's provider with nothing but its declared buffers, so
+// the launch plan is baked in as constants (GemvStatic) by the packaging step.
+constexpr int kGemvThreads = kThreads;
+struct GemvStatic {
+  int nsb, sb_per_split, k_splits, row_groups, row_tiles, stages, stride_s, xs_stride;
+  int off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc, contiguous, use_tma, consumer_warps;
+};
+template <int FMT, bool F16, int NT, bool GROUPS>
+__device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const void* x, const uint8_t* w,
+                                                  const CUtensorMap* wmap, float* out, unsigned char* scratch,
+                                                  int m, long long n, int k, int counter_bytes) {
+  GemvArgs a;
+  a.x = x;
+  a.w = w;
+  a.out = out;
+  a.counters = reinterpret_cast<unsigned int*>(scratch);
+  a.partials = reinterpret_cast<float*>(scratch + counter_bytes);
+  a.m = m;
+  a.n = n;
+  a.k = k;
+  a.row_bytes = row_bytes(FMT, k);
+  a.nsb = s.nsb;
+  a.sb_per_split = s.sb_per_split;
+  a.k_splits = s.k_splits;
+  a.row_groups = s.row_groups;
+  a.row_tiles = s.row_tiles;
+  a.stages = s.stages;
+  a.stride_s = s.stride_s;
+  a.xs_stride = s.xs_stride;
+  a.off_stage = s.off_stage;
+  a.off_xs = s.off_xs;
+  a.off_sx = s.off_sx;
+  a.off_red = s.off_red;
+  a.off_scl = s.off_scl;
+  a.off_zero = s.off_zero;
+  a.off_misc = s.off_misc;
+  a.contiguous = s.contiguous;
+  a.use_tma = s.use_tma;
+  a.consumer_warps = s.consumer_warps;
+  gemv_mma_body<FMT, F16, NT, GROUPS>(a, wmap);
+}
+
+#ifndef TB200_TBIN_WRAPPER
 TB200_DEFINE_STATUS_READER(read_gemv_status)
 
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
@@ -852,14 +901,49 @@ static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t 
   return cudaGetLastError();
 }
 
+static int fill_args(GemvArgs& a, const GemvPlan& plan, int fmt, long long m, long long n, long long k);
+
+bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n, long long k, int* out32) {
+  if (!plan.supported || fmt != kQ4_K) return false;
+  GemvArgs a{};
+  const int smem = fill_args(a, plan, fmt, m, n, k);
+  const int vals[] = {plan.k_splits * plan.row_groups, kThreads, smem, a.k_splits, a.row_groups, a.row_tiles,
+                      a.sb_per_split, a.nsb, a.stages, a.stride_s, a.xs_stride, a.off_stage, a.off_xs, a.off_sx,
+                      a.off_red, a.off_scl, a.off_zero, a.off_misc, a.contiguous, a.use_tma, a.consumer_warps,
+                      (int)(plan.scratch_bytes > 0x7fffffff ? 0x7fffffff : plan.scratch_bytes), plan.ctas_per_sm,
+                      kCounterBytes};
+  for (int i = 0; i < 32; ++i) out32[i] = i < (int)(sizeof(vals) / sizeof(int)) ? vals[i] : 0;
+  return true;
+}
+
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              float* out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream) {
   if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
   GemvArgs a{};
+  const int smem_total = fill_args(a, plan, fmt, m, n, k);
   a.x = x;
   a.w = w;
   a.out = out;
+  if (plan.k_splits > 1) {
+    if (!scratch) return cudaErrorInvalidValue;
+    a.counters = static_cast<unsigned int*>(scratch);
+    a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kCounterBytes);
+  }
+  const int grid = plan.k_splits * plan.row_groups;
+  const bool f16 = xt == kF16;
+  if (m == 1)
+    return f16 ? launch_variant<kQ4_K, true, 1, true>(a, grid, smem_total, stream)
+               : launch_variant<kQ4_K, false, 1, true>(a, grid, smem_total, stream);
+  if (m <= 8)
+    return f16 ? launch_variant<kQ4_K, true, 1, false>(a, grid, smem_total, stream)
+               : launch_variant<kQ4_K, false, 1, false>(a, grid, smem_total, stream);
+  return f16 ? launch_variant<kQ4_K, true, 2, false>(a, grid, smem_total, stream)
+             : launch_variant<kQ4_K, false, 2, false>(a, grid, smem_total, stream);
+}
+
+// Everything of GemvArgs that follows from the plan and the shape; returns the dynamic shared memory.
+static int fill_args(GemvArgs& a, const GemvPlan& plan, int fmt, long long m, long long n, long long k) {
   a.m = (int)m;
   a.n = n;
   a.k = (int)k;
@@ -883,32 +967,20 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.off_scl = L.off_scl;
   a.off_zero = L.off_zero;
   a.off_misc = L.off_misc;
-  {
-    // as many decode warps as divide the super-blocks of a K range most evenly (ties: more warps)
-    int best_w = kMaxConsumerWarps;
-    double best_eff = 0;
-    for (int w = kMaxConsumerWarps; w >= 4; --w) {
-      const int rounds = (plan.sb_per_split + w - 1) / w;
-      const double eff = (double)plan.sb_per_split / (rounds * w) * (0.9 + 0.1 * w / kMaxConsumerWarps);
-      if (eff > best_eff + 1e-9) { best_eff = eff; best_w = w; }
+  // as many decode warps as divide the super-blocks of a K range most evenly (ties: more warps)
+  int best_w = kMaxConsumerWarps;
+  double best_eff = 0;
+  for (int w = kMaxConsumerWarps; w >= 4; --w) {
+    const int rounds = (plan.sb_per_split + w - 1) / w;
+    const double eff = (double)plan.sb_per_split / (rounds * w) * (0.9 + 0.1 * w / kMaxConsumerWarps);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best_w = w;
     }
-    a.consumer_warps = best_w;
   }
-  if (plan.k_splits > 1) {
-    if (!scratch) return cudaErrorInvalidValue;
-    a.counters = static_cast<unsigned int*>(scratch);
-    a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kCounterBytes);
-  }
-  const int grid = plan.k_splits * plan.row_groups;
-  const bool f16 = xt == kF16;
-  if (m == 1)
-    return f16 ? launch_variant<kQ4_K, true, 1, true>(a, grid, L.total, stream)
-               : launch_variant<kQ4_K, false, 1, true>(a, grid, L.total, stream);
-  if (m <= 8)
-    return f16 ? launch_variant<kQ4_K, true, 1, false>(a, grid, L.total, stream)
-               : launch_variant<kQ4_K, false, 1, false>(a, grid, L.total, stream);
-  return f16 ? launch_variant<kQ4_K, true, 2, false>(a, grid, L.total, stream)
-             : launch_variant<kQ4_K, false, 2, false>(a, grid, L.total, stream);
+  a.consumer_warps = best_w;
+  return L.total;
 }
+#endif  // TB200_TBIN_WRAPPER
 
 }  // namespace tb200

@@ -37,11 +37,15 @@ struct GemvPlan {
 };
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
                         long long scratch_bytes_available, const DeviceInfo& dev);
+// All launch constants of a plan (grid, threads, shared memory, ring layout ...): see tbin.py.
+bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n, long long k, int* out32);
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              float* out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream);
 
 // tcgen05 / TMEM prefill GEMM (bf16 operands, fp32 accumulate).
+// {grid.x, grid.y, threads, dynamic shared memory, token tile, k per stage, 0, 0}
+void gemm_launch_config(long long m, long long n, int* out8);
 bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const DeviceInfo& dev);
 cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m,
                              long long n, long long k, cudaStream_t stream, const char** detail);

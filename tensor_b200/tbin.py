@@ -155,6 +155,7 @@ def build_gemv_tbin(path: str, encoding, m: int, n: int, k: int, x_dtype: str = 
         "off_stage", "off_xs", "off_sx", "off_red", "off_scl", "off_zero", "off_misc", "contiguous", "use_tma",
         "consumer_warps"))
     source = f"""// generated by tensor_b200.tbin: Q-format {fmt.name}, m={m}, n={n}, k={k}, x={x_dtype}
+#define TB200_TBIN_WRAPPER
 #include "gemv_mma.cu"
 extern "C" __global__ void __launch_bounds__(tb200::kGemvThreads, {cfg['ctas_per_sm']})
 kernel_kernel(const void* x, {wparam}, float* out{', unsigned char* scratch' if split else ''}) {{
@@ -193,6 +194,7 @@ def build_gemm_tbin(path: str, encoding, m: int, n: int, k: int) -> dict:
         raise ValueError(f"the tcgen05 GEMM does not cover {fmt.name} m={m} n={n} k={k}")
     grid_x, grid_y, threads, smem, tile_tok, block_k = (int(v) for v in cfg[:6])
     source = f"""// generated by tensor_b200.tbin: {fmt.name} GEMM, m={m}, n={n}, k={k}
+#define TB200_TBIN_WRAPPER
 #include "gemm_tcgen05.cu"
 extern "C" __global__ void __launch_bounds__(tb200::kGemmThreads, 2)
 kernel_kernel(const __grid_constant__ CUtensorMap x, const uint8_t* w, float* out) {{
