@@ -405,10 +405,16 @@ def run_gpu(args):
             "value": rate, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"the same nine GEMVs as a GPU step, {n_steps} passes, median {med * 1e3:.1f} ms per pass"}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # Every collective of this run has completed on every rank (the last one returned a value to
+        # the host).  Tearing the NCCL communicator down while CUDA graphs that captured its kernels
+        # are alive was seen to block, so drop the graphs first and leave without the teardown.
+        graphs.clear()
+        torch.cuda.synchronize(device)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
