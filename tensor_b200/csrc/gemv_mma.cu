@@ -449,6 +449,8 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   uint64_t* red_full = cbar + 1;        // [2] consumers -> reducer: partial sums of a tile are in place
   uint64_t* red_empty = red_full + 2;   // [2] reducer -> consumers: buffer may be overwritten
   uint64_t* xbar = red_empty + 2;       // activation rows have landed in shared memory
+  uint64_t* fin = xbar + 1;             // reducer -> consumers: verdict on who adds the K ranges
+  __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int W = a.consumer_warps;
@@ -470,6 +472,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     }
     ptx::mbar_init(cbar, W);
     ptx::mbar_init(xbar, 1);
+    ptx::mbar_init(fin, 1);
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&red_full[b], W);
       ptx::mbar_init(&red_empty[b], 1);
@@ -478,6 +481,42 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   }
   if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(smem + a.off_zero)[threadIdx.x] = 0u;
   __syncthreads();
+
+  // K split over CTAs: the last CTA of a group to finish adds every K range's partial sums, in K
+  // order (deterministic).  Work items = (row tile of the group, column, 4 consecutive rows), spread
+  // over all helper lanes (consumer warps + reducer) so many independent 16-byte loads are in flight.
+  auto add_partials = [&](int helper, int helpers) {
+    __threadfence();
+    const long long plane = (long long)a.m * a.n;
+    const int my_tiles = (a.row_tiles - rg + a.row_groups - 1) / a.row_groups;
+    const int per_tile = a.m * 4;
+    const bool vec = (a.n & 3) == 0;
+    for (int item = helper * 32 + lane; item < my_tiles * per_tile; item += helpers * 32) {
+      const int t = item / per_tile, rem = item - t * per_tile;
+      const int col = rem >> 2, r4 = (rem & 3) * 4;
+      const long long grow = ((long long)rg + (long long)t * a.row_groups) * kTileRows + r4;
+      if (grow >= a.n) continue;
+      const long long idx = (long long)col * a.n + grow;
+      if (vec) {
+        float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int q = 0; q < a.k_splits; ++q) {
+          const float4 p = __ldcg(reinterpret_cast<const float4*>(&a.partials[q * plane + idx]));
+          tot.x += p.x;
+          tot.y += p.y;
+          tot.z += p.z;
+          tot.w += p.w;
+        }
+        *reinterpret_cast<float4*>(&a.out[idx]) = tot;
+      } else {
+        for (int r = 0; r < 4 && grow + r < a.n; ++r) {
+          float total = 0.f;
+          for (int q = 0; q < a.k_splits; ++q) total += __ldcg(&a.partials[q * plane + idx + r]);
+          a.out[idx + r] = total;
+        }
+      }
+    }
+  };
 
   if (warp == kProducerWarp) {
     // ---------------- producer: bulk copies of the tile's weight rows ----------------
@@ -567,40 +606,12 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
         if (last) a.counters[rg] = 0u;  // every other K range has already arrived: ready for the next call
       }
       last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence();
-        // Work items = (row tile of this CTA group, column, 4 consecutive rows), spread over the
-        // lanes so that many independent 16-byte loads are in flight; each adds the K ranges in order.
-        const long long plane = (long long)a.m * a.n;
-        const int my_tiles = (a.row_tiles - rg + a.row_groups - 1) / a.row_groups;
-        const int per_tile = a.m * 4;
-        const bool vec = (a.n & 3) == 0;
-        for (int item = lane; item < my_tiles * per_tile; item += 32) {
-          const int t = item / per_tile, rem = item - t * per_tile;
-          const int col = rem >> 2, r4 = (rem & 3) * 4;
-          const long long grow = ((long long)rg + (long long)t * a.row_groups) * kTileRows + r4;
-          if (grow >= a.n) continue;
-          const long long idx = (long long)col * a.n + grow;
-          if (vec) {
-            float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-            for (int q = 0; q < a.k_splits; ++q) {
-              const float4 p = __ldcg(reinterpret_cast<const float4*>(&a.partials[q * plane + idx]));
-              tot.x += p.x;
-              tot.y += p.y;
-              tot.z += p.z;
-              tot.w += p.w;
-            }
-            *reinterpret_cast<float4*>(&a.out[idx]) = tot;
-          } else {
-            for (int r = 0; r < 4 && grow + r < a.n; ++r) {
-              float total = 0.f;
-              for (int q = 0; q < a.k_splits; ++q) total += __ldcg(&a.partials[q * plane + idx + r]);
-              a.out[idx + r] = total;
-            }
-          }
-        }
+      if (lane == 0) {
+        s_last = (int)last;
+        __threadfence_block();
+        ptx::mbar_arrive(fin);  // the consumer warps are waiting for the verdict
       }
+      if (last) add_partials(W, W + 1);
     }
     return;
   }
@@ -724,6 +735,13 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       s = 0;
       phase ^= 1;
     }
+  }
+  if (a.k_splits > 1) {
+    if (!ptx::mbar_wait(fin, 0)) {
+      report_timeout(0x70000u);
+      return;
+    }
+    if (*reinterpret_cast<volatile int*>(&s_last)) add_partials(cw, W + 1);
   }
 }
 
