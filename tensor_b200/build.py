@@ -66,6 +66,10 @@ def _compile(name: str) -> tuple[str, str]:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    if os.environ.get("TB200_GEMV_TRACE"):
+        # diagnostic build: the GEMV records a per-CTA timeline and prints it at process exit
+        if "-DTB200_GEMV_TRACE" not in COMMON:
+            COMMON.append("-DTB200_GEMV_TRACE")
     os.makedirs(LIB_DIR, exist_ok=True)
     stamp = os.path.join(LIB_DIR, "build.sha256")
     fp = _fingerprint()

@@ -24,6 +24,8 @@
 //    last CTA to arrive for a row tile adds them in a fixed order (deterministic).
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -33,10 +35,13 @@
 namespace tb200 {
 namespace {
 
-constexpr int kMaxConsumerWarps = 8;
-constexpr int kProducerWarp = kMaxConsumerWarps;     // streams weights into the ring
-constexpr int kReducerWarp = kMaxConsumerWarps + 1;  // adds the consumer warps' partial sums, writes out
-constexpr int kThreads = (kMaxConsumerWarps + 2) * 32;
+// Warp roles: warps 0 .. W-1 decode (W = consumer_warps, chosen per plan), warp W streams weights
+// into the ring, warp W+1 adds the decode warps' partial sums and writes out.  Plans with two CTAs
+// per SM use up to 8 decode warps, plans with one CTA per SM up to 16.
+constexpr int kMaxConsumerWarps = 16;
+constexpr int kNarrowWarps = 8;
+constexpr int kThreadsNarrow = (kNarrowWarps + 2) * 32;
+constexpr int kThreadsWide = (kMaxConsumerWarps + 2) * 32;
 constexpr int kTileRows = 16;
 constexpr int kMaxStages = 8;
 constexpr int kCounterBytes = 4096;  // one arrival counter per group of CTAs that share row tiles (<= 1024)
@@ -61,7 +66,11 @@ struct GemvArgs {
   int stride_s;   // shared-memory bytes between the rows of a stage
   int xs_stride;  // shared-memory bytes between staged activation rows
   int off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc;
-  int consumer_warps;  // warps that decode (<= 8), chosen to divide the super-blocks of a K range evenly
+  int consumer_warps;  // warps that decode, chosen to divide the super-blocks of a K range evenly
+#ifdef TB200_GEMV_TRACE
+  unsigned long long* trace;  // diagnostic timeline (only in trace builds)
+#endif
+  int red_bufs;        // 2: partial-sum buffers alternate between tiles; 1: a single buffer (shared memory is tight)
   int contiguous;  // one bulk copy per tile (K not split): stage rows are packed like global rows
   int use_tma;     // K split: one 2-D tiled TMA copy per tile (16 rows x the K range)
 };
@@ -99,97 +108,109 @@ __device__ __forceinline__ uint4 to_f16x8(uint4 v, float scale) {
 
 __device__ __forceinline__ float sum_f16x8(uint4 v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  float s = 0.f;
+  float part[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    s += f.x;
-    s += f.y;
+    part[i] = f.x + f.y;
   }
-  return s;
+  return (part[0] + part[1]) + (part[2] + part[3]);
 }
 
 // Batch staging (1 < m <= 16): the activation rows of this CTA's K range are fetched with bulk
-// async copies (one per row, a single round trip to L2 / HBM), then converted in place to fp16:
-// each aligned group of four values is stored as [x0, x2, x1, x3] so that an MMA B fragment is one
-// contiguous load, and the per-32-group sums Sx[g][b] of the staged values are kept in fp32.  bf16
-// inputs are scaled by one power of two per CTA so that the largest magnitude lands in
-// [2^14, 2^15): the conversion is then exact for every value within 2^-32 of the largest, and the
-// result is scaled back at the end.  Returns the factor that undoes the scaling.
-template <bool F16, int NTB, typename Sync>
-__device__ __forceinline__ float stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0,
-                                                   int klen, uint64_t* xbar, Sync&& consumer_sync, bool& ok) {
-  const int kConsumerThreads = a.consumer_warps * 32;
+// async copies (one per row, a single round trip to L2 / HBM), then converted in place to fp16 in
+// one pass: each aligned group of four values is stored as [x0, x2, x1, x3] so that an MMA B
+// fragment is one contiguous load.  Every 32-value scale group of every row gets its own power of
+// two (largest magnitude -> [2^14, 2^15)), so bf16 -> fp16 is exact for every value within 2^-32 of
+// the group's largest; sxu[g][b] = {sum of the staged fp16 values, factor that undoes the scaling}.
+template <bool F16, int NTB>
+__device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* smem, int ctid, int k0, int klen,
+                                                  uint64_t* xbar) {
+  const int threads = a.consumer_warps * 32;
   const int chunks = klen >> 3;  // 8 values (16 bytes) each; a multiple of 32
   const int total = NTB * chunks;
   uint8_t* xs = smem + a.off_xs;
-  float* sx = reinterpret_cast<float*>(smem + a.off_sx);
-  uint32_t* wmax = reinterpret_cast<uint32_t*>(smem + a.off_red);  // reused before the main loop
-  const uint16_t* xg = static_cast<const uint16_t*>(a.x);
-  const uint32_t row_bytes_x = (uint32_t)klen * 2;
-  if (ctid == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * row_bytes_x);
-  __syncwarp();
-  if (ctid < a.m) ptx::bulk_g2s(xs + (size_t)ctid * a.xs_stride, xg + (long long)ctid * a.k + k0, row_bytes_x, xbar);
-  // rows beyond m are zero
-  for (int idx = a.m * chunks + ctid; idx < total; idx += kConsumerThreads) {
+  float2* sxu = reinterpret_cast<float2*>(smem + a.off_sx);
+  // rows beyond m are zero, with zero group sums (done while the copies are in flight)
+  for (int idx = a.m * chunks + ctid; idx < total; idx += threads) {
     const int b = idx / chunks, c = idx - b * chunks;
     *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = make_uint4(0, 0, 0, 0);
+    if ((c & 3) == 0) sxu[(c >> 2) * NTB + b] = make_float2(0.f, 1.f);
   }
-  if (!ptx::mbar_wait(xbar, 0)) {
+  if (!ptx::mbar_wait(xbar, 0)) {  // the producer warp issued the row copies before any weight copy
     report_timeout(0x60000u);
-    ok = false;
-    return 1.f;
+    return false;
   }
-  float scale = 1.f, unscale = 1.f;
-  if constexpr (!F16) {
-    uint32_t mx = 0;
-    for (int idx = ctid; idx < a.m * chunks; idx += kConsumerThreads) {
-      const int b = idx / chunks, c = idx - b * chunks;
-      const uint4 v = *reinterpret_cast<const uint4*>(xs + (size_t)b * a.xs_stride + (c << 4));
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#ifdef TB200_GEMV_TRACE
+  if (a.trace && blockIdx.x == 0 && ctid == 0) a.trace[2] = ptx::global_timer_ns();
+#endif
+  // rows < m: convert in place.  Thread t walks chunks t, t + threads, ... of the flattened
+  // (row, chunk) space, four at a time so that four independent dependency chains (load, quad
+  // shuffles, convert, sum, store) overlap; trip counts are uniform, so the shuffles are warp-wide.
+  const int live = a.m * chunks;
+  const uint32_t xs_s = ptx::smem_addr(xs), sxu_s = ptx::smem_addr(sxu);
+  constexpr int U = 4;
+  int b = ctid / chunks, c = ctid - b * chunks;
+  for (int base = 0; base < live; base += U * threads) {
+#ifdef TB200_GEMV_TRACE
+    if (a.trace && blockIdx.x == 0 && ctid == 0 && base / (U * threads) < 4) a.trace[3 + base / (U * threads)] = ptx::global_timer_ns();
+#endif
+    uint32_t slot[U];
+    int cc[U], bb[U];
+    bool valid[U];
+    uint4 v[U];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+    for (int u = 0; u < U; ++u) {
+      valid[u] = base + u * threads + ctid < live;
+      cc[u] = c;
+      bb[u] = b;
+      slot[u] = xs_s + (uint32_t)b * a.xs_stride + (c << 4);
+      v[u] = valid[u] ? ptx::lds128(slot[u]) : make_uint4(0, 0, 0, 0);
+      c += threads;
+      while (c >= chunks) {
+        c -= chunks;
+        ++b;
+      }
+    }
+    float unscale[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float scale = 1.f;
+      unscale[u] = 1.f;
+      if constexpr (!F16) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        uint32_t mx = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const int e = (int)(mx >> 7);  // biased bf16 exponent of the group's largest magnitude
+        if (e > 0 && e < 255) {
+          int sh = 141 - e;
+          sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+          scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+          unscale[u] = __uint_as_float((uint32_t)(127 - sh) << 23);
+        }
+      }
+      v[u] = to_f16x8<F16>(v[u], scale);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((ctid & 31) == 0) wmax[ctid >> 5] = mx;
-    ok = consumer_sync();
-    if (!ok) return 1.f;
-#pragma unroll
-    for (int i = 0; i < kMaxConsumerWarps; ++i)
-      if (i < a.consumer_warps) mx = max(mx, wmax[i]);
-    const int e = (int)(mx >> 7);  // biased bf16 exponent of the largest magnitude
-    if (e > 0 && e < 255) {
-      int sh = 141 - e;  // largest -> [2^14, 2^15)
-      sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
-      scale = __uint_as_float((uint32_t)(sh + 127) << 23);
-      unscale = __uint_as_float((uint32_t)(127 - sh) << 23);
-    }
-    ok = consumer_sync();  // wmax is free again
-    if (!ok) return 1.f;
-  }
-  for (int base = 0; base < total; base += kConsumerThreads) {
-    const int idx = base + ctid;
-    const bool valid = idx < total;
-    const int b = valid ? idx / chunks : 0;
-    const int c = valid ? idx - b * chunks : 0;
-    uint4* slot = reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4));
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (valid) v = to_f16x8<F16>(*slot, scale);
-    float s = sum_f16x8(v);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    if (valid) {
-      uint4 p;
-      p.x = __byte_perm(v.x, v.y, 0x5410);
-      p.y = __byte_perm(v.x, v.y, 0x7632);
-      p.z = __byte_perm(v.z, v.w, 0x5410);
-      p.w = __byte_perm(v.z, v.w, 0x7632);
-      *slot = p;
-      if ((c & 3) == 0) sx[(c >> 2) * NTB + b] = s;
+    for (int u = 0; u < U; ++u) {
+      float sum = sum_f16x8(v[u]);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (valid[u]) {
+        uint4 p;
+        p.x = __byte_perm(v[u].x, v[u].y, 0x5410);
+        p.y = __byte_perm(v[u].x, v[u].y, 0x7632);
+        p.z = __byte_perm(v[u].z, v[u].w, 0x5410);
+        p.w = __byte_perm(v[u].z, v[u].w, 0x7632);
+        ptx::sts128(slot[u], p);
+        if ((cc[u] & 3) == 0) ptx::sts64f(sxu_s + (((cc[u] >> 2) * NTB + bb[u]) << 3), sum, unscale[u]);
+      }
     }
   }
-  return unscale;
+  return true;
 }
 
 // m == 1 staging: one pass, no CTA-wide reduction.  Each 32-value scale group gets its own power of
@@ -321,7 +342,7 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
   const uint32_t rowB = rowA + 8 * sm.stride_s;
   const uint32_t sclA = sm.scl + gid * (kSclRowFloats * 4), sclB = sclA + 8 * (kSclRowFloats * 4);
   const uint32_t xrow = sm.xs + gid * sm.xs_stride + ((sbl * 256 + 8 * tig) << 1);
-  const uint32_t sxp = sm.sx + ((sbl * 8) * NTB + 2 * tig) * 4;
+  const uint32_t sxp = sm.sx + ((sbl * 8) * NTB + 2 * tig) * 8;
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
@@ -345,15 +366,13 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
           ptx::mma16816<true>(c, ax.hi02, bx.hi02, ax.hi13, bx.hi13, xb.x, xb.y, zero);
           ptx::mma16816<true>(c, ay.hi02, by.hi02, ay.hi13, by.hi13, xb.z, xb.w, c);
         }
-        const float2 sxv = ptx::lds64f(sxp + (g * NTB + 8 * t) * 4);
-        acc[t][0] = fmaf(sA.x, c[0], acc[t][0]);
-        acc[t][1] = fmaf(sA.x, c[1], acc[t][1]);
-        acc[t][2] = fmaf(sB.x, c[2], acc[t][2]);
-        acc[t][3] = fmaf(sB.x, c[3], acc[t][3]);
-        acc[t][0] = fmaf(-sA.y, sxv.x, acc[t][0]);
-        acc[t][1] = fmaf(-sA.y, sxv.y, acc[t][1]);
-        acc[t][2] = fmaf(-sB.y, sxv.x, acc[t][2]);
-        acc[t][3] = fmaf(-sB.y, sxv.y, acc[t][3]);
+        const uint4 su = ptx::lds128(sxp + (g * NTB + 8 * t) * 8);  // {Sx, u} of columns 2*tig, 2*tig+1
+        const float sx0 = __uint_as_float(su.x), u0 = __uint_as_float(su.y);
+        const float sx1 = __uint_as_float(su.z), u1 = __uint_as_float(su.w);
+        acc[t][0] = fmaf(u0, fmaf(sA.x, c[0], -sA.y * sx0), acc[t][0]);
+        acc[t][1] = fmaf(u1, fmaf(sA.x, c[1], -sA.y * sx1), acc[t][1]);
+        acc[t][2] = fmaf(u0, fmaf(sB.x, c[2], -sB.y * sx0), acc[t][2]);
+        acc[t][3] = fmaf(u1, fmaf(sB.x, c[3], -sB.y * sx1), acc[t][3]);
       }
     }
   }
@@ -480,6 +499,15 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     ptx::fence_mbar_init();
   }
   if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(smem + a.off_zero)[threadIdx.x] = 0u;
+#ifdef TB200_GEMV_TRACE
+  // slots per traced CTA (blockIdx % 100 == 0): 0 start, 1 staged, 8+i tile data ready, 24+i tile decoded,
+  // 40+i tile reduced, 56+i tile copy issued
+  unsigned long long* trace = (a.trace && blockIdx.x % 100 == 0) ? a.trace + (blockIdx.x / 100) * 80 : nullptr;
+  if (trace && threadIdx.x == 0) trace[0] = ptx::global_timer_ns();
+#define TB200_TRACE(cond, slot) do { if (trace && (cond) && (slot) < 80) trace[slot] = ptx::global_timer_ns(); } while (0)
+#else
+#define TB200_TRACE(cond, slot) do { } while (0)
+#endif
   __syncthreads();
 
   // K split over CTAs: the last CTA of a group to finish adds every K range's partial sums, in K
@@ -518,9 +546,19 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     }
   };
 
-  if (warp == kProducerWarp) {
+  if (warp == W) {
     // ---------------- producer: bulk copies of the tile's weight rows ----------------
     const uint8_t* src0 = a.w + (long long)sb0 * kBlockBytes;
+    if constexpr (!GROUPS) {
+      // the activation rows go first: the decode warps cannot start before they have landed, and
+      // copies queue in issue order
+      const uint32_t x_row_bytes = (uint32_t)nsb_local * 512;
+      if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes);
+      __syncwarp();
+      if (lane < a.m)
+        ptx::bulk_g2s(smem + a.off_xs + (size_t)lane * a.xs_stride,
+                      static_cast<const uint16_t*>(a.x) + (long long)lane * a.k + sb0 * 256, x_row_bytes, xbar);
+    }
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int s = i % S;
@@ -531,6 +569,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       const long long row0 = (long long)rt * kTileRows;
       const int rows = (int)min((long long)kTileRows, a.n - row0);
       uint8_t* dst = smem + a.off_stage + (size_t)s * kTileRows * a.stride_s;
+      TB200_TRACE(lane == 0 && i < 16, 56 + i);
       if (a.contiguous) {
         // the K range is the whole row and rows are packed back to back: one copy per tile
         if (lane == 0) {
@@ -554,44 +593,58 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     return;
   }
 
-  if (warp == kReducerWarp) {
+  if (warp == W + 1) {
     // ---------------- reducer: sum the consumer warps' partials in warp order, write out ----------------
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
-      const int b = i & 1;
-      if (!ptx::mbar_wait(&red_full[b], (i >> 1) & 1)) {
+      const int b = a.red_bufs == 2 ? (i & 1) : 0;
+      const int use = a.red_bufs == 2 ? (i >> 1) : i;
+      if (!ptx::mbar_wait(&red_full[b], use & 1)) {
         report_timeout(0x40000u | (unsigned)b);
         return;
       }
       const float unscale = *unscale_slot;
-      const float* buf = red + b * red_per_buf;
-      float vals[kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1];
-      bool mine[kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1];
-      long long gidx[kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1];
-      constexpr int kPerLane = kRedPerWarp / 32 > 0 ? kRedPerWarp / 32 : 1;
+      // Four consecutive rows of one column per lane and step: 16-byte shared loads, independent
+      // across steps, added in warp order.
+      const float4* buf4 = reinterpret_cast<const float4*>(red + b * red_per_buf);
+      constexpr int kQuads = kRedPerWarp / 4;                 // float4 per warp partial
+      constexpr int kPerLane = (kQuads + 31) / 32;
+      float4 sum[kPerLane];
 #pragma unroll
-      for (int j = 0; j < kPerLane; ++j) {
-        const int e = lane + 32 * j;  // (column e / 16, row e % 16)
-        const int row = e & 15, col = e >> 4;
-        const long long grow = (long long)rt * kTileRows + row;
-        mine[j] = e < kRedPerWarp && col < a.m && grow < a.n;
-        gidx[j] = (long long)col * a.n + grow;
-        float v = 0.f;
-        if (e < kRedPerWarp)
-          for (int w8 = 0; w8 < W; ++w8) v += buf[w8 * kRedPerWarp + e];
-        vals[j] = v * unscale;
+      for (int j = 0; j < kPerLane; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int w8 = 0; w8 < W; ++w8) {
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+          const int f = lane + 32 * j;
+          if (f < kQuads) {
+            const float4 p = buf4[w8 * kQuads + f];
+            sum[j].x += p.x;
+            sum[j].y += p.y;
+            sum[j].z += p.z;
+            sum[j].w += p.w;
+          }
+        }
       }
       __syncwarp();
+      TB200_TRACE(lane == 0 && i < 16, 40 + i);
       if (lane == 0) ptx::mbar_arrive(&red_empty[b]);  // partials are in registers now
-      if (a.k_splits == 1) {
+      float* dst = a.k_splits == 1 ? a.out : a.partials + (long long)ks * a.m * a.n;
+      const bool vec = (a.n & 3) == 0;
 #pragma unroll
-        for (int j = 0; j < kPerLane; ++j)
-          if (mine[j]) a.out[gidx[j]] = vals[j];
-      } else {
-        const long long plane = (long long)a.m * a.n;
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j)
-          if (mine[j]) a.partials[ks * plane + gidx[j]] = vals[j];
+      for (int j = 0; j < kPerLane; ++j) {
+        const int f = lane + 32 * j;  // (column f / 4, rows 4 * (f % 4) ..)
+        const int col = f >> 2, r4 = (f & 3) * 4;
+        const long long grow = (long long)rt * kTileRows + r4;
+        if (f >= kQuads || col >= a.m || grow >= a.n) continue;
+        const float4 v = make_float4(sum[j].x * unscale, sum[j].y * unscale, sum[j].z * unscale, sum[j].w * unscale);
+        float* p = dst + (long long)col * a.n + grow;
+        if (vec) {
+          *reinterpret_cast<float4*>(p) = v;
+        } else {
+          const float e[4] = {v.x, v.y, v.z, v.w};
+          for (int r = 0; r < 4 && grow + r < a.n; ++r) p[r] = e[r];
+        }
       }
     }
     if (a.k_splits > 1) {
@@ -634,13 +687,11 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     stage_activations_groups<F16>(a, smem, ctid, sb0 * 256, nsb_local * 256);
     if (ctid == 0) *unscale_slot = 1.f;  // scaling is undone per group inside the item
   } else {
-    bool staged = true;
-    const float unscale =
-        stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, xbar, consumer_sync, staged);
-    if (!staged) return;
-    if (ctid == 0) *unscale_slot = unscale;
+    if (!stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, xbar)) return;
+    if (ctid == 0) *unscale_slot = 1.f;  // scaling is undone per group inside the item
   }
   if (!consumer_sync()) return;
+  TB200_TRACE(ctid == 0, 1);
 
   const int gid = lane >> 2, tig = lane & 3;
   const uint32_t smem_base = ptx::smem_addr(smem);
@@ -685,8 +736,11 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       report_timeout(0x20000u | (unsigned)s);
       return;
     }
+    TB200_TRACE(ctid == 0 && i < 16, 8 + i);
     const uint32_t stage = stage0 + s * stage_step;
-    float* redbuf = red + (i & 1) * red_per_buf + cw * kRedPerWarp;
+    const int rb = a.red_bufs == 2 ? (i & 1) : 0;
+    const int ruse = a.red_bufs == 2 ? (i >> 1) : i;
+    float* redbuf = red + rb * red_per_buf + cw * kRedPerWarp;
     if constexpr (GROUPS) {
       float accA = 0.f, accB = 0.f;
       for (int sbl = cw; sbl < nsb_l; sbl += Wp)
@@ -698,7 +752,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       accA += __shfl_xor_sync(0xffffffffu, accA, 2);
       accB += __shfl_xor_sync(0xffffffffu, accB, 1);
       accB += __shfl_xor_sync(0xffffffffu, accB, 2);
-      if (i >= 2 && !ptx::mbar_wait(&red_empty[i & 1], ((i >> 1) - 1) & 1)) {
+      if (ruse >= 1 && !ptx::mbar_wait(&red_empty[rb], (ruse - 1) & 1)) {
         report_timeout(0x50000u);
         return;
       }
@@ -716,7 +770,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
         q4k_item_batch<NT>(sm, stage, sbl, lane, acc);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
-      if (i >= 2 && !ptx::mbar_wait(&red_empty[i & 1], ((i >> 1) - 1) & 1)) {
+      if (ruse >= 1 && !ptx::mbar_wait(&red_empty[rb], (ruse - 1) & 1)) {
         report_timeout(0x50000u);
         return;
       }
@@ -730,7 +784,8 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       }
     }
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(&red_full[i & 1]);
+    TB200_TRACE(ctid == 0 && i < 16, 24 + i);
+    if (lane == 0) ptx::mbar_arrive(&red_full[rb]);
     if (++s == Sp) {
       s = 0;
       phase ^= 1;
@@ -745,14 +800,28 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   }
 }
 
-template <int FMT, bool F16, int NT, bool GROUPS>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int FMT, bool F16, int NT, bool GROUPS, bool WIDE>
+__global__ void __launch_bounds__(WIDE ? kThreadsWide : kThreadsNarrow, WIDE ? 1 : 2)
     gemv_mma_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap) {
   gemv_mma_body<FMT, F16, NT, GROUPS>(a, &wmap);
 }
 
 inline int round_up(int v, int to) { return (v + to - 1) / to * to; }
 inline int groups_limit(int slots, int splits) { return slots / splits; }
+// as many decode warps as divide the super-blocks of a K range most evenly (ties: more warps)
+inline int choose_warps(int sb_per_split, int max_warps) {
+  int best_w = max_warps;
+  double best_eff = 0;
+  for (int w = max_warps; w >= 4; --w) {
+    const int rounds = (sb_per_split + w - 1) / w;
+    const double eff = (double)sb_per_split / (rounds * w) * (0.9 + 0.1 * w / max_warps);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best_w = w;
+    }
+  }
+  return best_w;
+}
 // a tiled copy with 8-byte elements covers at most 256 elements = 2048 bytes per row
 inline bool tma_ok(int fmt, int sb_per_split) { return sb_per_split * block_bytes(fmt) <= 2048; }
 
@@ -767,7 +836,7 @@ struct Layout {
   int stride_s, xs_stride, stage_bytes, off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc, total;
 };
 
-Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed) {
+Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed, int warps, int red_bufs) {
   const bool groups = m == 1;
   const int ntb = groups ? 1 : (m <= 8 ? 8 : 16);
   Layout L;
@@ -781,11 +850,11 @@ Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed) {
   L.off_xs = off;
   off += ntb * L.xs_stride;
   L.off_sx = off;
-  off += round_up(sb_per_split * 8 * (groups ? 2 : ntb) * 4, 128);
+  off += round_up(sb_per_split * 8 * ntb * 8, 128);  // {group sum, unscale} per group and column
   L.off_red = off;
-  off += 2 * kMaxConsumerWarps * ntb * kTileRows * 4;
+  off += red_bufs * warps * ntb * kTileRows * 4;
   L.off_scl = off;
-  off += groups ? 0 : kMaxConsumerWarps * kTileRows * kSclRowFloats * 4;
+  off += groups ? 0 : warps * kTileRows * kSclRowFloats * 4;
   L.off_zero = off;  // 64 zero bytes: the B fragment of lanes whose weights feed another column
   off += 64;
   L.off_misc = off;  // the factor that undoes the activation scaling
@@ -799,10 +868,10 @@ Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed) {
 // ---- static-shape entry used by generated .tbin wrappers ------------------------------------------
 // A .tbin kernel is launched by the reference's provider with nothing but its declared buffers, so
 // the launch plan is baked in as constants (GemvStatic) by the packaging step.
-constexpr int kGemvThreads = kThreads;
 struct GemvStatic {
   int nsb, sb_per_split, k_splits, row_groups, row_tiles, stages, stride_s, xs_stride;
   int off_stage, off_xs, off_sx, off_red, off_scl, off_zero, off_misc, contiguous, use_tma, consumer_warps;
+  int red_bufs;
 };
 template <int FMT, bool F16, int NT, bool GROUPS>
 __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const void* x, const uint8_t* w,
@@ -836,6 +905,7 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
   a.contiguous = s.contiguous;
   a.use_tma = s.use_tma;
   a.consumer_warps = s.consumer_warps;
+  a.red_bufs = s.red_bufs;
   gemv_mma_body<FMT, F16, NT, GROUPS>(a, wmap);
 }
 
@@ -864,12 +934,18 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
       const long long need =
           splits > 1 ? (kCounterBytes + (long long)splits * m * n * 4) : 0;
       if (need > scratch_bytes_available) continue;
-      int stages = 0;
+      int stages = 0, red_bufs = 2;
+      const int warps = choose_warps(per, per_sm == 1 ? kMaxConsumerWarps : kNarrowWarps);
       Layout L{};
-      for (int s = kMaxStages; s >= 2; --s) {
-        L = make_layout(fmt, (int)m, per, s, splits == 1 || tma_ok(fmt, per));
-        if (L.total <= smem_limit) { stages = s; break; }
-      }
+      for (int rbufs = 2; rbufs >= 1 && !stages; --rbufs)
+        for (int s = kMaxStages; s >= 2; --s) {
+          L = make_layout(fmt, (int)m, per, s, splits == 1 || tma_ok(fmt, per), warps, rbufs);
+          if (L.total <= smem_limit) {
+            stages = s;
+            red_bufs = rbufs;
+            break;
+          }
+        }
       if (!stages) continue;
       // splitting K so finely that the ring holds little data cannot keep HBM busy
       if (splits > 1 && (long long)stages * L.stage_bytes * per_sm < 96 * 1024 && stages < kMaxStages) continue;
@@ -895,15 +971,17 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
         best.smem_bytes = L.total;
         best.scratch_bytes = need;
         best.ctas_per_sm = per_sm;
+        best.consumer_warps = warps;
+        best.red_bufs = red_bufs;
       }
     }
   }
   return best;
 }
 
-template <int FMT, bool F16, int NT, bool GROUPS>
+template <int FMT, bool F16, int NT, bool GROUPS, bool WIDE>
 static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t stream) {
-  auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS>;
+  auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS, WIDE>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   alignas(64) CUtensorMap wmap;
@@ -915,7 +993,7 @@ static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t 
                             (unsigned long long)a.row_bytes, box_inner, kTileRows, false))
       return cudaErrorNotSupported;
   }
-  kernel<<<grid, kThreads, smem, stream>>>(a, wmap);
+  kernel<<<grid, (a.consumer_warps + 2) * 32, smem, stream>>>(a, wmap);
   return cudaGetLastError();
 }
 
@@ -925,11 +1003,11 @@ bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n,
   if (!plan.supported || fmt != kQ4_K) return false;
   GemvArgs a{};
   const int smem = fill_args(a, plan, fmt, m, n, k);
-  const int vals[] = {plan.k_splits * plan.row_groups, kThreads, smem, a.k_splits, a.row_groups, a.row_tiles,
+  const int vals[] = {plan.k_splits * plan.row_groups, (a.consumer_warps + 2) * 32, smem, a.k_splits, a.row_groups, a.row_tiles,
                       a.sb_per_split, a.nsb, a.stages, a.stride_s, a.xs_stride, a.off_stage, a.off_xs, a.off_sx,
                       a.off_red, a.off_scl, a.off_zero, a.off_misc, a.contiguous, a.use_tma, a.consumer_warps,
                       (int)(plan.scratch_bytes > 0x7fffffff ? 0x7fffffff : plan.scratch_bytes), plan.ctas_per_sm,
-                      kCounterBytes};
+                      kCounterBytes, a.red_bufs};
   for (int i = 0; i < 32; ++i) out32[i] = i < (int)(sizeof(vals) / sizeof(int)) ? vals[i] : 0;
   return true;
 }
@@ -943,6 +1021,27 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   a.x = x;
   a.w = w;
   a.out = out;
+#ifdef TB200_GEMV_TRACE
+  {
+    static unsigned long long* host = nullptr;
+    if (!host) {
+      cudaHostAlloc((void**)&host, 80 * 8 * 8, cudaHostAllocMapped);
+      memset(host, 0, 80 * 8 * 8);
+      atexit([] {
+        for (int c = 0; c < 3; ++c) {
+          const unsigned long long* d = host + c * 80;
+          if (!d[0]) continue;
+          printf("trace cta %d: activations landed +%llu ns, staged +%llu ns; conversion rounds at +%llu +%llu +%llu +%llu\n",
+                 c * 100, d[2] ? d[2] - d[0] : 0ull, d[1] - d[0], d[3] - d[0], d[4] - d[0], d[5] - d[0], d[6] - d[0]);
+          for (int i = 0; i < 16 && d[8 + i]; ++i)
+            printf("  tile %2d: copy issued +%6llu  data ready +%6llu  decoded +%6llu  reduced +%6llu\n", i,
+                   d[56 + i] - d[0], d[8 + i] - d[0], d[24 + i] - d[0], d[40 + i] - d[0]);
+        }
+      });
+    }
+    a.trace = host;
+  }
+#endif
   if (plan.k_splits > 1) {
     if (!scratch) return cudaErrorInvalidValue;
     a.counters = static_cast<unsigned int*>(scratch);
@@ -950,14 +1049,16 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   }
   const int grid = plan.k_splits * plan.row_groups;
   const bool f16 = xt == kF16;
-  if (m == 1)
-    return f16 ? launch_variant<kQ4_K, true, 1, true>(a, grid, smem_total, stream)
-               : launch_variant<kQ4_K, false, 1, true>(a, grid, smem_total, stream);
-  if (m <= 8)
-    return f16 ? launch_variant<kQ4_K, true, 1, false>(a, grid, smem_total, stream)
-               : launch_variant<kQ4_K, false, 1, false>(a, grid, smem_total, stream);
-  return f16 ? launch_variant<kQ4_K, true, 2, false>(a, grid, smem_total, stream)
-             : launch_variant<kQ4_K, false, 2, false>(a, grid, smem_total, stream);
+  const bool wide = plan.ctas_per_sm == 1;
+#define TB200_GEMV_DISPATCH(NT, GROUPS)                                                                    \
+  (f16 ? (wide ? launch_variant<kQ4_K, true, NT, GROUPS, true>(a, grid, smem_total, stream)                \
+               : launch_variant<kQ4_K, true, NT, GROUPS, false>(a, grid, smem_total, stream))              \
+       : (wide ? launch_variant<kQ4_K, false, NT, GROUPS, true>(a, grid, smem_total, stream)               \
+               : launch_variant<kQ4_K, false, NT, GROUPS, false>(a, grid, smem_total, stream)))
+  if (m == 1) return TB200_GEMV_DISPATCH(1, true);
+  if (m <= 8) return TB200_GEMV_DISPATCH(1, false);
+  return TB200_GEMV_DISPATCH(2, false);
+#undef TB200_GEMV_DISPATCH
 }
 
 // Everything of GemvArgs that follows from the plan and the shape; returns the dynamic shared memory.
@@ -973,7 +1074,8 @@ static int fill_args(GemvArgs& a, const GemvPlan& plan, int fmt, long long m, lo
   a.row_tiles = (int)((n + kTileRows - 1) / kTileRows);
   a.stages = plan.stages;
   const bool tma = plan.k_splits > 1 && tma_ok(fmt, plan.sb_per_split);
-  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages, plan.k_splits == 1 || tma);
+  const Layout L = make_layout(fmt, (int)m, plan.sb_per_split, plan.stages, plan.k_splits == 1 || tma,
+                               plan.consumer_warps, plan.red_bufs);
   a.contiguous = plan.k_splits == 1;
   a.use_tma = tma;
   a.stride_s = L.stride_s;
@@ -985,18 +1087,8 @@ static int fill_args(GemvArgs& a, const GemvPlan& plan, int fmt, long long m, lo
   a.off_scl = L.off_scl;
   a.off_zero = L.off_zero;
   a.off_misc = L.off_misc;
-  // as many decode warps as divide the super-blocks of a K range most evenly (ties: more warps)
-  int best_w = kMaxConsumerWarps;
-  double best_eff = 0;
-  for (int w = kMaxConsumerWarps; w >= 4; --w) {
-    const int rounds = (plan.sb_per_split + w - 1) / w;
-    const double eff = (double)plan.sb_per_split / (rounds * w) * (0.9 + 0.1 * w / kMaxConsumerWarps);
-    if (eff > best_eff + 1e-9) {
-      best_eff = eff;
-      best_w = w;
-    }
-  }
-  a.consumer_warps = best_w;
+  a.consumer_warps = plan.consumer_warps;
+  a.red_bufs = plan.red_bufs;
   return L.total;
 }
 #endif  // TB200_TBIN_WRAPPER

@@ -34,6 +34,8 @@ struct GemvPlan {
   int smem_bytes = 0;
   long long scratch_bytes = 0;
   int ctas_per_sm = 1;
+  int consumer_warps = 8;
+  int red_bufs = 2;
 };
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
                         long long scratch_bytes_available, const DeviceInfo& dev);

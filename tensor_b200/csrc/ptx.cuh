@@ -26,14 +26,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One attempt; the hardware parks the warp until the phase completes or `suspend_ns` has passed,
+// so a waiting warp does not compete for issue slots with the warps that do the work.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t suspend_ns = 100000u) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_addr(bar)), "r"(parity)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(suspend_ns)
       : "memory");
   return ok != 0;
 }
@@ -50,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint64_t start = global_timer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < 8; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() - start > kWaitLimitNs) return false;
   }
@@ -97,6 +99,9 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
   float2 v;
   asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void sts64f(uint32_t addr, float a, float b) {
   asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(a), "f"(b) : "memory");

@@ -130,7 +130,7 @@ def _launch_config(encoding, m, n, k, scratch_bytes):
     names = ("grid", "threads", "smem_bytes", "k_splits", "row_groups", "row_tiles", "sb_per_split", "nsb",
              "stages", "stride_s", "xs_stride", "off_stage", "off_xs", "off_sx", "off_red", "off_scl",
              "off_zero", "off_misc", "contiguous", "use_tma", "consumer_warps", "scratch_bytes", "ctas_per_sm",
-             "counter_bytes")
+             "counter_bytes", "red_bufs")
     return dict(zip(names, (int(v) for v in out)))
 
 
@@ -153,11 +153,11 @@ def build_gemv_tbin(path: str, encoding, m: int, n: int, k: int, x_dtype: str = 
     fields = ", ".join(f"{cfg[key]}" for key in (
         "nsb", "sb_per_split", "k_splits", "row_groups", "row_tiles", "stages", "stride_s", "xs_stride",
         "off_stage", "off_xs", "off_sx", "off_red", "off_scl", "off_zero", "off_misc", "contiguous", "use_tma",
-        "consumer_warps"))
+        "consumer_warps", "red_bufs"))
     source = f"""// generated by tensor_b200.tbin: Q-format {fmt.name}, m={m}, n={n}, k={k}, x={x_dtype}
 #define TB200_TBIN_WRAPPER
 #include "gemv_mma.cu"
-extern "C" __global__ void __launch_bounds__(tb200::kGemvThreads, {cfg['ctas_per_sm']})
+extern "C" __global__ void __launch_bounds__({cfg['threads']}, {cfg['ctas_per_sm']})
 kernel_kernel(const void* x, {wparam}, float* out{', unsigned char* scratch' if split else ''}) {{
   const tb200::GemvStatic s = {{{fields}}};
   tb200::gemv_static_entry<{fmt.type_id}, {f16}, {nt}, {groups}>(
