@@ -64,31 +64,35 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return r;
 }
 
-// Store 32 consecutive bf16 of row `r` (k offset 32*h within the 64-wide stage) as four 16-byte
-// chunks at their swizzled positions: chunk c of row r lives at r*128 + ((c ^ (r & 7)) * 16).
-__device__ __forceinline__ void store_row_half(uint8_t* a_tile, int r, int h, const uint32_t (&v)[16]) {
-  uint8_t* row = a_tile + r * 128;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const int chunk = (4 * h + c) ^ (r & 7);
-    *reinterpret_cast<uint4*>(row + chunk * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-  }
-}
-
-// ---- per-format decode of 32 weights: row `wrow`, k-block kb (64 wide), half h -> 16 bf16x2 -------
-// Split into `fetch` (global loads into registers) and `decode`, so the loads of k-block kb+1 are
-// in flight while k-block kb is decoded.
+// ---- per-format decode of the [128 rows x 64 k] weight tile of one k-block by 256 threads --------
+// Split into `fetch` (global loads into registers, issued one k-block ahead), `decode` (exact fp32
+// arithmetic, rounded to bf16) and `store` (swizzled K-major tile: 16-byte chunk c of row r lives
+// at r*128 + ((c ^ (r & 7)) * 16), exactly what a 128-byte-swizzle TMA load would produce).
 
 template <int FMT> struct Decoder;
 
 template <> struct Decoder<kQ4_K> {
+  // thread t -> row t/2, half h = t%2: 32 weights of group 2p+h (p = kb%4), i.e. the low / high
+  // nibbles of quant bytes 32p .. 32p+31 of super-block kb/4.
+  struct Ctx {
+    const uint8_t* wrow;
+    int r, h;
+  };
   struct Raw {
     uint4 hdr, q0, q1;
   };
-  // k-block kb: super-block kb/4, group pair p = kb%4; half h is group 2p+h (low / high nibbles
-  // of quant bytes 32p .. 32p+31).
-  __device__ static __forceinline__ Raw fetch(const uint8_t* wrow, int kb, int /*h*/) {
-    const uint8_t* blk = wrow + (kb >> 2) * 144;
+  struct Out {
+    uint32_t v[16];
+  };
+  __device__ static __forceinline__ Ctx context(const uint8_t* w, long long row_bytes_, int n0, int N, int t) {
+    Ctx c;
+    c.r = t >> 1;
+    c.h = t & 1;
+    c.wrow = w + (long long)min(n0 + c.r, N - 1) * row_bytes_;  // rows past N: decoded and dropped
+    return c;
+  }
+  __device__ static __forceinline__ Raw fetch(const Ctx& c, int kb) {
+    const uint8_t* blk = c.wrow + (kb >> 2) * 144;
     const int p = kb & 3;
     Raw r;
     r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
@@ -96,7 +100,8 @@ template <> struct Decoder<kQ4_K> {
     r.q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * p));
     return r;
   }
-  __device__ static __forceinline__ void decode(const Raw& r, int kb, int h, uint32_t (&v)[16]) {
+  __device__ static __forceinline__ void decode(const Ctx& c, const Raw& r, int kb, Out& o) {
+    const int h = c.h;
     const int p = kb & 3, g = 2 * p + h;
     const uint4 hdr = r.hdr;
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
@@ -119,57 +124,100 @@ template <> struct Decoder<kQ4_K> {
       float f[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) f[b] = fmaf(dsc, byte_magic(nib, b) - 8388608.f, -dm);
-      v[2 * i] = pack_bf16(f[0], f[1]);
-      v[2 * i + 1] = pack_bf16(f[2], f[3]);
+      o.v[2 * i] = pack_bf16(f[0], f[1]);
+      o.v[2 * i + 1] = pack_bf16(f[2], f[3]);
+    }
+  }
+  __device__ static __forceinline__ void store(const Ctx& c, uint8_t* a_tile, const Out& o) {
+    uint8_t* row = a_tile + c.r * 128;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int chunk = (4 * c.h + q) ^ (c.r & 7);
+      *reinterpret_cast<uint4*>(row + chunk * 16) = make_uint4(o.v[4 * q], o.v[4 * q + 1], o.v[4 * q + 2], o.v[4 * q + 3]);
     }
   }
 };
 
 template <> struct Decoder<kQ6_K> {
-  // Blocks are 210 bytes, so a row's blocks are only 2-byte aligned: 32-byte spans are read as nine
-  // aligned words and realigned with funnel shifts at decode time.
-  struct Raw {
-    uint32_t ql[9], qh[9];
-    uint32_t shift;  // 0 or 16: misalignment of the block in bits
-    unsigned short scales, d;
+  // Blocks are 210 bytes: a row's blocks are only 2-byte aligned, and one thread per (row, half)
+  // would issue 4-byte loads that touch 32 different cache lines per warp instruction (measured:
+  // the L1 data pipe becomes the bound).  Instead eight lanes share a row: lane i of the group
+  // owns 4-byte word i of each 32-byte span, so a warp instruction covers four rows x 32
+  // contiguous bytes.  Four passes of 32 rows cover the tile.  Per pass a thread decodes 8 weights:
+  // 4 of quarter 2*(kb%2) from its low-span word and 4 of quarter 2*(kb%2)+1 from its high-span
+  // word, both with the same qh word.  Misaligned words are rebuilt from two aligned ones, the
+  // second taken from the neighbouring lane (lane 7 loads its own).
+  static constexpr int kPasses = 4;
+  struct Ctx {
+    const uint8_t* wrow[kPasses];
+    int row0, i;  // first row of the thread (pass p adds 32 p), word index 0..7
   };
-  // k-block kb: super-block kb/4, j = kb%4 covers weights 64j .. 64j+63: half-block j/2, quarters
-  // 2(j%2)+h; ql bytes 64(j/2) + 32h + lane, nibble j%2; qh bytes 32(j/2) + lane, bit pair 2(j%2)+h.
-  __device__ static __forceinline__ Raw fetch(const uint8_t* wrow, int kb, int h) {
-    const uint8_t* blk = wrow + (kb >> 2) * 210;
-    const int j = kb & 3, half = j >> 1;
-    const uint8_t* ql = blk + 64 * half + 32 * h;
-    const uint8_t* qh = blk + 128 + 32 * half;
-    Raw r;
-    r.shift = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 2) * 8;
-    const uint32_t* lp = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(ql) & ~uintptr_t(3));
-    const uint32_t* hp = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(qh) & ~uintptr_t(3));
+  struct Raw {
+    uint32_t lo[kPasses], hi[kPasses], qh[kPasses];
+    uint32_t meta[kPasses];  // scale of the low quarter | scale of the high quarter << 8 | d << 16
+  };
+  struct Out {
+    uint2 a[kPasses], b[kPasses];  // bf16 x 4 of the low / high quarter
+  };
+  __device__ static __forceinline__ Ctx context(const uint8_t* w, long long row_bytes_, int n0, int N, int t) {
+    Ctx c;
+    c.i = t & 7;
+    c.row0 = t >> 3;
 #pragma unroll
-    for (int i = 0; i < 9; ++i) {
-      r.ql[i] = __ldg(lp + i);
-      r.qh[i] = __ldg(hp + i);
+    for (int p = 0; p < kPasses; ++p) c.wrow[p] = w + (long long)min(n0 + c.row0 + 32 * p, N - 1) * row_bytes_;
+    return c;
+  }
+  __device__ static __forceinline__ uint32_t word_at(const uint8_t* p, int i) {
+    const uint32_t* a = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(p) & ~uintptr_t(3));
+    const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 2) * 8;
+    const uint32_t w0 = __ldg(a);
+    uint32_t w1 = __shfl_down_sync(0xffffffffu, w0, 1, 8);
+    if (i == 7) w1 = __ldg(a + 1);
+    return __funnelshift_r(w0, w1, sh);
+  }
+  __device__ static __forceinline__ Raw fetch(const Ctx& c, int kb) {
+    const int j = kb & 3, half = j >> 1, nib = j & 1;
+    Raw r;
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const uint8_t* blk = c.wrow[p] + (kb >> 2) * 210;
+      r.lo[p] = word_at(blk + 64 * half + 4 * c.i, c.i);
+      r.hi[p] = word_at(blk + 64 * half + 32 + 4 * c.i, c.i);
+      r.qh[p] = word_at(blk + 128 + 32 * half + 4 * c.i, c.i);
+      const uint8_t* sc = blk + 192 + 8 * half + 4 * nib + (c.i >> 2);
+      r.meta[p] = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 2) << 8) |
+                  ((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(blk + 208)) << 16);
     }
-    r.scales = __ldg(reinterpret_cast<const unsigned short*>(blk + 192 + 4 * j + 2 * h));
-    r.d = __ldg(reinterpret_cast<const unsigned short*>(blk + 208));
     return r;
   }
-  __device__ static __forceinline__ void decode(const Raw& r, int kb, int h, uint32_t (&v)[16]) {
-    const int j = kb & 3, quarter = 2 * (j & 1) + h;
-    const float d = __half2float(__ushort_as_half(r.d));
-    const float ds0 = d * (float)(int)(int8_t)(r.scales & 0xFF);
-    const float ds1 = d * (float)(int)(int8_t)(r.scales >> 8);
-    const int lsh = 4 * (j & 1), hsh = 2 * quarter;
+  __device__ static __forceinline__ void decode(const Ctx&, const Raw& r, int kb, Out& o) {
+    const int nib = kb & 1;
+    const int lsh = 4 * nib;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t lw = __funnelshift_r(r.ql[i], r.ql[i + 1], r.shift);
-      const uint32_t hw = __funnelshift_r(r.qh[i], r.qh[i + 1], r.shift);
-      const uint32_t q = ((lw >> lsh) & 0x0F0F0F0Fu) | (((hw >> hsh) & 0x03030303u) << 4);
-      const float ds = i < 4 ? ds0 : ds1;
-      float f[4];
+    for (int p = 0; p < kPasses; ++p) {
+      const float d = __half2float(__ushort_as_half((unsigned short)(r.meta[p] >> 16)));
+      const float dsa = d * (float)(int)(int8_t)(r.meta[p] & 0xFF);
+      const float dsb = d * (float)(int)(int8_t)((r.meta[p] >> 8) & 0xFF);
+      const uint32_t qa = ((r.lo[p] >> lsh) & 0x0F0F0F0Fu) | (((r.qh[p] >> lsh) & 0x03030303u) << 4);
+      const uint32_t qb = ((r.hi[p] >> lsh) & 0x0F0F0F0Fu) | (((r.qh[p] >> (lsh + 2)) & 0x03030303u) << 4);
+      float fa[4], fb[4];
 #pragma unroll
-      for (int b = 0; b < 4; ++b) f[b] = (byte_magic(q, b) - 8388640.f) * ds;  // 2^23 + 32
-      v[2 * i] = pack_bf16(f[0], f[1]);
-      v[2 * i + 1] = pack_bf16(f[2], f[3]);
+      for (int b = 0; b < 4; ++b) {
+        fa[b] = (byte_magic(qa, b) - 8388640.f) * dsa;  // 2^23 + 32
+        fb[b] = (byte_magic(qb, b) - 8388640.f) * dsb;
+      }
+      o.a[p] = make_uint2(pack_bf16(fa[0], fa[1]), pack_bf16(fa[2], fa[3]));
+      o.b[p] = make_uint2(pack_bf16(fb[0], fb[1]), pack_bf16(fb[2], fb[3]));
+    }
+  }
+  __device__ static __forceinline__ void store(const Ctx& c, uint8_t* a_tile, const Out& o) {
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const int r = c.row0 + 32 * p;
+      uint8_t* row = a_tile + r * 128 + (c.i & 1) * 8;
+      // k = 4 i .. 4 i + 3 of the low quarter: chunk i / 2; the high quarter is 32 k (4 chunks) further
+      *reinterpret_cast<uint2*>(row + ((((c.i >> 1)) ^ (r & 7)) << 4)) = o.a[p];
+      *reinterpret_cast<uint2*>(row + (((4 + (c.i >> 1)) ^ (r & 7)) << 4)) = o.b[p];
     }
   }
 };
@@ -251,25 +299,23 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
     }
   } else {
     // ---------------- decode warps, then epilogue ----------------
-    const int t = threadIdx.x - 64;
-    const int r = t >> 1, h = t & 1;
-    const int grow = min(n0 + r, N - 1);  // rows past N are decoded from the last row and dropped
-    const uint8_t* wrow = w + (long long)grow * row_bytes_;
+    using D = Decoder<FMT>;
+    const typename D::Ctx ctx = D::context(w, row_bytes_, n0, N, (int)threadIdx.x - 64);
     bool ok = true;
-    typename Decoder<FMT>::Raw raw = Decoder<FMT>::fetch(wrow, 0, h);
+    typename D::Raw raw = D::fetch(ctx, 0);
     for (int kb = 0; kb < k_blocks; ++kb) {
       const int s = kb % kStages;
       // start the loads of the next k-block before decoding this one (clamped on the last)
-      const typename Decoder<FMT>::Raw next = Decoder<FMT>::fetch(wrow, min(kb + 1, k_blocks - 1), h);
-      uint32_t v[16];
-      Decoder<FMT>::decode(raw, kb, h, v);
+      const typename D::Raw next = D::fetch(ctx, min(kb + 1, k_blocks - 1));
+      typename D::Out decoded;
+      D::decode(ctx, raw, kb, decoded);
       raw = next;
       if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
         report_timeout(0x30000u | (unsigned)kb);
         ok = false;
         break;
       }
-      store_row_half(a_tiles + s * kABytes, r, h, v);
+      D::store(ctx, a_tiles + s * kABytes, decoded);
       ptx::fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
       ptx::mbar_arrive(&full_a[s]);
     }
