@@ -58,12 +58,14 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def workload_config(world: int):
+def workload_config(world: int, gather: str = "fused"):
     return {
         "workload": "q4_k decode GEMV: gate/up 18944x3584 + down 3584x18944, batch 1/4/16 (9 GEMVs per step)",
         "format": FORMAT, "batches": list(BATCHES), "activations": "bf16", "output": "fp32",
         "l2": "weights rotate over a ring of sets > 3x L2; every launch streams from HBM",
-        "parallelism": f"N-sharded x{world}" + (" + NCCL all-gather per projection" if world > 1 else ""),
+        "parallelism": f"N-sharded x{world}" + ("" if world == 1 else (
+            " + peer stores in the GEMV epilogue over NVLink and one barrier kernel after gate+up and after down"
+            if gather == "fused" else " + NCCL all-gather (gate+up together, then down)")),
     }
 
 
@@ -195,7 +197,8 @@ def run_gpu(args):
 
     import tensor_b200 as tb
     from tensor_b200 import synth
-    from tensor_b200.projection import QuantLinear, shard_rows
+    from tensor_b200.peer import PeerArena
+    from tensor_b200.projection import FusedGatherGroup, GatherGroup, QuantLinear
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -207,6 +210,8 @@ def run_gpu(args):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner would share stdout with the JSON line
         dist.init_process_group("nccl", device_id=device)
     peaks = measured_peaks()
     fmt = tb.get_format(FORMAT)
@@ -227,11 +232,20 @@ def run_gpu(args):
     lins = {b: [QuantLinear(weights[0][j], fmt, n, k, b, rank=rank, world=world, variant="auto")
                 for j, (_, n, k) in enumerate(SHAPES)] for b in BATCHES}
     launches_per_step = len(BATCHES) * len(SHAPES)
+    barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused" else 0
+    # gate and up are needed together (one collective for both); down follows
+    if args.gather == "fused":
+        # the GEMVs store their columns into every rank's output; one barrier kernel per group
+        out_bytes = sum(b * n * 4 + 256 for b in BATCHES for _, n, _ in SHAPES)
+        arena = PeerArena(out_bytes + (1 << 16), device, rank, world)
+        groups = {b: [FusedGatherGroup(lins[b][0:2], arena), FusedGatherGroup(lins[b][2:3], arena)] for b in BATCHES}
+    else:
+        groups = {b: [GatherGroup(lins[b][0:2]), GatherGroup(lins[b][2:3])] for b in BATCHES}
 
     def step(slot, batches=BATCHES):
         for b in batches:
-            for j in range(len(SHAPES)):
-                lins[b][j].forward(acts[b][j], raw=weights[slot][j])
+            groups[b][0].forward(acts[b][0:2], raws=weights[slot][0:2])
+            groups[b][1].forward(acts[b][2:3], raws=weights[slot][2:3])
 
     # ---- CUDA graphs: one per ring slot (launch-bound otherwise: a GEMV is a few microseconds) ----
     stream = torch.cuda.Stream(device)
@@ -395,8 +409,8 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16 mma / f32 accumulate", "data": "synthetic",
-        "config": workload_config(world), "clocks": clocks, "e2e": e2e,
-        "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cases": cases,
+        "config": workload_config(world, args.gather), "clocks": clocks, "e2e": e2e,
+        "gpu_launches": (launches_per_step + barriers_per_step) * args.steps, "roofline": roofline, "cases": cases,
         "prefill": prefill, "cuda_graphs": use_graphs, "device_status": status,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -424,6 +438,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=("fused", "nccl"),
+                    help="multi-GPU: peer stores inside the GEMV + barrier kernel, or NCCL all-gather")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -162,6 +162,47 @@ int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void *x, const vo
 int32_t tb200_gguf_gemv_static(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
                                int64_t m, int64_t n, int64_t k, void *stream, TensorErrorV1 *error);
 
+/* N-sharded GEMV: this rank holds n of the projection's rows (w is [n, k]) and writes its n result
+ * columns into `out_count` destinations: element (row, col) goes to
+ * outs[i][row * out_ld + col_offset + col].  outs is a HOST array of device addresses; outs[0] is
+ * normally this rank's own full-width output and outs[1..] the other ranks' outputs as mapped into
+ * this process (CUDA IPC / peer access), so the all-gather of the reference-side plan "shard along
+ * N, gather `out`" happens in the kernel's own stores over NVLink.  Follow it (once per group of
+ * projections) with tb200_peer_barrier before anything reads the outputs.  out_count <= 8,
+ * out_ld >= col_offset + n.  The reference has no multi-GPU path; the per-shard call is an
+ * ordinary launch(x, w_shard, out_shard) (src/tensor/providers/cuda/device.py:30-39). */
+#define TB200_MAX_PEERS 8
+int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void *x, const void *w,
+                                float *const *outs, int32_t out_count, int64_t out_ld,
+                                int64_t col_offset, int64_t m, int64_t n, int64_t k, void *scratch,
+                                int64_t scratch_bytes, int32_t variant, void *stream,
+                                TensorErrorV1 *error);
+
+/* Barrier between the GPUs of one box over peer-mapped signal pads.  pads is a HOST array of
+ * `world` device addresses: pads[i] is rank i's pad (TB200_SIGNAL_PAD_BYTES, 4-byte aligned,
+ * zero-filled once before the first use) as mapped into this process.  The kernel announces on
+ * every peer's pad that all work enqueued on `stream` before it is complete, then waits until
+ * every peer has announced the same; the wait gives up after two seconds and leaves
+ * 0x90000 | peer in the device status word (tb200_gguf_device_status).  Every rank must call it
+ * the same number of times, each rank on its own GPU.  No counterpart in the reference. */
+#define TB200_SIGNAL_PAD_BYTES 256
+int32_t tb200_peer_barrier(uint32_t *const *pads, int32_t rank, int32_t world, void *stream,
+                           TensorErrorV1 *error);
+
+/* Peer mapping of host-owned device memory between the processes of one box (one process per
+ * GPU), for the two entry points above.  tb200_peer_export writes the 64-byte CUDA IPC handle of
+ * the allocation that contains ptr and ptr's byte offset inside it; the host sends both to the other
+ * ranks by its own means.  tb200_peer_open maps such an allocation into the calling process on the
+ * current device (peer access is enabled as a side effect) and returns its base: the peer's ptr is
+ * base + offset.  An allocation can be opened once per process; tb200_peer_close unmaps it.  The
+ * library allocates nothing here either: the memory stays the exporting host's.  The exporting
+ * allocation must come from cudaMalloc (for PyTorch: the default caching allocator, not expandable
+ * segments).  No counterpart in the reference. */
+#define TB200_PEER_HANDLE_BYTES 64
+int32_t tb200_peer_export(const void *ptr, uint8_t *handle, int64_t *offset, TensorErrorV1 *error);
+int32_t tb200_peer_open(const uint8_t *handle, void **base, TensorErrorV1 *error);
+int32_t tb200_peer_close(void *base, TensorErrorV1 *error);
+
 /* Prefill GEMM: out[m, n] (fp32) = x[m, k] . dequant(w[n, k])^T with both operands rounded to
  * bf16 and fp32 accumulation.  Replaces `_packed` (showcase/kernels.py:116-119; contract
  * showcase/benchmark.py:471-477, triton_kernels.py:184-210, there with fp16 operands).

@@ -20,6 +20,7 @@ static_assert(sizeof(TensorArgumentV1) == 64, "TensorArgumentV1 layout");
 static_assert(sizeof(TensorStreamV1) == 16, "TensorStreamV1 layout");
 static_assert(sizeof(TensorCallV1) == 72, "TensorCallV1 layout");
 static_assert(sizeof(TensorErrorV1) == 512, "TensorErrorV1 layout");
+static_assert(tb200::kMaxOutputs == TB200_MAX_PEERS && tb200::kSignalWords * 4 == TB200_SIGNAL_PAD_BYTES, "peer limits");
 
 namespace tb200 {
 
@@ -203,14 +204,16 @@ int32_t tb200_gguf_gemm_launch_config(int32_t format, int64_t m, int64_t n, int6
 }
 
 int32_t tb200_gguf_device_status(uint32_t* status, TensorErrorV1* error) {
-  unsigned int a = 0, b = 0;
+  unsigned int a = 0, b = 0, c = 0;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return cuda_fail(error, "cudaDeviceSynchronize", e);
   if ((e = read_gemv_status(&a, true)) != cudaSuccess) return cuda_fail(error, "reading GEMV status", e);
   if ((e = read_gemm_status(&b, true)) != cudaSuccess) return cuda_fail(error, "reading GEMM status", e);
-  if (status) *status = a ? a : b;
-  if (a || b)
-    return fail(error, TENSOR_ERROR_PROVIDER, "a bounded device-side wait gave up (gemv 0x%x, gemm 0x%x)", a, b);
+  if ((e = read_barrier_status(&c, true)) != cudaSuccess) return cuda_fail(error, "reading barrier status", e);
+  if (status) *status = a ? a : (b ? b : c);
+  if (a || b || c)
+    return fail(error, TENSOR_ERROR_PROVIDER,
+                "a bounded device-side wait gave up (gemv 0x%x, gemm 0x%x, peer barrier 0x%x)", a, b, c);
   return ok(error);
 }
 
@@ -227,17 +230,17 @@ int32_t tb200_gguf_dequant(int32_t format, const void* w, float* out, int64_t n,
   return ok(error);
 }
 
-int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
-                        int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
-                        TensorErrorV1* error) {
-  if (int32_t s = check_shape(error, format, m, n, k)) return s;
-  if (x_dtype != TENSOR_FLOAT16 && x_dtype != TENSOR_BFLOAT16 && x_dtype != TENSOR_FLOAT32)
-    return fail(error, TENSOR_ERROR_ARGUMENT, "activation dtype %d is not float16, bfloat16 or float32", x_dtype);
-  if (variant < 0 || variant > 2) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
-  if (m == 0 || n == 0) return ok(error);
+}  // extern "C"
+
+namespace {
+// Shared by the plain and the sharded entry points: `out` says where the [m, n] result goes.
+int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* w, const OutSpec& out, int64_t m,
+                    int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
+                    TensorErrorV1* error) {
   if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
   if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
-  if (int32_t s = check_pointer(error, "out", out, 4, true)) return s;
+  for (int i = 0; i < out.count; ++i)
+    if (int32_t s = check_pointer(error, "out", out.ptr[i], 4, true)) return s;
   if (int32_t s = check_pointer(error, "scratch", scratch, 256, false)) return s;
   if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
   const DeviceInfo* dev;
@@ -258,6 +261,95 @@ int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void* x, const vo
   }
   cudaError_t e = launch_gemv_simple(format, x_dtype, x, wp, out, m, n, k, false, st);
   if (e != cudaSuccess) return cuda_fail(error, "GEMV launch", e);
+  return ok(error);
+}
+
+int32_t check_gemv_scalars(TensorErrorV1* error, int32_t format, int32_t x_dtype, int64_t m, int64_t n, int64_t k,
+                           int32_t variant) {
+  if (int32_t s = check_shape(error, format, m, n, k)) return s;
+  if (x_dtype != TENSOR_FLOAT16 && x_dtype != TENSOR_BFLOAT16 && x_dtype != TENSOR_FLOAT32)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "activation dtype %d is not float16, bfloat16 or float32", x_dtype);
+  if (variant < 0 || variant > 2) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  return TENSOR_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
+                        int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
+                        TensorErrorV1* error) {
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n, k, variant)) return s;
+  if (m == 0 || n == 0) return ok(error);
+  return gemv_common(format, x_dtype, x, w, single_output(out, n), m, n, k, scratch, scratch_bytes, variant, stream,
+                     error);
+}
+
+int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, const void* w, float* const* outs,
+                                int32_t out_count, int64_t out_ld, int64_t col_offset, int64_t m, int64_t n,
+                                int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
+                                TensorErrorV1* error) {
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n, k, variant)) return s;
+  if (!outs) return fail(error, TENSOR_ERROR_ARGUMENT, "outs is null");
+  if (out_count < 1 || out_count > TB200_MAX_PEERS)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "out_count %d is not in 1..%d", out_count, TB200_MAX_PEERS);
+  if (col_offset < 0 || out_ld < col_offset + n)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "columns %lld..%lld do not fit a row of %lld", (long long)col_offset,
+                (long long)(col_offset + n), (long long)out_ld);
+  if (m == 0 || n == 0) return ok(error);
+  OutSpec spec{};
+  spec.count = out_count;
+  spec.ld = out_ld;
+  for (int i = 0; i < out_count; ++i) {
+    if (!outs[i]) return fail(error, TENSOR_ERROR_ARGUMENT, "outs[%d] is null", i);
+    spec.ptr[i] = outs[i] + col_offset;
+  }
+  return gemv_common(format, x_dtype, x, w, spec, m, n, k, scratch, scratch_bytes, variant, stream, error);
+}
+
+int32_t tb200_peer_export(const void* ptr, uint8_t* handle, int64_t* offset, TensorErrorV1* error) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == TB200_PEER_HANDLE_BYTES, "IPC handle size");
+  if (!ptr || !handle || !offset) return fail(error, TENSOR_ERROR_ARGUMENT, "ptr, handle and offset are required");
+  void* base = nullptr;
+  size_t size = 0;
+  if (!allocation_range(ptr, &base, &size))
+    return fail(error, TENSOR_ERROR_PROVIDER, "%p is not inside a device allocation of this process", ptr);
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, base);
+  if (e != cudaSuccess) return cuda_fail(error, "cudaIpcGetMemHandle", e);
+  memcpy(handle, &h, sizeof(h));
+  *offset = (int64_t)(static_cast<const char*>(ptr) - static_cast<const char*>(base));
+  return ok(error);
+}
+
+int32_t tb200_peer_open(const uint8_t* handle, void** base, TensorErrorV1* error) {
+  if (!handle || !base) return fail(error, TENSOR_ERROR_ARGUMENT, "handle and base are required");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(error, "cudaIpcOpenMemHandle", e);
+  *base = p;
+  return ok(error);
+}
+
+int32_t tb200_peer_close(void* base, TensorErrorV1* error) {
+  if (!base) return ok(error);
+  cudaError_t e = cudaIpcCloseMemHandle(base);
+  if (e != cudaSuccess) return cuda_fail(error, "cudaIpcCloseMemHandle", e);
+  return ok(error);
+}
+
+int32_t tb200_peer_barrier(uint32_t* const* pads, int32_t rank, int32_t world, void* stream, TensorErrorV1* error) {
+  if (!pads) return fail(error, TENSOR_ERROR_ARGUMENT, "pads is null");
+  if (world < 1 || world > TB200_MAX_PEERS || rank < 0 || rank >= world)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "rank %d of world %d (at most %d ranks)", rank, world, TB200_MAX_PEERS);
+  for (int i = 0; i < world; ++i)
+    if (int32_t s = check_pointer(error, "pad", pads[i], 4, true)) return s;
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaError_t e = launch_peer_barrier(pads, rank, world, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(error, "peer barrier launch", e);
   return ok(error);
 }
 

@@ -50,7 +50,10 @@ constexpr int kSclRowFloats = 18;  // 8 x (scale, offset) pairs + 2 floats of pa
 struct GemvArgs {
   const void* x;
   const uint8_t* w;
-  float* out;
+  float* outs[kMaxOutputs];  // destinations of the result (own buffer first, then peer-mapped ones)
+  int n_out;
+  int out_vec;               // every destination takes 16-byte stores
+  long long out_ld;          // elements between the batch rows of a destination
   float* partials;
   unsigned int* counters;
   int m;
@@ -525,6 +528,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       const long long grow = ((long long)rg + (long long)t * a.row_groups) * kTileRows + r4;
       if (grow >= a.n) continue;
       const long long idx = (long long)col * a.n + grow;
+      const long long oidx = (long long)col * a.out_ld + grow;
       if (vec) {
         float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
@@ -535,12 +539,18 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
           tot.z += p.z;
           tot.w += p.w;
         }
-        *reinterpret_cast<float4*>(&a.out[idx]) = tot;
+        if (a.out_vec) {
+          for (int d = 0; d < a.n_out; ++d) *reinterpret_cast<float4*>(&a.outs[d][oidx]) = tot;
+        } else {
+          const float e[4] = {tot.x, tot.y, tot.z, tot.w};
+          for (int d = 0; d < a.n_out; ++d)
+            for (int r = 0; r < 4; ++r) a.outs[d][oidx + r] = e[r];
+        }
       } else {
         for (int r = 0; r < 4 && grow + r < a.n; ++r) {
           float total = 0.f;
           for (int q = 0; q < a.k_splits; ++q) total += __ldcg(&a.partials[q * plane + idx + r]);
-          a.out[idx + r] = total;
+          for (int d = 0; d < a.n_out; ++d) a.outs[d][oidx + r] = total;
         }
       }
     }
@@ -629,8 +639,11 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       __syncwarp();
       TB200_TRACE(lane == 0 && i < 16, 40 + i);
       if (lane == 0) ptx::mbar_arrive(&red_empty[b]);  // partials are in registers now
-      float* dst = a.k_splits == 1 ? a.out : a.partials + (long long)ks * a.m * a.n;
-      const bool vec = (a.n & 3) == 0;
+      const bool final_out = a.k_splits == 1;
+      float* part = a.partials + (long long)ks * a.m * a.n;
+      const bool vec = final_out ? a.out_vec != 0 : (a.n & 3) == 0;
+      const long long ld = final_out ? a.out_ld : a.n;
+      const int dests = final_out ? a.n_out : 1;
 #pragma unroll
       for (int j = 0; j < kPerLane; ++j) {
         const int f = lane + 32 * j;  // (column f / 4, rows 4 * (f % 4) ..)
@@ -638,12 +651,14 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
         const long long grow = (long long)rt * kTileRows + r4;
         if (f >= kQuads || col >= a.m || grow >= a.n) continue;
         const float4 v = make_float4(sum[j].x * unscale, sum[j].y * unscale, sum[j].z * unscale, sum[j].w * unscale);
-        float* p = dst + (long long)col * a.n + grow;
-        if (vec) {
-          *reinterpret_cast<float4*>(p) = v;
-        } else {
-          const float e[4] = {v.x, v.y, v.z, v.w};
-          for (int r = 0; r < 4 && grow + r < a.n; ++r) p[r] = e[r];
+        for (int d = 0; d < dests; ++d) {
+          float* p = (final_out ? a.outs[d] : part) + (long long)col * ld + grow;
+          if (vec) {
+            *reinterpret_cast<float4*>(p) = v;
+          } else {
+            const float e[4] = {v.x, v.y, v.z, v.w};
+            for (int r = 0; r < 4 && grow + r < a.n; ++r) p[r] = e[r];
+          }
         }
       }
     }
@@ -880,7 +895,10 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
   GemvArgs a;
   a.x = x;
   a.w = w;
-  a.out = out;
+  a.outs[0] = out;
+  a.n_out = 1;
+  a.out_ld = n;
+  a.out_vec = (n & 3) == 0;
   a.counters = reinterpret_cast<unsigned int*>(scratch);
   a.partials = reinterpret_cast<float*>(scratch + counter_bytes);
   a.m = m;
@@ -1013,14 +1031,21 @@ bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n,
 }
 
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
-                             float* out, long long m, long long n, long long k, void* scratch,
+                             const OutSpec& out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream) {
   if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
+  if (out.count < 1 || out.count > kMaxOutputs || out.ld < n) return cudaErrorInvalidValue;
   GemvArgs a{};
   const int smem_total = fill_args(a, plan, fmt, m, n, k);
   a.x = x;
   a.w = w;
-  a.out = out;
+  a.n_out = out.count;
+  a.out_ld = out.ld;
+  a.out_vec = (n & 3) == 0 && (out.ld & 3) == 0;
+  for (int d = 0; d < out.count; ++d) {
+    a.outs[d] = out.ptr[d];
+    if (reinterpret_cast<uintptr_t>(out.ptr[d]) & 15) a.out_vec = 0;
+  }
 #ifdef TB200_GEMV_TRACE
   {
     static unsigned long long* host = nullptr;

@@ -12,7 +12,7 @@ namespace tb200 {
 template <int FMT, typename XT, int NB>
 __global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__ x,
                                                           const uint8_t* __restrict__ w,
-                                                          float* __restrict__ out, int m,
+                                                          const OutSpec out, int m,
                                                           long long n, int k, int weights_bf16) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -41,12 +41,13 @@ __global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__
     float v = acc[b];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0 && b0 + b < m) out[(long long)(b0 + b) * n + row] = v;
+    if (lane == 0 && b0 + b < m)
+      for (int d = 0; d < out.count; ++d) out.ptr[d][(long long)(b0 + b) * out.ld + row] = v;
   }
 }
 
 template <int FMT, typename XT>
-static cudaError_t launch_typed(const void* x, const uint8_t* w, float* out, long long m,
+static cudaError_t launch_typed(const void* x, const uint8_t* w, const OutSpec& out, long long m,
                                 long long n, long long k, bool weights_bf16, cudaStream_t stream) {
   const int warps = 8;
   dim3 block(warps * 32);
@@ -68,7 +69,7 @@ static cudaError_t launch_typed(const void* x, const uint8_t* w, float* out, lon
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(int xt, const void* x, const uint8_t* w, float* out, long long m,
+static cudaError_t launch_fmt(int xt, const void* x, const uint8_t* w, const OutSpec& out, long long m,
                               long long n, long long k, bool wb, cudaStream_t s) {
   switch (xt) {
     case kF16: return launch_typed<FMT, __half>(x, w, out, m, n, k, wb, s);
@@ -78,7 +79,7 @@ static cudaError_t launch_fmt(int xt, const void* x, const uint8_t* w, float* ou
   return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w, float* out,
+cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w, const OutSpec& out,
                                long long m, long long n, long long k, bool weights_bf16,
                                cudaStream_t stream) {
   if (m == 0 || n == 0) return cudaSuccess;

@@ -17,11 +17,34 @@ const DeviceInfo* device_info(cudaError_t* err);
 cudaError_t launch_dequant(int fmt, const uint8_t* w, float* out, long long n, long long k,
                            cudaStream_t stream);
 
+// Where a GEMV writes its [m, n] result: element (row, col) goes to ptr[i][row * ld + col] for every
+// i < count.  One destination with ld == n is the plain case; an N-sharded projection passes the
+// same column window of every rank's full-width output (ptr[1..] are peer-mapped addresses), so
+// the all-gather happens in the kernel's own stores.
+constexpr int kMaxOutputs = 8;
+struct OutSpec {
+  float* ptr[kMaxOutputs];
+  int count;
+  long long ld;
+};
+inline OutSpec single_output(float* out, long long n) {
+  OutSpec o{};
+  o.ptr[0] = out;
+  o.count = 1;
+  o.ld = n;
+  return o;
+}
+
 // SIMT fallback: any m, any K that is a multiple of the block size.  weights_bf16 rounds each
 // decoded weight to bf16 first (the GEMM operand contract).
-cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w, float* out,
+cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w, const OutSpec& out,
                                long long m, long long n, long long k, bool weights_bf16,
                                cudaStream_t stream);
+inline cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w, float* out,
+                                      long long m, long long n, long long k, bool weights_bf16,
+                                      cudaStream_t stream) {
+  return launch_gemv_simple(fmt, xt, x, w, single_output(out, n), m, n, k, weights_bf16, stream);
+}
 
 // Bulk-copy pipeline + mma.sync GEMV for m <= 16.
 struct GemvPlan {
@@ -42,8 +65,19 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
 // All launch constants of a plan (grid, threads, shared memory, ring layout ...): see tbin.py.
 bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n, long long k, int* out32);
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
-                             float* out, long long m, long long n, long long k, void* scratch,
+                             const OutSpec& out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream);
+inline cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
+                                    float* out, long long m, long long n, long long k, void* scratch,
+                                    cudaStream_t stream) {
+  return launch_gemv_fast(plan, fmt, xt, x, w, single_output(out, n), m, n, k, scratch, stream);
+}
+
+// Cross-GPU barrier over peer-mapped signal pads (one pad of kSignalWords uint32 per rank, zeroed
+// once): every rank tells every peer that all work it enqueued before is complete and visible,
+// then waits (bounded) until every peer has said the same.  pads[i] is rank i's pad as mapped here.
+constexpr int kSignalWords = 64;
+cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, cudaStream_t stream);
 
 // tcgen05 / TMEM prefill GEMM (bf16 operands, fp32 accumulate).
 // {grid.x, grid.y, threads, dynamic shared memory, token tile, k per stage, 0, 0}
@@ -60,7 +94,11 @@ bool make_tensor_map_2d(void* map_out, TmaType type, const void* base, unsigned 
                         unsigned box_outer, bool swizzle_128b);
 
 // Sticky status words of the pipelined kernels (bounded waits that gave up); these synchronise.
+// Base address and size of the device allocation that contains ptr (driver cuMemGetAddressRange).
+bool allocation_range(const void* ptr, void** base, size_t* size);
+
 cudaError_t read_gemv_status(unsigned int* value, bool clear);
 cudaError_t read_gemm_status(unsigned int* value, bool clear);
+cudaError_t read_barrier_status(unsigned int* value, bool clear);
 
 }  // namespace tb200

@@ -1,6 +1,6 @@
-// Host-side encoding of 2-D TMA tensor maps.  cuTensorMapEncodeTiled is resolved through the CUDA
-// runtime at first use, so the library has no link-time dependency on libcuda and still loads on a
-// machine without a driver.
+// Host-side calls into the CUDA driver: encoding of 2-D TMA tensor maps and the address range of
+// an allocation.  The driver functions are resolved through the CUDA runtime at first use, so the
+// library has no link-time dependency on libcuda and still loads on a machine without a driver.
 #include <cuda.h>
 
 #include "kernels.h"
@@ -41,6 +41,25 @@ bool make_tensor_map_2d(void* map_out, TmaType type, const void* base, unsigned 
                             swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+bool allocation_range(const void* ptr, void** base, size_t* size) {
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<RangeFn>(p);
+  }();
+  if (!fn) return false;
+  CUdeviceptr b = 0;
+  size_t n = 0;
+  if (fn(&b, &n, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS) return false;
+  *base = reinterpret_cast<void*>(b);
+  *size = n;
+  return true;
 }
 
 }  // namespace tb200

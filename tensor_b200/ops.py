@@ -169,3 +169,45 @@ def gemm(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out: torch.
              abi.scalar_argument(fmt.type_id), abi.scalar_argument(_VARIANTS[variant])]
     _invoke(lib().tb200_gguf_gemm_v1, args, device, stream)
     return out
+
+
+_X_DTYPE_IDS = {torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
+
+
+def gemv_sharded(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out_ptrs, out_ld: int,
+                 col_offset: int, scratch: torch.Tensor | None = None, variant="auto", stream=None) -> None:
+    """The GEMV of one rank of an N-sharded projection: ``w`` holds this rank's ``n`` rows and the
+    ``[m, n]`` result goes to columns ``col_offset .. col_offset + n`` of every ``[m, out_ld]`` fp32
+    matrix whose device address is in ``out_ptrs`` (own output first, then the other ranks' outputs
+    as mapped by :class:`tensor_b200.peer.PeerArena`).  See ``tb200_gguf_gemv_sharded``."""
+    fmt = get_format(encoding)
+    m = _infer_m(x, k)
+    _require_cuda("x", x)
+    _require_cuda("w", w)
+    if w.dtype != torch.uint8 or w.numel() != fmt.weight_bytes(n, k):
+        raise ValueError(f"w must hold the {fmt.weight_bytes(n, k)} raw bytes of [{n}, {k}] in {fmt.name}")
+    try:
+        x_dtype = _X_DTYPE_IDS[x.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported activation dtype {x.dtype}") from None
+    device = _same_device(x, w, scratch)
+    ptrs = [int(p) for p in out_ptrs]
+    table = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_gguf_gemv_sharded(
+            fmt.type_id, x_dtype, x.data_ptr(), w.data_ptr(), table, len(ptrs), out_ld, col_offset, m, n, k,
+            scratch.data_ptr() if scratch is not None else None, scratch.numel() if scratch is not None else 0,
+            _VARIANTS[variant], _stream_handle(device, stream), ctypes.byref(error))
+    raise_for_status(status, error)
+
+
+def peer_barrier(pad_ptrs, rank: int, device: torch.device, stream=None) -> None:
+    """Enqueue the cross-GPU barrier (``tb200_peer_barrier``) on ``stream``; ``pad_ptrs[i]`` is the
+    address of rank i's signal pad as mapped in this process."""
+    ptrs = [int(p) for p in pad_ptrs]
+    table = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_peer_barrier(table, rank, len(ptrs), _stream_handle(device, stream), ctypes.byref(error))
+    raise_for_status(status, error)

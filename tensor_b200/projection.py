@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import torch
 
+from . import ops
 from .formats import get_format
 from .kernel import GEMV_MAX_ROWS, GgufKernel
 
@@ -110,6 +111,89 @@ class QuantLinear:
     __call__ = forward
 
 
+class GatherGroup:
+    """Several projections that consume the same step's activations and whose outputs are needed
+    together (e.g. gate and up of one MLP): their local outputs live back to back in one buffer and
+    ONE all-gather moves them all, instead of one collective per projection.  Decode messages are
+    a few KB to a few hundred KB, so the collective's launch latency, not its bandwidth, is what
+    the step pays for."""
+
+    def __init__(self, linears):
+        self.linears = list(linears)
+        first = self.linears[0]
+        self.world, self.group, self.device = first.world, first.group, first.device
+        if any(l.world != self.world or l.device != self.device for l in self.linears):
+            raise ValueError("projections of a group must share the device and the process group")
+        if self.world > 1:
+            sizes = [l.m * l.n_local for l in self.linears]
+            self._local = torch.empty(sum(sizes), dtype=torch.float32, device=self.device)
+            self._gathered = torch.empty((self.world, sum(sizes)), dtype=torch.float32, device=self.device)
+            offset = 0
+            self._spans = []
+            for l, size in zip(self.linears, sizes):
+                # the kernel writes straight into its slice of the group buffer
+                l.out_local = self._local[offset:offset + size].view(l.m, l.n_local)
+                self._spans.append((offset, size))
+                offset += size
+
+    def forward(self, xs, raws=None):
+        """``xs[i]`` is the activation of projection i (``raws[i]`` optionally replaces its weight);
+        returns the list of full ``[m, N]`` outputs."""
+        for i, l in enumerate(self.linears):
+            l.kernel.launch(xs[i], l.raw if raws is None or raws[i] is None else raws[i], l.out_local)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self._gathered, self._local.view(1, -1), group=self.group)
+            for l, (offset, size) in zip(self.linears, self._spans):
+                part = self._gathered[:, offset:offset + size].view(self.world, l.m, l.n_local)
+                l.out.view(l.m, self.world, l.n_local).copy_(part.permute(1, 0, 2))
+        return [l.out for l in self.linears]
+
+    __call__ = forward
+
+
+class FusedGatherGroup:
+    """The same contract as :class:`GatherGroup` without a collective call: every projection's kernel
+    stores its columns into every rank's ``[m, N]`` output over NVLink (peer-mapped memory from a
+    :class:`tensor_b200.peer.PeerArena`) and ONE barrier kernel per group orders those stores before
+    whatever reads the outputs next.  A decode step moves a few KB per projection, so what the step
+    pays for is latency: the stores ride inside the GEMV and the barrier is a single small launch.
+
+    Outputs are reused from call to call.  Correct reuse needs a barrier between two writes of the
+    same buffer by any rank, with the reader's use of the first value enqueued before its side of
+    that barrier: one call of ``forward`` per group and step gives exactly that."""
+
+    def __init__(self, linears, arena):
+        self.linears = list(linears)
+        self.arena = arena
+        first = self.linears[0]
+        self.world, self.rank, self.device = first.world, first.rank, first.device
+        if arena.world != self.world or arena.rank != self.rank or arena.device != self.device:
+            raise ValueError("the arena belongs to another rank, world or device")
+        self._targets = []
+        for l in self.linears:
+            if l.world != self.world or l.device != self.device:
+                raise ValueError("projections of a group must share the device and the process group")
+            if l.kernel.op != "gemv":
+                raise ValueError("the fused gather covers decode GEMVs (m <= 16)")
+            offset = arena.take(l.m * l.n * 4)
+            l.out = arena.view(offset, (l.m, l.n))
+            self._targets.append(arena.ptrs(offset))
+        self._pads = arena.pad_ptrs()
+
+    def forward(self, xs, raws=None):
+        for i, l in enumerate(self.linears):
+            raw = l.raw if raws is None or raws[i] is None else raws[i]
+            ops.gemv_sharded(xs[i], raw, l.format, l.n_local, l.k, self._targets[i], l.n, l.rank * l.n_local,
+                             scratch=l.kernel._scratch, variant=l.kernel.variant)
+        if self.world > 1:
+            ops.peer_barrier(self._pads, self.rank, self.device)
+        return [l.out for l in self.linears]
+
+    __call__ = forward
+
+
 class HostProjection:
     """Host-buffer front end: activations arrive in (pinned) host memory and results are returned
     in host memory; weights stay resident on the GPU.  One call = H2D copy of ``x``, the kernel(s),
@@ -137,5 +221,5 @@ class HostProjection:
         return self.y_host
 
 
-__all__ = ["GEMV_MAX_ROWS", "HostProjection", "QuantLinear", "all_gather_columns", "shard_rows",
+__all__ = ["FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "all_gather_columns", "shard_rows",
            "shard_weight_bytes"]

@@ -160,3 +160,54 @@ def test_ops_refuse_cpu_tensors():
         k.launch(x, w, None)
     with pytest.raises(ValueError):
         k._check((x, w))
+
+
+# ---- N-sharded entry points: argument checks run before any device is touched -------------------
+
+def _sharded(out_count=1, out_ld=64, col_offset=0, n=32, outs=None, fmt=12, k=256):
+    import ctypes
+
+    from tensor_b200 import abi
+    from tensor_b200._native import lib
+
+    table = (ctypes.c_void_p * 8)(*(outs if outs is not None else [0x1000] * 8))
+    err = abi.TensorErrorV1()
+    status = lib().tb200_gguf_gemv_sharded(fmt, 13, 0x1000, 0x1000, table, out_count, out_ld, col_offset, 1, n, k,
+                                           None, 0, 0, None, ctypes.byref(err))
+    return status, err.message.decode()
+
+
+def test_sharded_gemv_rejects_bad_destinations():
+    assert _sharded(out_count=0)[0] == 2
+    assert _sharded(out_count=9)[0] == 2
+    status, message = _sharded(out_ld=40, col_offset=16, n=32)
+    assert status == 2 and "do not fit" in message
+    assert _sharded(col_offset=-4)[0] == 2
+    assert _sharded(outs=[0x1000, 0] + [0x1000] * 6, out_count=2)[0] == 2
+    assert _sharded(fmt=99)[0] == 2
+    # well-formed arguments get as far as the device check (no GPU here: provider error, never a CPU result)
+    assert _sharded()[0] == 3
+
+
+def test_peer_barrier_rejects_bad_ranks():
+    import ctypes
+
+    from tensor_b200 import abi
+    from tensor_b200._native import lib
+
+    table = (ctypes.c_void_p * 8)(*([0x1000] * 8))
+    err = abi.TensorErrorV1()
+    assert lib().tb200_peer_barrier(table, 2, 2, None, ctypes.byref(err)) == 2
+    assert lib().tb200_peer_barrier(table, 0, 9, None, ctypes.byref(err)) == 2
+    assert lib().tb200_peer_barrier(None, 0, 2, None, ctypes.byref(err)) == 2
+    assert lib().tb200_peer_barrier(table, 0, 2, None, ctypes.byref(err)) == 3
+
+
+def test_bump_allocator_gives_every_rank_the_same_offsets():
+    from tensor_b200.peer import BumpAllocator
+
+    a, b = BumpAllocator(4096), BumpAllocator(4096)
+    sizes = [256, 100, 4, 1000]
+    assert [a.take(s) for s in sizes] == [b.take(s) for s in sizes] == [0, 256, 512, 768]
+    with pytest.raises(MemoryError):
+        a.take(4096)

@@ -1,0 +1,100 @@
+"""N-sharded projections on two GPUs: every rank owns N/2 rows of each weight, computes its columns
+with the same kernel, and the gather (one NCCL collective per projection, one for a group of
+projections, or the kernels' own peer stores followed by the barrier kernel) must reproduce the
+single-GPU result bit for bit.  Skipped with fewer than two GPUs."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, result_path):
+    import torch.distributed as dist
+
+    import tensor_b200 as tb
+    from tensor_b200 import synth
+    from tensor_b200.peer import PeerArena
+    from tensor_b200.projection import FusedGatherGroup, GatherGroup, QuantLinear, shard_weight_bytes
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    ok = True
+    arena = PeerArena(4 << 20, dev, rank, world)
+    shapes = [(2048, 3584), (2048, 3584), (1024, 4096)]
+    for m in (1, 4):
+        fulls = [synth.make_weights("q4_k", n, k, seed=10 + i, device=dev) for i, (n, k) in enumerate(shapes)]
+        xs = [synth.make_activations(m, k, seed=20 + i, device=dev) for i, (_, k) in enumerate(shapes)]
+        # what the gather must reproduce: every rank's rows computed here with the same kernel
+        # (the same plan, so the same summation order) and placed side by side
+        want = []
+        for (n, k), x, w in zip(shapes, xs, fulls):
+            kern = tb.gguf(m, n // world, k, "q4_k", op="gemv", device=dev)
+            want.append(torch.cat([kern(x, shard_weight_bytes(w, "q4_k", n, k, r, world).clone())
+                                   for r in range(world)], dim=1))
+            full = tb.gguf(m, n, k, "q4_k", op="gemv", device=dev)(x, w)
+            ok &= bool(torch.allclose(want[-1], full, rtol=1e-4, atol=1e-4))
+        lins = [QuantLinear(shard_weight_bytes(w, "q4_k", n, k, rank, world).clone(), "q4_k", n, k, m,
+                            rank=rank, world=world) for (n, k), w in zip(shapes, fulls)]
+        for lin, x, ref in zip(lins, xs, want):
+            ok &= bool(torch.equal(lin.forward(x), ref))
+        group = GatherGroup(lins[0:2])
+        outs = group.forward(xs[0:2])
+        ok &= bool(torch.equal(outs[0], want[0])) and bool(torch.equal(outs[1], want[1]))
+        # the same through peer stores + barrier; twice in a row, NaN-prefilled, to show that the
+        # second call does not read the first call's values
+        fused = FusedGatherGroup(lins, arena)
+        for _ in range(2):
+            for lin in lins:
+                lin.out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            outs = fused.forward(xs)
+            torch.cuda.synchronize()
+            for got, ref in zip(outs, want):
+                ok &= bool(torch.equal(got, ref))
+        ok &= tb.device_status() == 0
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    if rank == 0:
+        with open(result_path, "w") as f:
+            f.write(str(int(flag.item())))
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)  # leave without tearing NCCL down (nothing is in flight)
+
+
+@pytest.mark.timeout(240)
+def test_two_gpu_sharded_projection_is_bit_identical(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    path = str(tmp_path / "ok.txt")
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, path)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(200)
+    for p in procs:
+        if p.is_alive():
+            p.kill()  # the exact process this test started
+            pytest.fail("a rank did not finish")
+    assert open(path).read() == "1"
