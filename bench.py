@@ -64,8 +64,10 @@ def workload_config(world: int, gather: str = "fused"):
         "format": FORMAT, "batches": list(BATCHES), "activations": "bf16", "output": "fp32",
         "l2": "weights rotate over a ring of sets > 3x L2; every launch streams from HBM",
         "parallelism": f"N-sharded x{world}" + ("" if world == 1 else (
+            " + peer stores in the GEMV epilogue over NVLink, signal/wait between ranks inside the same launches"
+            if gather == "fused" else
             " + peer stores in the GEMV epilogue over NVLink and one barrier kernel after gate+up and after down"
-            if gather == "fused" else " + NCCL all-gather (gate+up together, then down)")),
+            if gather == "fused-barrier" else " + NCCL all-gather (gate+up together, then down)")),
     }
 
 
@@ -232,13 +234,15 @@ def run_gpu(args):
     lins = {b: [QuantLinear(weights[0][j], fmt, n, k, b, rank=rank, world=world, variant="auto")
                 for j, (_, n, k) in enumerate(SHAPES)] for b in BATCHES}
     launches_per_step = len(BATCHES) * len(SHAPES)
-    barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused" else 0
+    barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused-barrier" else 0
     # gate and up are needed together (one collective for both); down follows
-    if args.gather == "fused":
+    if args.gather in ("fused", "fused-barrier"):
         # the GEMVs store their columns into every rank's output; one barrier kernel per group
         out_bytes = sum(b * n * 4 + 256 for b in BATCHES for _, n, _ in SHAPES)
         arena = PeerArena(out_bytes + (1 << 16), device, rank, world)
-        groups = {b: [FusedGatherGroup(lins[b][0:2], arena), FusedGatherGroup(lins[b][2:3], arena)] for b in BATCHES}
+        fold = args.gather == "fused"  # ordering inside the GEMV launches; else one barrier kernel per group
+        groups = {b: [FusedGatherGroup(lins[b][0:2], arena, fold), FusedGatherGroup(lins[b][2:3], arena, fold)]
+                  for b in BATCHES}
     else:
         groups = {b: [GatherGroup(lins[b][0:2]), GatherGroup(lins[b][2:3])] for b in BATCHES}
 
@@ -438,8 +442,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", default="fused", choices=("fused", "nccl"),
-                    help="multi-GPU: peer stores inside the GEMV + barrier kernel, or NCCL all-gather")
+    ap.add_argument("--gather", default="fused", choices=("fused", "fused-barrier", "nccl"),
+                    help="multi-GPU: peer stores and signal/wait inside the GEMV launches; the same stores with a "
+                         "barrier kernel per group; or NCCL all-gather")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -178,6 +178,23 @@ int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void *x, 
                                 int64_t scratch_bytes, int32_t variant, void *stream,
                                 TensorErrorV1 *error);
 
+/* The same with the cross-GPU ordering folded into the launch, so that a decode step needs no
+ * barrier kernels: with TB200_PEER_WAIT the kernel waits, after filling its weight ring and before
+ * it reads x, until every peer has signalled as often as this rank has; with TB200_PEER_SIGNAL
+ * the last CTA to store its outputs signals every peer.  pads / rank / world are those of
+ * tb200_peer_barrier, and both forms count on the same pads, so they can be mixed: a signal by
+ * one and the matching wait by the other.  Typical step: gate (wait), up (signal), down (wait and
+ * signal).  The waits are bounded like the barrier's (status 0x80000 | peer).  Where the shape is
+ * served by the fallback kernel the same ordering is enforced with separate wait / signal launches. */
+#define TB200_PEER_WAIT 1
+#define TB200_PEER_SIGNAL 2
+int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void *x, const void *w,
+                                     float *const *outs, int32_t out_count, int64_t out_ld,
+                                     int64_t col_offset, int64_t m, int64_t n, int64_t k,
+                                     void *scratch, int64_t scratch_bytes, int32_t variant,
+                                     uint32_t *const *pads, int32_t rank, int32_t world,
+                                     int32_t sync, void *stream, TensorErrorV1 *error);
+
 /* Barrier between the GPUs of one box over peer-mapped signal pads.  pads is a HOST array of
  * `world` device addresses: pads[i] is rank i's pad (TB200_SIGNAL_PAD_BYTES, 4-byte aligned,
  * zero-filled once before the first use) as mapped into this process.  The kernel announces on
@@ -188,6 +205,10 @@ int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void *x, 
 #define TB200_SIGNAL_PAD_BYTES 256
 int32_t tb200_peer_barrier(uint32_t *const *pads, int32_t rank, int32_t world, void *stream,
                            TensorErrorV1 *error);
+/* One half of the barrier: mode TB200_PEER_SIGNAL announces, TB200_PEER_WAIT waits until every peer
+ * has announced as often as this rank has; both together are tb200_peer_barrier. */
+int32_t tb200_peer_sync(uint32_t *const *pads, int32_t rank, int32_t world, int32_t mode,
+                        void *stream, TensorErrorV1 *error);
 
 /* Peer mapping of host-owned device memory between the processes of one box (one process per
  * GPU), for the two entry points above.  tb200_peer_export writes the 64-byte CUDA IPC handle of

@@ -16,7 +16,8 @@ EXPORTS = (
     "tb200_gguf_device_status", "tb200_gguf_gemv_plan", "tb200_gguf_gemv_launch_config",
     "tb200_gguf_gemm_launch_config", "tb200_gguf_dequant", "tb200_gguf_gemv", "tb200_gguf_gemm",
     "tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1",
-    "tb200_gguf_gemv_static", "tb200_gguf_gemv_sharded", "tb200_peer_barrier",
+    "tb200_gguf_gemv_static", "tb200_gguf_gemv_sharded", "tb200_gguf_gemv_sharded_sync", "tb200_peer_barrier",
+    "tb200_peer_sync",
     "tb200_peer_export", "tb200_peer_open", "tb200_peer_close",
 )
 
@@ -74,6 +75,11 @@ def lib():
     handle.tb200_gguf_gemv_sharded.restype = i32
     handle.tb200_gguf_gemv_sharded.argtypes = [i32, i32, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i64, i64,
                                                vp, i64, i32, vp, err]
+    handle.tb200_gguf_gemv_sharded_sync.restype = i32
+    handle.tb200_gguf_gemv_sharded_sync.argtypes = [i32, i32, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i64, i64,
+                                                    vp, i64, i32, ctypes.POINTER(vp), i32, i32, i32, vp, err]
+    handle.tb200_peer_sync.restype = i32
+    handle.tb200_peer_sync.argtypes = [ctypes.POINTER(vp), i32, i32, i32, vp, err]
     handle.tb200_peer_barrier.restype = i32
     handle.tb200_peer_barrier.argtypes = [ctypes.POINTER(vp), i32, i32, vp, err]
     handle.tb200_peer_export.restype = i32

@@ -20,6 +20,7 @@ static_assert(sizeof(TensorArgumentV1) == 64, "TensorArgumentV1 layout");
 static_assert(sizeof(TensorStreamV1) == 16, "TensorStreamV1 layout");
 static_assert(sizeof(TensorCallV1) == 72, "TensorCallV1 layout");
 static_assert(sizeof(TensorErrorV1) == 512, "TensorErrorV1 layout");
+static_assert(tb200::kPeerWait == TB200_PEER_WAIT && tb200::kPeerSignal == TB200_PEER_SIGNAL, "sync bits");
 static_assert(tb200::kMaxOutputs == TB200_MAX_PEERS && tb200::kSignalWords * 4 == TB200_SIGNAL_PAD_BYTES, "peer limits");
 
 namespace tb200 {
@@ -236,7 +237,7 @@ namespace {
 // Shared by the plain and the sharded entry points: `out` says where the [m, n] result goes.
 int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* w, const OutSpec& out, int64_t m,
                     int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
-                    TensorErrorV1* error) {
+                    TensorErrorV1* error, const PeerSync* peers = nullptr) {
   if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
   if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
   for (int i = 0; i < out.count; ++i)
@@ -250,7 +251,7 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (variant != TB200_VARIANT_SIMPLE) {
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
     if (plan.supported) {
-      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st);
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch", e);
       return ok(error);
     }
@@ -259,9 +260,27 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
                   "the pipelined GEMV does not cover format %d, dtype %d, m=%lld, n=%lld, k=%lld", format, x_dtype,
                   (long long)m, (long long)n, (long long)k);
   }
+  // the fallback kernel knows nothing of peers: order it with separate launches
+  if (peers && (peers->flags & kPeerWait)) {
+    cudaError_t e = launch_peer_barrier(peers->pads, peers->rank, peers->world, kPeerWait, st);
+    if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
+  }
   cudaError_t e = launch_gemv_simple(format, x_dtype, x, wp, out, m, n, k, false, st);
   if (e != cudaSuccess) return cuda_fail(error, "GEMV launch", e);
+  if (peers && (peers->flags & kPeerSignal)) {
+    e = launch_peer_barrier(peers->pads, peers->rank, peers->world, kPeerSignal, st);
+    if (e != cudaSuccess) return cuda_fail(error, "peer signal launch", e);
+  }
   return ok(error);
+}
+
+int32_t check_pads(TensorErrorV1* error, uint32_t* const* pads, int32_t rank, int32_t world) {
+  if (!pads) return fail(error, TENSOR_ERROR_ARGUMENT, "pads is null");
+  if (world < 1 || world > TB200_MAX_PEERS || rank < 0 || rank >= world)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "rank %d of world %d (at most %d ranks)", rank, world, TB200_MAX_PEERS);
+  for (int i = 0; i < world; ++i)
+    if (int32_t s = check_pointer(error, "pad", pads[i], 4, true)) return s;
+  return TENSOR_OK;
 }
 
 int32_t check_gemv_scalars(TensorErrorV1* error, int32_t format, int32_t x_dtype, int64_t m, int64_t n, int64_t k,
@@ -285,10 +304,11 @@ int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void* x, const vo
                      error);
 }
 
-int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, const void* w, float* const* outs,
-                                int32_t out_count, int64_t out_ld, int64_t col_offset, int64_t m, int64_t n,
-                                int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
-                                TensorErrorV1* error) {
+int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w,
+                                     float* const* outs, int32_t out_count, int64_t out_ld, int64_t col_offset,
+                                     int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
+                                     int32_t variant, uint32_t* const* pads, int32_t rank, int32_t world,
+                                     int32_t sync, void* stream, TensorErrorV1* error) {
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n, k, variant)) return s;
   if (!outs) return fail(error, TENSOR_ERROR_ARGUMENT, "outs is null");
   if (out_count < 1 || out_count > TB200_MAX_PEERS)
@@ -296,7 +316,15 @@ int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, 
   if (col_offset < 0 || out_ld < col_offset + n)
     return fail(error, TENSOR_ERROR_ARGUMENT, "columns %lld..%lld do not fit a row of %lld", (long long)col_offset,
                 (long long)(col_offset + n), (long long)out_ld);
-  if (m == 0 || n == 0) return ok(error);
+  if (sync & ~(TB200_PEER_WAIT | TB200_PEER_SIGNAL)) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown sync bits 0x%x", sync);
+  PeerSync peers{};
+  if (sync) {
+    if (int32_t s = check_pads(error, pads, rank, world)) return s;
+    for (int i = 0; i < world; ++i) peers.pads[i] = pads[i];
+    peers.rank = rank;
+    peers.world = world;
+    peers.flags = world > 1 ? sync : 0;
+  }
   OutSpec spec{};
   spec.count = out_count;
   spec.ld = out_ld;
@@ -304,7 +332,42 @@ int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, 
     if (!outs[i]) return fail(error, TENSOR_ERROR_ARGUMENT, "outs[%d] is null", i);
     spec.ptr[i] = outs[i] + col_offset;
   }
-  return gemv_common(format, x_dtype, x, w, spec, m, n, k, scratch, scratch_bytes, variant, stream, error);
+  if (m == 0 || n == 0) {
+    // nothing to compute, but the peers still count on this rank's signal
+    if (peers.flags) {
+      const DeviceInfo* dev;
+      if (int32_t s = require_device(error, &dev)) return s;
+      cudaError_t e = launch_peer_barrier(peers.pads, rank, world, peers.flags, static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return cuda_fail(error, "peer sync launch", e);
+    }
+    return ok(error);
+  }
+  return gemv_common(format, x_dtype, x, w, spec, m, n, k, scratch, scratch_bytes, variant, stream, error,
+                     peers.flags ? &peers : nullptr);
+}
+
+int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, const void* w, float* const* outs,
+                                int32_t out_count, int64_t out_ld, int64_t col_offset, int64_t m, int64_t n,
+                                int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
+                                TensorErrorV1* error) {
+  return tb200_gguf_gemv_sharded_sync(format, x_dtype, x, w, outs, out_count, out_ld, col_offset, m, n, k, scratch,
+                                      scratch_bytes, variant, nullptr, 0, 1, 0, stream, error);
+}
+
+int32_t tb200_peer_sync(uint32_t* const* pads, int32_t rank, int32_t world, int32_t mode, void* stream,
+                        TensorErrorV1* error) {
+  if (int32_t s = check_pads(error, pads, rank, world)) return s;
+  if (!(mode & (TB200_PEER_WAIT | TB200_PEER_SIGNAL)) || (mode & ~(TB200_PEER_WAIT | TB200_PEER_SIGNAL)))
+    return fail(error, TENSOR_ERROR_ARGUMENT, "mode 0x%x is not TB200_PEER_WAIT, TB200_PEER_SIGNAL or both", mode);
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaError_t e = launch_peer_barrier(pads, rank, world, mode, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(error, "peer sync launch", e);
+  return ok(error);
+}
+
+int32_t tb200_peer_barrier(uint32_t* const* pads, int32_t rank, int32_t world, void* stream, TensorErrorV1* error) {
+  return tb200_peer_sync(pads, rank, world, TB200_PEER_WAIT | TB200_PEER_SIGNAL, stream, error);
 }
 
 int32_t tb200_peer_export(const void* ptr, uint8_t* handle, int64_t* offset, TensorErrorV1* error) {
@@ -337,19 +400,6 @@ int32_t tb200_peer_close(void* base, TensorErrorV1* error) {
   if (!base) return ok(error);
   cudaError_t e = cudaIpcCloseMemHandle(base);
   if (e != cudaSuccess) return cuda_fail(error, "cudaIpcCloseMemHandle", e);
-  return ok(error);
-}
-
-int32_t tb200_peer_barrier(uint32_t* const* pads, int32_t rank, int32_t world, void* stream, TensorErrorV1* error) {
-  if (!pads) return fail(error, TENSOR_ERROR_ARGUMENT, "pads is null");
-  if (world < 1 || world > TB200_MAX_PEERS || rank < 0 || rank >= world)
-    return fail(error, TENSOR_ERROR_ARGUMENT, "rank %d of world %d (at most %d ranks)", rank, world, TB200_MAX_PEERS);
-  for (int i = 0; i < world; ++i)
-    if (int32_t s = check_pointer(error, "pad", pads[i], 4, true)) return s;
-  const DeviceInfo* dev;
-  if (int32_t s = require_device(error, &dev)) return s;
-  cudaError_t e = launch_peer_barrier(pads, rank, world, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(error, "peer barrier launch", e);
   return ok(error);
 }
 

@@ -54,6 +54,11 @@ struct GemvArgs {
   int n_out;
   int out_vec;               // every destination takes 16-byte stores
   long long out_ld;          // elements between the batch rows of a destination
+  // N-sharded runs: signal pads of every rank (as mapped here), see peer_barrier.cu for the layout.
+  // sync bit 0: wait, before activations are read, until every peer has signalled as often as this
+  // rank has; bit 1: signal every peer once all CTAs of this launch have stored their outputs.
+  unsigned int* pads[kMaxOutputs];
+  int rank, world, sync;
   float* partials;
   unsigned int* counters;
   int m;
@@ -473,6 +478,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   uint64_t* xbar = red_empty + 2;       // activation rows have landed in shared memory
   uint64_t* fin = xbar + 1;             // reducer -> consumers: verdict on who adds the K ranges
   __shared__ int s_last;
+  __shared__ int s_exit;  // warps of this CTA that have stored everything they will store
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int W = a.consumer_warps;
@@ -488,6 +494,10 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   volatile float* unscale_slot = reinterpret_cast<volatile float*>(smem + a.off_misc);
 
   if (threadIdx.x == 0) {
+    s_exit = 0;
+    // all CTAs of this grid are resident at once, so the next kernel on the stream may be
+    // scheduled as CTAs of this one retire
+    ptx::grid_launch_dependents();
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(&full[s], 1);
       ptx::mbar_init(&empty[s], W);
@@ -556,22 +566,81 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     }
   };
 
+  // Peers (N-sharded runs).  wait_peers: one warp polls this rank's pad until every peer's count
+  // has reached this rank's own count of signals sent (bounded; gives up with status 0x80000|peer).
+  auto wait_peers = [&]() {
+    if (!(a.sync & 1)) return;
+    const unsigned int* mine = a.pads[a.rank];
+    const unsigned int expected = *reinterpret_cast<const volatile unsigned int*>(mine + 32);
+    if (lane < a.world && lane != a.rank) {
+      const unsigned long long t0 = ptx::global_timer_ns();
+      for (;;) {
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + lane) : "memory");
+        if ((int)(seen - expected) >= 0) break;
+        if (ptx::global_timer_ns() - t0 > ptx::kWaitLimitNs) {
+          report_timeout(0x80000u | (unsigned)lane);
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    __syncwarp();
+  };
+  // cta_done: every warp calls it on its normal way out.  The last warp of the CTA counts the CTA
+  // in; the last CTA of the grid bumps this rank's count and stores it into every peer's pad.
+  // Ordering is handed along that chain (CTA-scope fence -> shared counter -> GPU-scope fence ->
+  // global counter -> ONE system-scope fence -> flags): a system-scope fence per warp costs
+  // microseconds once a few thousand of them queue up.
+  auto cta_done = [&]() {
+    if (!(a.sync & 2)) return;
+    __syncwarp();
+    unsigned int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&s_exit, 1) == W + 1;
+    }
+    if (!__shfl_sync(0xffffffffu, last, 0)) return;
+    if (lane != 0) return;
+    unsigned int* mine = a.pads[a.rank];
+    __threadfence();
+    if (atomicAdd(mine + 34, 1u) != gridDim.x - 1) return;
+    __threadfence_system();
+    mine[34] = 0u;
+    const unsigned int epoch = mine[32] + 1u;
+    mine[32] = epoch;
+    for (int p = 0; p < a.world; ++p)
+      if (p != a.rank)
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.pads[p] + a.rank), "r"(epoch) : "memory");
+  };
+
   if (warp == W) {
     // ---------------- producer: bulk copies of the tile's weight rows ----------------
     const uint8_t* src0 = a.w + (long long)sb0 * kBlockBytes;
-    if constexpr (!GROUPS) {
-      // the activation rows go first: the decode warps cannot start before they have landed, and
-      // copies queue in issue order
-      const uint32_t x_row_bytes = (uint32_t)nsb_local * 512;
-      if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes);
-      __syncwarp();
-      if (lane < a.m)
-        ptx::bulk_g2s(smem + a.off_xs + (size_t)lane * a.xs_stride,
-                      static_cast<const uint16_t*>(a.x) + (long long)lane * a.k + sb0 * 256, x_row_bytes, xbar);
-    }
+    // Weights never depend on the kernel before this one, activations may: the ring is filled
+    // first (while the previous kernel drains, if this launch overlaps it), then the dependency
+    // wait, then the activation rows.
+    auto fetch_activations = [&]() {
+      ptx::grid_dependency_wait();
+      // one poller per CTA: thousands of warps polling the same pad would queue the peers' flag
+      // stores behind their loads
+      wait_peers();
+      if constexpr (GROUPS) {
+        if ((a.sync & 1) && lane == 0) ptx::mbar_arrive(xbar);  // releases the decode warps
+      } else {
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // the copies below read through the async proxy
+        const uint32_t x_row_bytes = (uint32_t)nsb_local * 512;
+        if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes);
+        __syncwarp();
+        if (lane < a.m)
+          ptx::bulk_g2s(smem + a.off_xs + (size_t)lane * a.xs_stride,
+                        static_cast<const uint16_t*>(a.x) + (long long)lane * a.k + sb0 * 256, x_row_bytes, xbar);
+      }
+    };
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int s = i % S;
+      if (i == S) fetch_activations();  // the ring is full; nothing frees a stage before activations arrive
       if (i >= S && !ptx::mbar_wait(&empty[s], ((i / S) - 1) & 1)) {
         report_timeout(0x10000u | (unsigned)s);
         break;
@@ -600,11 +669,14 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
           ptx::bulk_g2s(dst + (size_t)lane * a.stride_s, src0 + (row0 + lane) * a.row_bytes, range_bytes, &full[s]);
       }
     }
+    if (i <= S) fetch_activations();
+    cta_done();
     return;
   }
 
   if (warp == W + 1) {
     // ---------------- reducer: sum the consumer warps' partials in warp order, write out ----------------
+    ptx::grid_dependency_wait();  // outputs and scratch may still be in use by the kernel before
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int b = a.red_bufs == 2 ? (i & 1) : 0;
@@ -681,12 +753,22 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       }
       if (last) add_partials(W, W + 1);
     }
+    cta_done();
     return;
   }
 
   // ---------------- consumers ----------------
   const int cw = warp;
   if (cw >= W) return;
+  ptx::grid_dependency_wait();  // activations may come from the kernel before
+  if constexpr (GROUPS) {
+    // the decode warps read the activations themselves: hold them until the producer warp has
+    // seen the peers' signals
+    if ((a.sync & 1) && !ptx::mbar_wait(xbar, 0)) {
+      report_timeout(0x60000u);
+      return;
+    }
+  }
   const int ctid = threadIdx.x;
   uint32_t cphase = 0;
   // All consumer warps meet here; returns false if the (bounded) wait gave up.
@@ -813,6 +895,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     }
     if (*reinterpret_cast<volatile int*>(&s_last)) add_partials(cw, W + 1);
   }
+  cta_done();
 }
 
 template <int FMT, bool F16, int NT, bool GROUPS, bool WIDE>
@@ -899,6 +982,9 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
   a.n_out = 1;
   a.out_ld = n;
   a.out_vec = (n & 3) == 0;
+  a.rank = 0;
+  a.world = 1;
+  a.sync = 0;
   a.counters = reinterpret_cast<unsigned int*>(scratch);
   a.partials = reinterpret_cast<float*>(scratch + counter_bytes);
   a.m = m;
@@ -942,11 +1028,17 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
   const long long row_tiles = (n + kTileRows - 1) / kTileRows;
   if (row_tiles > 0x7fffffffLL) return best;
   double best_cost = 1e300;
+  // TB200_GEMV_FORCE="<k splits>:<CTAs per SM>" pins the plan search (tuning experiments only).
+  static const char* forced = getenv("TB200_GEMV_FORCE");
+  int force_splits = 0, force_per_sm = 0;
+  if (forced) sscanf(forced, "%d:%d", &force_splits, &force_per_sm);
   // Two CTAs per SM hide each other's barriers and reductions when the shared memory allows it.
   for (int per_sm = 2; per_sm >= 1; --per_sm) {
+    if (force_per_sm && per_sm != force_per_sm) continue;
     const int slots = dev.sm_count * per_sm;
     const int smem_limit = per_sm == 1 ? dev.max_smem_optin : (dev.max_smem_optin + 1024) / 2 - 1024;
     for (int splits = 1; splits <= nsb && splits <= 64; ++splits) {
+      if (force_splits && splits != force_splits) continue;
       const int per = (nsb + splits - 1) / splits;
       if ((splits - 1) * per >= nsb) continue;  // an empty K range
       const long long need =
@@ -997,6 +1089,15 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
   return best;
 }
 
+// TB200_GEMV_NO_OVERLAP=1 in the environment launches every GEMV fully serialized (for A/B timing).
+static bool overlap_launches() {
+  static const bool on = [] {
+    const char* v = getenv("TB200_GEMV_NO_OVERLAP");
+    return !(v && *v && *v != '0');
+  }();
+  return on;
+}
+
 template <int FMT, bool F16, int NT, bool GROUPS, bool WIDE>
 static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t stream) {
   auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS, WIDE>;
@@ -1011,8 +1112,20 @@ static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t 
                             (unsigned long long)a.row_bytes, box_inner, kTileRows, false))
       return cudaErrorNotSupported;
   }
-  kernel<<<grid, (a.consumer_warps + 2) * 32, smem, stream>>>(a, wmap);
-  return cudaGetLastError();
+  // Programmatic serialization: this kernel may start (barrier setup, filling its weight ring)
+  // while the previous kernel on the stream drains; it waits for that kernel before it touches
+  // activations, outputs or scratch.  Works the same inside a stream capture.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)((a.consumer_warps + 2) * 32));
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, a, wmap);
 }
 
 static int fill_args(GemvArgs& a, const GemvPlan& plan, int fmt, long long m, long long n, long long k);
@@ -1032,10 +1145,18 @@ bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n,
 
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const PeerSync* peers) {
   if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
   if (out.count < 1 || out.count > kMaxOutputs || out.ld < n) return cudaErrorInvalidValue;
   GemvArgs a{};
+  if (peers && peers->flags) {
+    if (peers->world < 1 || peers->world > kMaxOutputs || peers->rank < 0 || peers->rank >= peers->world)
+      return cudaErrorInvalidValue;
+    for (int i = 0; i < peers->world; ++i) a.pads[i] = peers->pads[i];
+    a.rank = peers->rank;
+    a.world = peers->world;
+    a.sync = peers->flags;
+  }
   const int smem_total = fill_args(a, plan, fmt, m, n, k);
   a.x = x;
   a.w = w;

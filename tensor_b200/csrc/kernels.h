@@ -64,9 +64,19 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
                         long long scratch_bytes_available, const DeviceInfo& dev);
 // All launch constants of a plan (grid, threads, shared memory, ring layout ...): see tbin.py.
 bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n, long long k, int* out32);
+// Cross-GPU ordering folded into a GEMV launch (N-sharded runs): pads[i] is rank i's signal pad as
+// mapped here; flags bit 0 = wait for the peers before reading activations, bit 1 = signal the
+// peers after the last output store.
+constexpr int kPeerWait = 1, kPeerSignal = 2;
+struct PeerSync {
+  unsigned int* pads[kMaxOutputs];
+  int rank;
+  int world;
+  int flags;
+};
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
-                             cudaStream_t stream);
+                             cudaStream_t stream, const PeerSync* peers = nullptr);
 inline cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                                     float* out, long long m, long long n, long long k, void* scratch,
                                     cudaStream_t stream) {
@@ -77,7 +87,8 @@ inline cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const
 // once): every rank tells every peer that all work it enqueued before is complete and visible,
 // then waits (bounded) until every peer has said the same.  pads[i] is rank i's pad as mapped here.
 constexpr int kSignalWords = 64;
-cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, cudaStream_t stream);
+// mode: kPeerSignal | kPeerWait (a full barrier), or one of them alone
+cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, int mode, cudaStream_t stream);
 
 // tcgen05 / TMEM prefill GEMM (bf16 operands, fp32 accumulate).
 // {grid.x, grid.y, threads, dynamic shared memory, token tile, k per stage, 0, 0}

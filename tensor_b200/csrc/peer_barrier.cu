@@ -5,8 +5,13 @@
 //
 // One signal pad per rank (kSignalWords uint32, zeroed once before the first use, never reset):
 //   word j < world : epoch last announced by rank j (written by rank j through its peer mapping)
-//   word 32        : this rank's own epoch counter (device-resident so that a captured launch can
-//                    be replayed: nothing about the epoch is baked into the launch)
+//   word 32        : this rank's own epoch counter = signals it has sent (device-resident so that
+//                    a captured launch can be replayed: nothing about the epoch is baked into it)
+//   word 34        : CTAs of the running GEMV that have stored their outputs (used when the signal
+//                    is folded into the GEMV, see gemv_mma.cu; back to zero after every launch)
+// The two halves can be used apart: a signal (count up, tell the peers) once this rank's stores are
+// done, and a wait (until every peer's count has reached this rank's own) before anything reads
+// what the peers stored; the pipelined GEMV does both inside its own launch.
 // A launch on rank r: epoch = ++pad_r[32]; fence; release-store epoch into pad_j[r] for every peer j;
 // then wait until pad_r[j] has reached epoch for every j.  Epochs only grow, so a peer that is
 // already one barrier ahead satisfies the wait.  Everything enqueued on the stream before the
@@ -29,20 +34,28 @@ struct BarrierArgs {
   unsigned int* pads[kMaxOutputs];
   int rank;
   int world;
+  int mode;
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
+  // launched with programmatic serialization: wait for the kernel before (whose peer stores this
+  // barrier publishes), and let the kernel after start its own independent prologue
+  ptx::grid_dependency_wait();
+  if (threadIdx.x == 0) ptx::grid_launch_dependents();
   unsigned int* mine = a.pads[a.rank];
   unsigned int epoch = 0;
   if (threadIdx.x == 0) {
-    epoch = mine[32] + 1u;
-    mine[32] = epoch;
+    epoch = mine[32];
+    if (a.mode & kPeerSignal) mine[32] = ++epoch;
   }
   epoch = __shfl_sync(0xffffffffu, epoch, 0);
   const int peer = (int)threadIdx.x;
   if (peer >= a.world || peer == a.rank) return;
-  __threadfence_system();
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.pads[peer] + a.rank), "r"(epoch) : "memory");
+  if (a.mode & kPeerSignal) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.pads[peer] + a.rank), "r"(epoch) : "memory");
+  }
+  if (!(a.mode & kPeerWait)) return;
   const unsigned long long t0 = ptx::global_timer_ns();
   const unsigned int* slot = mine + peer;
   for (;;) {
@@ -59,15 +72,25 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
 
 }  // namespace
 
-cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, cudaStream_t stream) {
+cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, int mode, cudaStream_t stream) {
   if (world < 1 || world > kMaxOutputs || rank < 0 || rank >= world) return cudaErrorInvalidValue;
+  if (!(mode & (kPeerSignal | kPeerWait))) return cudaErrorInvalidValue;
   if (world == 1) return cudaSuccess;
   BarrierArgs a{};
   for (int i = 0; i < world; ++i) a.pads[i] = pads[i];
   a.rank = rank;
   a.world = world;
-  peer_barrier_kernel<<<1, 32, 0, stream>>>(a);
-  return cudaGetLastError();
+  a.mode = mode;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, peer_barrier_kernel, a);
 }
 
 TB200_DEFINE_STATUS_READER(read_barrier_status)

@@ -58,6 +58,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while the kernel
+// before it on the stream is still running.  grid_dependency_wait() returns once that kernel has
+// completed and its writes are visible; everything that reads data a predecessor may have written,
+// or writes anything a predecessor may read, must come after it.  Launched without the attribute,
+// both instructions do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- async proxy ------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -174,12 +174,18 @@ def gemm(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out: torch.
 _X_DTYPE_IDS = {torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
 
 
+PEER_WAIT, PEER_SIGNAL = 1, 2
+
+
 def gemv_sharded(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out_ptrs, out_ld: int,
-                 col_offset: int, scratch: torch.Tensor | None = None, variant="auto", stream=None) -> None:
+                 col_offset: int, scratch: torch.Tensor | None = None, variant="auto", stream=None,
+                 pad_ptrs=None, rank: int = 0, sync: int = 0) -> None:
     """The GEMV of one rank of an N-sharded projection: ``w`` holds this rank's ``n`` rows and the
     ``[m, n]`` result goes to columns ``col_offset .. col_offset + n`` of every ``[m, out_ld]`` fp32
     matrix whose device address is in ``out_ptrs`` (own output first, then the other ranks' outputs
-    as mapped by :class:`tensor_b200.peer.PeerArena`).  See ``tb200_gguf_gemv_sharded``."""
+    as mapped by :class:`tensor_b200.peer.PeerArena`).  ``sync`` folds the cross-GPU ordering into
+    the launch (``PEER_WAIT`` before the activations are read, ``PEER_SIGNAL`` after the last
+    store) over the signal pads ``pad_ptrs`` (rank order).  See ``tb200_gguf_gemv_sharded_sync``."""
     fmt = get_format(encoding)
     m = _infer_m(x, k)
     _require_cuda("x", x)
@@ -190,24 +196,35 @@ def gemv_sharded(x: torch.Tensor, w: torch.Tensor, encoding, n: int, k: int, out
         x_dtype = _X_DTYPE_IDS[x.dtype]
     except KeyError:
         raise ValueError(f"unsupported activation dtype {x.dtype}") from None
+    if sync and pad_ptrs is None:
+        raise ValueError("sync needs the signal pads")
     device = _same_device(x, w, scratch)
     ptrs = [int(p) for p in out_ptrs]
     table = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
+    pads = [int(p) for p in (pad_ptrs or [])]
+    pad_table = (ctypes.c_void_p * max(len(pads), 1))(*pads)
     error = abi.TensorErrorV1()
     with torch.cuda.device(device):
-        status = lib().tb200_gguf_gemv_sharded(
+        status = lib().tb200_gguf_gemv_sharded_sync(
             fmt.type_id, x_dtype, x.data_ptr(), w.data_ptr(), table, len(ptrs), out_ld, col_offset, m, n, k,
             scratch.data_ptr() if scratch is not None else None, scratch.numel() if scratch is not None else 0,
-            _VARIANTS[variant], _stream_handle(device, stream), ctypes.byref(error))
+            _VARIANTS[variant], pad_table if pads else None, rank, max(len(pads), 1), sync,
+            _stream_handle(device, stream), ctypes.byref(error))
     raise_for_status(status, error)
 
 
-def peer_barrier(pad_ptrs, rank: int, device: torch.device, stream=None) -> None:
-    """Enqueue the cross-GPU barrier (``tb200_peer_barrier``) on ``stream``; ``pad_ptrs[i]`` is the
-    address of rank i's signal pad as mapped in this process."""
+def peer_sync(pad_ptrs, rank: int, device: torch.device, mode: int = PEER_WAIT | PEER_SIGNAL, stream=None) -> None:
+    """Enqueue one or both halves of the cross-GPU barrier (``tb200_peer_sync``) on ``stream``;
+    ``pad_ptrs[i]`` is the address of rank i's signal pad as mapped in this process."""
     ptrs = [int(p) for p in pad_ptrs]
     table = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
     error = abi.TensorErrorV1()
     with torch.cuda.device(device):
-        status = lib().tb200_peer_barrier(table, rank, len(ptrs), _stream_handle(device, stream), ctypes.byref(error))
+        status = lib().tb200_peer_sync(table, rank, len(ptrs), mode, _stream_handle(device, stream),
+                                       ctypes.byref(error))
     raise_for_status(status, error)
+
+
+def peer_barrier(pad_ptrs, rank: int, device: torch.device, stream=None) -> None:
+    """Signal and wait (``tb200_peer_barrier``)."""
+    peer_sync(pad_ptrs, rank, device, PEER_WAIT | PEER_SIGNAL, stream)

@@ -156,17 +156,21 @@ class GatherGroup:
 class FusedGatherGroup:
     """The same contract as :class:`GatherGroup` without a collective call: every projection's kernel
     stores its columns into every rank's ``[m, N]`` output over NVLink (peer-mapped memory from a
-    :class:`tensor_b200.peer.PeerArena`) and ONE barrier kernel per group orders those stores before
-    whatever reads the outputs next.  A decode step moves a few KB per projection, so what the step
-    pays for is latency: the stores ride inside the GEMV and the barrier is a single small launch.
+    :class:`tensor_b200.peer.PeerArena`), and the ordering between ranks rides in the same launches:
+    the group's first GEMV waits for the peers' previous signal before it reads its activations,
+    its last GEMV signals the peers once every output is stored.  A decode step moves a few KB per
+    projection, so what the step pays for is latency: no extra launch, and the wait sits behind the
+    kernel's weight prefetch.  With ``fold_sync=False`` one barrier kernel follows the group instead.
 
-    Outputs are reused from call to call.  Correct reuse needs a barrier between two writes of the
-    same buffer by any rank, with the reader's use of the first value enqueued before its side of
-    that barrier: one call of ``forward`` per group and step gives exactly that."""
+    Whatever reads the outputs must run after a wait: the next group's first GEMV (folded), or
+    :meth:`wait` for any other consumer.  Outputs are reused from call to call; that is safe because
+    a rank's next write to a peer's buffer comes after it has seen that peer's following signal,
+    which the peer sends after it has consumed the buffer."""
 
-    def __init__(self, linears, arena):
+    def __init__(self, linears, arena, fold_sync: bool = True):
         self.linears = list(linears)
         self.arena = arena
+        self.fold_sync = fold_sync
         first = self.linears[0]
         self.world, self.rank, self.device = first.world, first.rank, first.device
         if arena.world != self.world or arena.rank != self.rank or arena.device != self.device:
@@ -183,13 +187,23 @@ class FusedGatherGroup:
         self._pads = arena.pad_ptrs()
 
     def forward(self, xs, raws=None):
+        last = len(self.linears) - 1
         for i, l in enumerate(self.linears):
             raw = l.raw if raws is None or raws[i] is None else raws[i]
+            sync = 0
+            if self.fold_sync and self.world > 1:
+                sync = (ops.PEER_WAIT if i == 0 else 0) | (ops.PEER_SIGNAL if i == last else 0)
             ops.gemv_sharded(xs[i], raw, l.format, l.n_local, l.k, self._targets[i], l.n, l.rank * l.n_local,
-                             scratch=l.kernel._scratch, variant=l.kernel.variant)
-        if self.world > 1:
+                             scratch=l.kernel._scratch, variant=l.kernel.variant,
+                             pad_ptrs=self._pads if sync else None, rank=self.rank, sync=sync)
+        if self.world > 1 and not self.fold_sync:
             ops.peer_barrier(self._pads, self.rank, self.device)
         return [l.out for l in self.linears]
+
+    def wait(self) -> None:
+        """Enqueue the wait a consumer other than the next group needs (no-op after a barrier)."""
+        if self.world > 1 and self.fold_sync:
+            ops.peer_sync(self._pads, self.rank, self.device, ops.PEER_WAIT)
 
     __call__ = forward
 

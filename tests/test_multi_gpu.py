@@ -33,7 +33,7 @@ def _rank_main(rank, world, port, result_path):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     ok = True
-    arena = PeerArena(4 << 20, dev, rank, world)
+    arena = PeerArena(8 << 20, dev, rank, world)
     shapes = [(2048, 3584), (2048, 3584), (1024, 4096)]
     for m in (1, 4):
         fulls = [synth.make_weights("q4_k", n, k, seed=10 + i, device=dev) for i, (n, k) in enumerate(shapes)]
@@ -56,16 +56,18 @@ def _rank_main(rank, world, port, result_path):
         ok &= bool(torch.equal(outs[0], want[0])) and bool(torch.equal(outs[1], want[1]))
         # the same through peer stores + barrier; twice in a row, NaN-prefilled, to show that the
         # second call does not read the first call's values
-        fused = FusedGatherGroup(lins, arena)
-        for _ in range(2):
-            for lin in lins:
-                lin.out.fill_(float("nan"))
-            torch.cuda.synchronize()
-            dist.barrier()
-            outs = fused.forward(xs)
-            torch.cuda.synchronize()
-            for got, ref in zip(outs, want):
-                ok &= bool(torch.equal(got, ref))
+        for fold in (False, True):
+            fused = FusedGatherGroup(lins, arena, fold_sync=fold)
+            for _ in range(2):
+                for lin in lins:
+                    lin.out.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                outs = fused.forward(xs)
+                fused.wait()
+                torch.cuda.synchronize()
+                for got, ref in zip(outs, want):
+                    ok &= bool(torch.equal(got, ref))
         ok &= tb.device_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
