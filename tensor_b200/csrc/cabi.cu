@@ -188,7 +188,8 @@ int32_t tb200_gguf_gemv_launch_config(int32_t format, int32_t x_dtype, int64_t m
   b200.sm_count = 148;
   b200.max_smem_optin = 232448;
   b200.cc_major = 10;
-  GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch_bytes, b200);
+  // a packaged kernel is a single launch: no conversion kernel ahead of it
+  GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch_bytes, b200, false);
   return gemv_launch_config(plan, format, m, n, k, out32) ? TENSOR_OK : TENSOR_ERROR_ARGUMENT;
 }
 

@@ -59,6 +59,9 @@ struct GemvArgs {
   // rank has; bit 1: signal every peer once all CTAs of this launch have stored their outputs.
   unsigned int* pads[kMaxOutputs];
   int rank, world, sync;
+  // batch plans: activations converted ahead of this launch (see gemv_prepare_kernel); null = convert here
+  const uint16_t* x16;
+  const float2* x_table;
   float* partials;
   unsigned int* counters;
   int m;
@@ -218,6 +221,81 @@ __device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* sm
       }
     }
   }
+  return true;
+}
+
+// The same conversion done ONCE per GEMV by a small kernel of its own, into global scratch, in
+// exactly the layout the CTAs keep in shared memory: x16[b][k] (fp16, each aligned group of four
+// stored as [x0, x2, x1, x3]) and table[k / 32][NTB] = {sum of the staged values, unscale}, with
+// {0, 1} for the columns past m.  One thread per 8 values; K / 8 is a multiple of 32, so a warp is
+// all-valid or all-invalid and the quad shuffles are safe.
+#ifndef TB200_TBIN_WRAPPER
+template <bool F16>
+__global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
+                                                           float2* __restrict__ table, int m, int k, int ntb) {
+  ptx::grid_dependency_wait();  // x may come from the kernel before; the GEMV before may still read x16
+  if (threadIdx.x == 0) ptx::grid_launch_dependents();
+  const int chunks = k >> 3;
+  const int live = m * chunks;
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid < live) {
+    const int b = tid / chunks, c = tid - b * chunks;
+    uint4 v = *reinterpret_cast<const uint4*>(x + (long long)b * k + (c << 3));
+    float scale = 1.f, unscale = 1.f;
+    if constexpr (!F16) {
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t mx = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const int e = (int)(mx >> 7);
+      if (e > 0 && e < 255) {
+        int sh = 141 - e;
+        sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+        scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+        unscale = __uint_as_float((uint32_t)(127 - sh) << 23);
+      }
+    }
+    v = to_f16x8<F16>(v, scale);
+    float sum = sum_f16x8(v);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    uint4 p;
+    p.x = __byte_perm(v.x, v.y, 0x5410);
+    p.y = __byte_perm(v.x, v.y, 0x7632);
+    p.z = __byte_perm(v.z, v.w, 0x5410);
+    p.w = __byte_perm(v.z, v.w, 0x7632);
+    *reinterpret_cast<uint4*>(x16 + (long long)b * k + (c << 3)) = p;
+    if ((c & 3) == 0) table[(long long)(c >> 2) * ntb + b] = make_float2(sum, unscale);
+  }
+  // columns past m: zero sums
+  const int groups = k >> 5, spare = ntb - m;
+  for (int i = tid; i < groups * spare; i += gridDim.x * blockDim.x) {
+    const int g = i / spare, b = m + (i - g * spare);
+    table[(long long)g * ntb + b] = make_float2(0.f, 1.f);
+  }
+}
+#endif  // TB200_TBIN_WRAPPER
+
+// Batch staging when the activations were converted ahead of the launch: the producer warp copies
+// this CTA's K range of x16 and of the table into place; the decode warps only clear the rows past m.
+template <int NTB>
+__device__ __forceinline__ bool stage_prepared(const GemvArgs& a, uint8_t* smem, int ctid, int klen, uint64_t* xbar) {
+  const int threads = a.consumer_warps * 32;
+  const int chunks = klen >> 3;
+  uint8_t* xs = smem + a.off_xs;
+  for (int idx = a.m * chunks + ctid; idx < NTB * chunks; idx += threads) {
+    const int b = idx / chunks, c = idx - b * chunks;
+    *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = make_uint4(0, 0, 0, 0);
+  }
+  if (!ptx::mbar_wait(xbar, 0)) {
+    report_timeout(0x60000u);
+    return false;
+  }
+#ifdef TB200_GEMV_TRACE
+  if (a.trace && blockIdx.x == 0 && ctid == 0) a.trace[2] = ptx::global_timer_ns();
+#endif
   return true;
 }
 
@@ -630,11 +708,15 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       } else {
         asm volatile("fence.proxy.async.global;" ::: "memory");  // the copies below read through the async proxy
         const uint32_t x_row_bytes = (uint32_t)nsb_local * 512;
-        if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes);
+        const uint32_t table_bytes = a.x16 ? (uint32_t)nsb_local * 8 * NTB * 8 : 0u;
+        const uint16_t* src = a.x16 ? a.x16 : static_cast<const uint16_t*>(a.x);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes + table_bytes);
         __syncwarp();
         if (lane < a.m)
-          ptx::bulk_g2s(smem + a.off_xs + (size_t)lane * a.xs_stride,
-                        static_cast<const uint16_t*>(a.x) + (long long)lane * a.k + sb0 * 256, x_row_bytes, xbar);
+          ptx::bulk_g2s(smem + a.off_xs + (size_t)lane * a.xs_stride, src + (long long)lane * a.k + sb0 * 256,
+                        x_row_bytes, xbar);
+        if (a.x16 && lane == 31)
+          ptx::bulk_g2s(smem + a.off_sx, a.x_table + (long long)sb0 * 8 * NTB, table_bytes, xbar);
       }
     };
     int i = 0;
@@ -753,6 +835,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       }
       if (last) add_partials(W, W + 1);
     }
+    TB200_TRACE(lane == 0, 72);
     cta_done();
     return;
   }
@@ -761,6 +844,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   const int cw = warp;
   if (cw >= W) return;
   ptx::grid_dependency_wait();  // activations may come from the kernel before
+  TB200_TRACE(threadIdx.x == 0, 7);
   if constexpr (GROUPS) {
     // the decode warps read the activations themselves: hold them until the producer warp has
     // seen the peers' signals
@@ -784,7 +868,11 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     stage_activations_groups<F16>(a, smem, ctid, sb0 * 256, nsb_local * 256);
     if (ctid == 0) *unscale_slot = 1.f;  // scaling is undone per group inside the item
   } else {
-    if (!stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, xbar)) return;
+    if (a.x16) {
+      if (!stage_prepared<NTB>(a, smem, ctid, nsb_local * 256, xbar)) return;
+    } else if (!stage_activations<F16, NTB>(a, smem, ctid, sb0 * 256, nsb_local * 256, xbar)) {
+      return;
+    }
     if (ctid == 0) *unscale_slot = 1.f;  // scaling is undone per group inside the item
   }
   if (!consumer_sync()) return;
@@ -985,6 +1073,8 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
   a.rank = 0;
   a.world = 1;
   a.sync = 0;
+  a.x16 = nullptr;
+  a.x_table = nullptr;
   a.counters = reinterpret_cast<unsigned int*>(scratch);
   a.partials = reinterpret_cast<float*>(scratch + counter_bytes);
   a.m = m;
@@ -1017,7 +1107,7 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
 TB200_DEFINE_STATUS_READER(read_gemv_status)
 
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
-                        long long scratch_bytes_available, const DeviceInfo& dev) {
+                        long long scratch_bytes_available, const DeviceInfo& dev, bool allow_prep) {
   GemvPlan best;
   if (fmt != kQ4_K) return best;
   if (xt != kBF16 && xt != kF16) return best;
@@ -1027,6 +1117,12 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
   const int nsb = (int)(k / 256);
   const long long row_tiles = (n + kTileRows - 1) / kTileRows;
   if (row_tiles > 0x7fffffffLL) return best;
+  // converted activations + table, placed after the counters and the partial sums
+  const int ntb = m <= 8 ? 8 : 16;
+  const long long prep_x_bytes = (m * k * 2 + 255) / 256 * 256;
+  // (worth a launch of its own only for the larger batches: up to 8 rows the CTAs convert faster than
+  // an extra kernel takes to come and go)
+  const long long prep_bytes = (allow_prep && m > 8) ? prep_x_bytes + ((k / 32) * ntb * 8 + 255) / 256 * 256 : 0;
   double best_cost = 1e300;
   // TB200_GEMV_FORCE="<k splits>:<CTAs per SM>" pins the plan search (tuning experiments only).
   static const char* forced = getenv("TB200_GEMV_FORCE");
@@ -1080,6 +1176,15 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
         best.stage_bytes = L.stage_bytes;
         best.smem_bytes = L.total;
         best.scratch_bytes = need;
+        best.prep_x_offset = best.prep_table_offset = 0;
+        if (prep_bytes) {
+          const long long base = need ? need : kCounterBytes;  // keep the counter page even without a split
+          if (base + prep_bytes <= scratch_bytes_available) {
+            best.prep_x_offset = base;
+            best.prep_table_offset = base + prep_x_bytes;
+            best.scratch_bytes = base + prep_bytes;
+          }
+        }
         best.ctas_per_sm = per_sm;
         best.consumer_warps = warps;
         best.red_bufs = red_bufs;
@@ -1177,8 +1282,9 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
         for (int c = 0; c < 3; ++c) {
           const unsigned long long* d = host + c * 80;
           if (!d[0]) continue;
-          printf("trace cta %d: activations landed +%llu ns, staged +%llu ns; conversion rounds at +%llu +%llu +%llu +%llu\n",
-                 c * 100, d[2] ? d[2] - d[0] : 0ull, d[1] - d[0], d[3] - d[0], d[4] - d[0], d[5] - d[0], d[6] - d[0]);
+          printf("trace cta %d (start %llu): dependency resolved +%llu ns, activations landed +%llu ns, staged +%llu ns; conversion rounds at +%llu +%llu +%llu +%llu; last warp out +%llu\n",
+                 c * 100, d[0] % 1000000ull, d[7] ? d[7] - d[0] : 0ull, d[2] ? d[2] - d[0] : 0ull, d[1] - d[0], d[3] - d[0], d[4] - d[0], d[5] - d[0], d[6] - d[0],
+                 d[72] ? d[72] - d[0] : 0ull);
           for (int i = 0; i < 16 && d[8 + i]; ++i)
             printf("  tile %2d: copy issued +%6llu  data ready +%6llu  decoded +%6llu  reduced +%6llu\n", i,
                    d[56 + i] - d[0], d[8 + i] - d[0], d[24 + i] - d[0], d[40 + i] - d[0]);
@@ -1192,6 +1298,28 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     if (!scratch) return cudaErrorInvalidValue;
     a.counters = static_cast<unsigned int*>(scratch);
     a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kCounterBytes);
+  }
+  if (plan.prep_x_offset) {
+    if (!scratch || m < 2) return cudaErrorInvalidValue;
+    uint16_t* x16 = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(scratch) + plan.prep_x_offset);
+    float2* table = reinterpret_cast<float2*>(static_cast<uint8_t*>(scratch) + plan.prep_table_offset);
+    const int ntb = m <= 8 ? 8 : 16;
+    const long long threads = m * (k / 8);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_launches() ? 1 : 0;
+    const uint16_t* xin = static_cast<const uint16_t*>(x);
+    cudaError_t e = xt == kF16 ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, (int)m, (int)k, ntb)
+                               : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, (int)m, (int)k, ntb);
+    if (e != cudaSuccess) return e;
+    a.x16 = x16;
+    a.x_table = table;
   }
   const int grid = plan.k_splits * plan.row_groups;
   const bool f16 = xt == kF16;

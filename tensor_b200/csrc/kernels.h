@@ -59,9 +59,15 @@ struct GemvPlan {
   int ctas_per_sm = 1;
   int consumer_warps = 8;
   int red_bufs = 2;
+  // Batch plans (8 < m <= 16) with scratch to spare: a small kernel ahead of the GEMV converts the
+  // activations once (fp16, scaled per 32-value group, fragment order) and every CTA copies the
+  // result, instead of every CTA converting all of them.  Offsets into the scratch buffer; 0 = the
+  // CTAs convert on their own.
+  long long prep_x_offset = 0;
+  long long prep_table_offset = 0;
 };
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
-                        long long scratch_bytes_available, const DeviceInfo& dev);
+                        long long scratch_bytes_available, const DeviceInfo& dev, bool allow_prep = true);
 // All launch constants of a plan (grid, threads, shared memory, ring layout ...): see tbin.py.
 bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n, long long k, int* out32);
 // Cross-GPU ordering folded into a GEMV launch (N-sharded runs): pads[i] is rank i's signal pad as
