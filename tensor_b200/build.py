@@ -70,6 +70,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         # diagnostic build: the GEMV records a per-CTA timeline and prints it at process exit
         if "-DTB200_GEMV_TRACE" not in COMMON:
             COMMON.append("-DTB200_GEMV_TRACE")
+    for extra in os.environ.get("TB200_EXTRA_DEFINES", "").split():
+        # experiment switches, e.g. TB200_EXTRA_DEFINES="TB200_SHIFT_BY_MULTIPLY"
+        if f"-D{extra}" not in COMMON:
+            COMMON.append(f"-D{extra}")
     os.makedirs(LIB_DIR, exist_ok=True)
     stamp = os.path.join(LIB_DIR, "build.sha256")
     fp = _fingerprint()

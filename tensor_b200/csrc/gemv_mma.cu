@@ -233,8 +233,11 @@ __device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* sm
 template <bool F16>
 __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
                                                            float2* __restrict__ table, int m, int k, int ntb) {
-  ptx::grid_dependency_wait();  // x may come from the kernel before; the GEMV before may still read x16
+  // Let the GEMV behind this kernel start at once (it fills its weight ring, then waits for this
+  // kernel to complete, which in turn has waited for the kernel before): the trigger must come
+  // before the wait, or the GEMV could not be scheduled until the previous kernel has drained.
   if (threadIdx.x == 0) ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // x may come from the kernel before; the GEMV before may still read x16
   const int chunks = k >> 3;
   const int live = m * chunks;
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -311,10 +314,17 @@ __device__ __forceinline__ void stage_activations_groups(const GemvArgs& a, uint
   uint8_t* xs = smem + a.off_xs;
   float2* sxu = reinterpret_cast<float2*>(smem + a.off_sx);
   const uint16_t* xg = static_cast<const uint16_t*>(a.x);
-  for (int base = 0; base < chunks; base += threads) {
+  // the first two rounds' loads go out together (one round trip instead of two)
+  uint4 ahead[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+    if (r * threads + ctid < chunks) ahead[r] = *reinterpret_cast<const uint4*>(xg + k0 + ((r * threads + ctid) << 3));
+  int round = 0;
+  for (int base = 0; base < chunks; base += threads, ++round) {
     const int c = base + ctid;  // chunks is a multiple of 32: a warp is all-valid or all-invalid
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (c < chunks) v = *reinterpret_cast<const uint4*>(xg + k0 + (c << 3));
+    if (round < 2) v = round ? ahead[1] : ahead[0];
+    else if (c < chunks) v = *reinterpret_cast<const uint4*>(xg + k0 + (c << 3));
     float scale = 1.f, unscale = 1.f;
     if constexpr (!F16) {
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -384,7 +394,7 @@ struct Nibbles {
 };
 __device__ __forceinline__ Nibbles split_nibbles(uint32_t w, const NibbleConsts& k) {
   Nibbles r;
-  const uint32_t w8 = w >> 8;
+  const uint32_t w8 = w >> 8;  // (w * 2^24 >> 32 on the multiplier pipe was measured slower)
   r.lo02 = and_or(w, k.lo, k.bits);
   r.hi02 = and_or(w, k.hi, k.bits);
   r.lo13 = and_or(w8, k.lo, k.bits);
@@ -722,7 +732,11 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int s = i % S;
-      if (i == S) fetch_activations();  // the ring is full; nothing frees a stage before activations arrive
+      // Batch mode: the ring is filled first (nothing frees a stage before the activations arrive).
+      // m == 1: the decode warps load x themselves and their loads would come back behind every
+      // weight byte already requested by this SM, so one stage is held back until the dependency
+      // has resolved and those loads are on their way.
+      if (i == (GROUPS && S > 2 ? S - 1 : S)) fetch_activations();
       if (i >= S && !ptx::mbar_wait(&empty[s], ((i / S) - 1) & 1)) {
         report_timeout(0x10000u | (unsigned)s);
         break;
@@ -751,7 +765,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
           ptx::bulk_g2s(dst + (size_t)lane * a.stride_s, src0 + (row0 + lane) * a.row_bytes, range_bytes, &full[s]);
       }
     }
-    if (i <= S) fetch_activations();
+    if (i <= (GROUPS && S > 2 ? S - 1 : S)) fetch_activations();
     cta_done();
     return;
   }

@@ -38,10 +38,11 @@ struct BarrierArgs {
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
-  // launched with programmatic serialization: wait for the kernel before (whose peer stores this
-  // barrier publishes), and let the kernel after start its own independent prologue
-  ptx::grid_dependency_wait();
+  // launched with programmatic serialization: let the kernel after start its own independent
+  // prologue right away (it waits for this kernel's completion before it reads anything), then wait
+  // for the kernel before, whose peer stores this barrier publishes
   if (threadIdx.x == 0) ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
   unsigned int* mine = a.pads[a.rank];
   unsigned int epoch = 0;
   if (threadIdx.x == 0) {
