@@ -269,13 +269,14 @@ def run_gpu(args):
                 out.append(g)
         return out
 
-    use_graphs = True
-    try:
-        graphs["all"] = capture(BATCHES)
-    except Exception as exc:  # pragma: no cover - e.g. a collective that cannot be captured
-        use_graphs = False
-        if rank == 0:
-            print(f"[bench] CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+    use_graphs = not args.no_graphs
+    if use_graphs:
+        try:
+            graphs["all"] = capture(BATCHES)
+        except Exception as exc:  # pragma: no cover - e.g. a collective that cannot be captured
+            use_graphs = False
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
 
     def run_steps(count, key="all", batches=BATCHES, offset=0):
         with torch.cuda.stream(stream):
@@ -444,6 +445,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="launch every kernel eagerly (for per-kernel profiling; the numbers then include "
+                         "the host's launch overhead)")
     ap.add_argument("--gather", default="fused", choices=("fused", "fused-barrier", "nccl"),
                     help="multi-GPU: peer stores and signal/wait inside the GEMV launches; the same stores with a "
                          "barrier kernel per group; or NCCL all-gather")
