@@ -118,14 +118,29 @@ template <> struct Decoder<kQ4_K> {
     const float dsc = d * (float)sc;
     const float dm = dmin * (float)mn;
     const uint32_t words[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    // A nibble that sits at bit s < 20 of a word becomes the float 2^23 + q * 2^s with one logic op
+    // ((w & mask) | 0x4B000000), q * 2^s after subtracting 2^23, and d*sc*q - dmin*mn with one FMA
+    // against d*sc*2^-s (a power-of-two rescale: exact).  The nibbles of bytes 2 and 3 that sit at
+    // bit 20 or above are reached through w >> 12.  Masks and shifts depend on the thread's half.
+    const uint32_t m0 = h ? 0x000000F0u : 0x0000000Fu, m1 = h ? 0x0000F000u : 0x00000F00u;
+    const uint32_t m2 = h ? 0x00000F00u : 0x000000F0u, m3 = h ? 0x000F0000u : 0x0000F000u;
+    const float s0 = dsc * (h ? 0.0625f : 1.f), s1 = dsc * (h ? 0x1p-12f : 0x1p-8f);
+    const float s2 = dsc * (h ? 0x1p-8f : 0x1p-4f), s3 = dsc * (h ? 0x1p-16f : 0x1p-12f);
+    const uint32_t magic = 0x4B000000u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t nib = (words[i] >> (4 * h)) & 0x0F0F0F0Fu;
-      float f[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) f[b] = fmaf(dsc, byte_magic(nib, b) - 8388608.f, -dm);
-      o.v[2 * i] = pack_bf16(f[0], f[1]);
-      o.v[2 * i + 1] = pack_bf16(f[2], f[3]);
+      const uint32_t w = words[i], ws = w >> 12;
+      uint32_t t0, t1, t2, t3;
+      asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t0) : "r"(w), "r"(m0), "r"(magic));
+      asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t1) : "r"(w), "r"(m1), "r"(magic));
+      asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t2) : "r"(ws), "r"(m2), "r"(magic));
+      asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t3) : "r"(ws), "r"(m3), "r"(magic));
+      const float f0 = fmaf(s0, __uint_as_float(t0) - 8388608.f, -dm);
+      const float f1 = fmaf(s1, __uint_as_float(t1) - 8388608.f, -dm);
+      const float f2 = fmaf(s2, __uint_as_float(t2) - 8388608.f, -dm);
+      const float f3 = fmaf(s3, __uint_as_float(t3) - 8388608.f, -dm);
+      o.v[2 * i] = pack_bf16(f0, f1);
+      o.v[2 * i + 1] = pack_bf16(f2, f3);
     }
   }
   __device__ static __forceinline__ void store(const Ctx& c, uint8_t* a_tile, const Out& o) {
