@@ -58,9 +58,11 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def workload_config(world: int, gather: str = "fused"):
+def workload_config(world: int, gather: str = "fused", grouped: bool = False):
     return {
         "workload": "q4_k decode GEMV: gate/up 18944x3584 + down 3584x18944, batch 1/4/16 (9 GEMVs per step)",
+        "launches": ("gate and up share their activations and run as one grouped launch (6 GEMV launches per step)"
+                     if grouped else "one launch per GEMV"),
         "format": FORMAT, "batches": list(BATCHES), "activations": "bf16", "output": "fp32",
         "l2": "weights rotate over a ring of sets > 3x L2; every launch streams from HBM",
         "parallelism": f"N-sharded x{world}" + ("" if world == 1 else (
@@ -200,7 +202,7 @@ def run_gpu(args):
     import tensor_b200 as tb
     from tensor_b200 import synth
     from tensor_b200.peer import PeerArena
-    from tensor_b200.projection import FusedGatherGroup, GatherGroup, QuantLinear
+    from tensor_b200.projection import FusedGatherGroup, GatherGroup, QuantLinear, QuantLinearPair
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -233,10 +235,11 @@ def run_gpu(args):
             for b in BATCHES}
     lins = {b: [QuantLinear(weights[0][j], fmt, n, k, b, rank=rank, world=world, variant="auto")
                 for j, (_, n, k) in enumerate(SHAPES)] for b in BATCHES}
-    launches_per_step = len(BATCHES) * len(SHAPES)
+    grouped = world == 1 and not args.separate_gate_up   # gate + up as one launch
+    launches_per_step = len(BATCHES) * (len(SHAPES) - 1 if grouped else len(SHAPES))
     barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused-barrier" else 0
     # batches above 8 run a small activation-conversion kernel ahead of each GEMV
-    barriers_per_step += sum(len(SHAPES) for b in BATCHES if b > 8)
+    barriers_per_step += sum(launches_per_step // len(BATCHES) for b in BATCHES if b > 8)
     # gate and up are needed together (one collective for both); down follows
     if args.gather in ("fused", "fused-barrier"):
         # the GEMVs store their columns into every rank's output; one barrier kernel per group
@@ -248,9 +251,18 @@ def run_gpu(args):
     else:
         groups = {b: [GatherGroup(lins[b][0:2]), GatherGroup(lins[b][2:3])] for b in BATCHES}
 
+    # one GPU: gate and up read the same activations and go out as ONE launch over both weights
+    pairs = None
+    if world == 1 and not args.separate_gate_up:
+        pairs = {b: QuantLinearPair(weights[0][0], SHAPES[0][1], weights[0][1], SHAPES[1][1], fmt, SHAPES[0][2], b)
+                 for b in BATCHES}
+
     def step(slot, batches=BATCHES):
         for b in batches:
-            groups[b][0].forward(acts[b][0:2], raws=weights[slot][0:2])
+            if pairs is not None:
+                pairs[b].forward(acts[b][0], raw1=weights[slot][0], raw2=weights[slot][1])
+            else:
+                groups[b][0].forward(acts[b][0:2], raws=weights[slot][0:2])
             groups[b][1].forward(acts[b][2:3], raws=weights[slot][2:3])
 
     # ---- CUDA graphs: one per ring slot (launch-bound otherwise: a GEMV is a few microseconds) ----
@@ -332,7 +344,7 @@ def run_gpu(args):
         cases.append({"batch": b, "us_per_3_gemv": t * 1e3, "gbps": bytes_b / (t * 1e-3) / 1e9})
 
     # ---- roofline of the dominant kernel: the pipelined GEMV ----
-    launch_bytes_local = set_bytes_local / len(SHAPES)  # all three shapes hold the same byte count
+    launch_bytes_local = set_bytes_local * len(BATCHES) / launches_per_step  # weight bytes of an average launch
     avg_launch_s = ms_per_step * 1e-3 / launches_per_step
     achieved = launch_bytes_local / avg_launch_s / 1e9
     best = max(cases, key=lambda c: c["gbps"])
@@ -341,32 +353,40 @@ def run_gpu(args):
         "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
         "peak_source": peaks["source"], "traffic": None,
         "algorithmic_bytes_per_launch": launch_bytes_local,
-        "note": "average over the nine launches of a step (batch 1/4/16), gaps between launches included; "
+        "note": f"average over the {launches_per_step} GEMV launches of a step (batch 1/4/16"
+                + (", gate and up grouped into one launch" if grouped else "")
+                + "), gaps between launches included; "
                 f"best batch ({best['batch']}) reaches {best['gbps'] / world:.0f} GB/s per GPU",
     }
     if world == 1:
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu capture
-        # (profiles/gemv_q4k_batch1_18944x3584.md): equal to the algorithmic bytes, i.e. no re-reads
-        roofline["traffic"] = 38245120
+        # dram__bytes_read.sum + dram__bytes_write.sum from the committed ncu capture of one 38,191,104-byte
+        # launch (profiles/gemv_q4k_batch1_18944x3584.md: 38,245,120 B, i.e. no re-reads), scaled to the
+        # weight bytes of an average launch of this run (traffic is proportional to the rows streamed)
+        roofline["traffic"] = round(launch_bytes_local * 38245120 / 38191104)
 
     # ---- end to end: host buffers in, host buffers out, every step ----
-    x_host = {b: [a.cpu().pin_memory() for a in acts[b]] for b in BATCHES}
-    y_host = {b: [torch.empty((b, n), dtype=torch.float32).pin_memory() for _, n, _ in SHAPES] for b in BATCHES}
+    # device tensors that travel: with the grouped launch gate and up share one activation buffer
+    # and one [m, 2N] output
+    live_acts = {b: ([acts[b][0], acts[b][2]] if pairs is not None else list(acts[b])) for b in BATCHES}
+    live_outs = {b: ([pairs[b].out, lins[b][2].out] if pairs is not None else [l.out for l in lins[b]])
+                 for b in BATCHES}
+    x_host = {b: [a.cpu().pin_memory() for a in live_acts[b]] for b in BATCHES}
+    y_host = {b: [torch.empty(tuple(o.shape), dtype=torch.float32).pin_memory() for o in live_outs[b]] for b in BATCHES}
     h2d = sum(t.numel() * t.element_size() for b in BATCHES for t in x_host[b])
     d2h = sum(t.numel() * 4 for b in BATCHES for t in y_host[b])
 
     def e2e_step(i):
         with torch.cuda.stream(stream):
             for b in BATCHES:
-                for j in range(len(SHAPES)):
-                    acts[b][j].copy_(x_host[b][j], non_blocking=True)
+                for dst, src in zip(live_acts[b], x_host[b]):
+                    dst.copy_(src, non_blocking=True)
             if use_graphs:
                 graphs["all"][i % ring].replay()
             else:
                 step(i % ring)
             for b in BATCHES:
-                for j in range(len(SHAPES)):
-                    y_host[b][j].copy_(lins[b][j].out, non_blocking=True)
+                for dst, src in zip(y_host[b], live_outs[b]):
+                    dst.copy_(src, non_blocking=True)
         stream.synchronize()
 
     for i in range(3):
@@ -416,7 +436,7 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16 mma / f32 accumulate", "data": "synthetic",
-        "config": workload_config(world, args.gather), "clocks": clocks, "e2e": e2e,
+        "config": workload_config(world, args.gather, grouped), "clocks": clocks, "e2e": e2e,
         "gpu_launches": (launches_per_step + barriers_per_step) * args.steps, "roofline": roofline, "cases": cases,
         "prefill": prefill, "cuda_graphs": use_graphs, "device_status": status,
     }
@@ -445,6 +465,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--separate-gate-up", action="store_true",
+                    help="one GPU: launch gate and up as two GEMVs instead of one grouped launch")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel eagerly (for per-kernel profiling; the numbers then include "
                          "the host's launch overhead)")

@@ -162,6 +162,19 @@ int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void *x, const vo
 int32_t tb200_gguf_gemv_static(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
                                int64_t m, int64_t n, int64_t k, void *stream, TensorErrorV1 *error);
 
+/* Two weights of the same format and K applied to the same activations in ONE launch (gate and up
+ * of an MLP, or q/k/v): out[m, n1 + n2] holds x . dequant(w1)^T in columns 0 .. n1 and
+ * x . dequant(w2)^T in columns n1 .. n1 + n2, exactly as two calls of tb200_gguf_gemv would have
+ * produced them.  A decode GEMV costs several microseconds of launch, staging and tail whatever its
+ * size; grouping pays them once.  Where the pipelined kernel cannot take the pair in one launch
+ * (K split across CTAs, n1 not a multiple of 16, other formats) the call issues two launches into
+ * the same output.  scratch: as tb200_gguf_gemv for the shape (m, n1 + n2, k).  The reference
+ * launches one kernel per weight (showcase/kernels.py:114-119); no counterpart there. */
+int32_t tb200_gguf_gemv_pair(int32_t format, int32_t x_dtype, const void *x, const void *w1, int64_t n1,
+                             const void *w2, int64_t n2, float *out, int64_t m, int64_t k,
+                             void *scratch, int64_t scratch_bytes, int32_t variant, void *stream,
+                             TensorErrorV1 *error);
+
 /* N-sharded GEMV: this rank holds n of the projection's rows (w is [n, k]) and writes its n result
  * columns into `out_count` destinations: element (row, col) goes to
  * outs[i][row * out_ld + col_offset + col].  outs is a HOST array of device addresses; outs[0] is

@@ -355,6 +355,43 @@ int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, 
                                       scratch_bytes, variant, nullptr, 0, 1, 0, stream, error);
 }
 
+int32_t tb200_gguf_gemv_pair(int32_t format, int32_t x_dtype, const void* x, const void* w1, int64_t n1,
+                             const void* w2, int64_t n2, float* out, int64_t m, int64_t k, void* scratch,
+                             int64_t scratch_bytes, int32_t variant, void* stream, TensorErrorV1* error) {
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n1, k, variant)) return s;
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n2, k, variant)) return s;
+  if (m == 0 || n1 + n2 == 0) return ok(error);
+  const int64_t n = n1 + n2;
+  if (n1 > 0 && n2 > 0 && variant != TB200_VARIANT_SIMPLE) {
+    // one launch over both weights when the pipelined kernel takes the concatenated shape unsplit
+    if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
+    if (int32_t s = check_pointer(error, "w1", w1, 16, k > 0)) return s;
+    if (int32_t s = check_pointer(error, "w2", w2, 16, k > 0)) return s;
+    if (int32_t s = check_pointer(error, "out", out, 4, true)) return s;
+    if (int32_t s = check_pointer(error, "scratch", scratch, 256, false)) return s;
+    if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
+    const DeviceInfo* dev;
+    if (int32_t s = require_device(error, &dev)) return s;
+    GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
+    if (plan.supported && plan.k_splits == 1 && n1 % kGemvTileRows == 0) {
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), single_output(out, n), m,
+                                       n, k, scratch, static_cast<cudaStream_t>(stream), nullptr,
+                                       static_cast<const uint8_t*>(w2), n1);
+      if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch (two weights)", e);
+      return ok(error);
+    }
+  }
+  // otherwise two launches, each into its own column window of the same [m, n1 + n2] output
+  OutSpec first = single_output(out, n), second = single_output(out + n1, n);
+  if (n1 > 0)
+    if (int32_t s = gemv_common(format, x_dtype, x, w1, first, m, n1, k, scratch, scratch_bytes, variant, stream, error))
+      return s;
+  if (n2 > 0)
+    if (int32_t s = gemv_common(format, x_dtype, x, w2, second, m, n2, k, scratch, scratch_bytes, variant, stream, error))
+      return s;
+  return ok(error);
+}
+
 int32_t tb200_peer_sync(uint32_t* const* pads, int32_t rank, int32_t world, int32_t mode, void* stream,
                         TensorErrorV1* error) {
   if (int32_t s = check_pads(error, pads, rank, world)) return s;

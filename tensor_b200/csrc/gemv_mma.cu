@@ -50,6 +50,11 @@ constexpr int kSclRowFloats = 18;  // 8 x (scale, offset) pairs + 2 floats of pa
 struct GemvArgs {
   const void* x;
   const uint8_t* w;
+  // Grouped launch: rows [n1, n) come from a second weight of the same K and format that shares
+  // the activations (gate and up of an MLP); the output is the [m, n] concatenation.  n1 is a
+  // multiple of the tile height; null = a single weight.
+  const uint8_t* w2;
+  long long n1;
   float* outs[kMaxOutputs];  // destinations of the result (own buffer first, then peer-mapped ones)
   int n_out;
   int out_vec;               // every destination takes 16-byte stores
@@ -142,10 +147,10 @@ __device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* sm
   const int total = NTB * chunks;
   uint8_t* xs = smem + a.off_xs;
   float2* sxu = reinterpret_cast<float2*>(smem + a.off_sx);
-  // rows beyond m are zero, with zero group sums (done while the copies are in flight)
+  // columns beyond m have no activation rows in shared memory (their B fragments are loaded from a
+  // block of zeros); their group sums are zero (done while the copies are in flight)
   for (int idx = a.m * chunks + ctid; idx < total; idx += threads) {
     const int b = idx / chunks, c = idx - b * chunks;
-    *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = make_uint4(0, 0, 0, 0);
     if ((c & 3) == 0) sxu[(c >> 2) * NTB + b] = make_float2(0.f, 1.f);
   }
   if (!ptx::mbar_wait(xbar, 0)) {  // the producer warp issued the row copies before any weight copy
@@ -285,13 +290,6 @@ __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __res
 // this CTA's K range of x16 and of the table into place; the decode warps only clear the rows past m.
 template <int NTB>
 __device__ __forceinline__ bool stage_prepared(const GemvArgs& a, uint8_t* smem, int ctid, int klen, uint64_t* xbar) {
-  const int threads = a.consumer_warps * 32;
-  const int chunks = klen >> 3;
-  uint8_t* xs = smem + a.off_xs;
-  for (int idx = a.m * chunks + ctid; idx < NTB * chunks; idx += threads) {
-    const int b = idx / chunks, c = idx - b * chunks;
-    *reinterpret_cast<uint4*>(xs + (size_t)b * a.xs_stride + (c << 4)) = make_uint4(0, 0, 0, 0);
-  }
   if (!ptx::mbar_wait(xbar, 0)) {
     report_timeout(0x60000u);
     return false;
@@ -405,12 +403,17 @@ __device__ __forceinline__ Nibbles split_nibbles(uint32_t w, const NibbleConsts&
 // Shared-memory addresses (32-bit, shared window) a consumer warp needs; computed once per CTA.
 struct SmemMap {
   uint32_t xs, sx, scl;  // staged activations, group sums, this warp's scale scratch
+  uint32_t zero;         // 64 zero bytes (B fragments of batch columns past m)
+  int m;
   int stride_s, xs_stride;
   NibbleConsts nc;
 };
 
 // ---- Q4_K, batch on the MMA columns (1 < m <= 16) ------------------------------------------------
-template <int NT>
+// Shared memory holds only the m live activation rows.  PARTIAL (m below the columns of the MMA
+// tiles): a lane whose batch column is past m loads its B fragments from a block of zeros instead
+// (address and stride picked per lane), so no zero rows are stored.
+template <int NT, bool PARTIAL>
 __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage, int sbl, int lane,
                                                float (&acc)[NT][4]) {
   constexpr int NTB = NT * 8;
@@ -438,6 +441,12 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
   const uint32_t rowB = rowA + 8 * sm.stride_s;
   const uint32_t sclA = sm.scl + gid * (kSclRowFloats * 4), sclB = sclA + 8 * (kSclRowFloats * 4);
   const uint32_t xrow = sm.xs + gid * sm.xs_stride + ((sbl * 256 + 8 * tig) << 1);
+  uint32_t xlive[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const bool live = !PARTIAL || 8 * t + gid < sm.m;
+    xlive[t] = live ? xrow + 8 * t * sm.xs_stride : sm.zero;  // the zero block spans all eight group offsets
+  }
   const uint32_t sxp = sm.sx + ((sbl * 8) * NTB + 2 * tig) * 8;
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -453,7 +462,7 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
       const float2 sB = ptx::lds64f(sclB + g * 8);
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint4 xb = ptx::lds128(xrow + 8 * t * sm.xs_stride + g * 64);
+        const uint4 xb = ptx::lds128(xlive[t] + g * 64);
         float c[4];
         if (nib == 0) {
           ptx::mma16816<true>(c, ax.lo02, bx.lo02, ax.lo13, bx.lo13, xb.x, xb.y, zero);
@@ -599,7 +608,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     }
     ptx::fence_mbar_init();
   }
-  if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(smem + a.off_zero)[threadIdx.x] = 0u;
+  if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + a.off_zero)[threadIdx.x] = 0u;
 #ifdef TB200_GEMV_TRACE
   // slots per traced CTA (blockIdx % 100 == 0): 0 start, 1 staged, 8+i tile data ready, 24+i tile decoded,
   // 40+i tile reduced, 56+i tile copy issued
@@ -745,11 +754,15 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       const int rows = (int)min((long long)kTileRows, a.n - row0);
       uint8_t* dst = smem + a.off_stage + (size_t)s * kTileRows * a.stride_s;
       TB200_TRACE(lane == 0 && i < 16, 56 + i);
+      // which weight the tile's rows live in (grouped launches), and its first row there
+      const bool second = a.w2 != nullptr && row0 >= a.n1;
+      const uint8_t* wsrc = second ? a.w2 + (long long)sb0 * kBlockBytes : src0;
+      const long long wrow0 = second ? row0 - a.n1 : row0;
       if (a.contiguous) {
         // the K range is the whole row and rows are packed back to back: one copy per tile
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
-          ptx::bulk_g2s(dst, src0 + row0 * a.row_bytes, (uint32_t)rows * range_bytes, &full[s]);
+          ptx::bulk_g2s(dst, wsrc + wrow0 * a.row_bytes, (uint32_t)rows * range_bytes, &full[s]);
         }
       } else if (a.use_tma) {
         // K is split: one tiled copy fetches the K range of all 16 rows (rows past N and
@@ -762,7 +775,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
         if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)rows * range_bytes);
         __syncwarp();
         if (lane < rows)
-          ptx::bulk_g2s(dst + (size_t)lane * a.stride_s, src0 + (row0 + lane) * a.row_bytes, range_bytes, &full[s]);
+          ptx::bulk_g2s(dst + (size_t)lane * a.stride_s, wsrc + (wrow0 + lane) * a.row_bytes, range_bytes, &full[s]);
       }
     }
     if (i <= (GROUPS && S > 2 ? S - 1 : S)) fetch_activations();
@@ -898,6 +911,8 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   sm.xs = pin(smem_base + a.off_xs);
   sm.sx = pin(smem_base + a.off_sx);
   sm.scl = pin(smem_base + a.off_scl + cw * (kTileRows * kSclRowFloats * 4));
+  sm.zero = pin(smem_base + a.off_zero);
+  sm.m = pin(a.m);
   sm.stride_s = pin(a.stride_s);
   sm.xs_stride = pin(a.xs_stride);
   sm.nc = nibble_consts();
@@ -961,12 +976,14 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       }
     } else {
       float acc[NT][4];
+      const bool partial_batch = sm.m < NTB;
 #pragma unroll
       for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
       for (int sbl = cw; sbl < nsb_l; sbl += Wp)
-        q4k_item_batch<NT>(sm, stage, sbl, lane, acc);
+        if (partial_batch) q4k_item_batch<NT, true>(sm, stage, sbl, lane, acc);
+        else q4k_item_batch<NT, false>(sm, stage, sbl, lane, acc);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
       if (ruse >= 1 && !ptx::mbar_wait(&red_empty[rb], (ruse - 1) & 1)) {
@@ -1048,15 +1065,15 @@ Layout make_layout(int fmt, int m, int sb_per_split, int stages, bool packed, in
   L.off_stage = off;
   off += stages * L.stage_bytes;
   L.off_xs = off;
-  off += ntb * L.xs_stride;
+  off += (groups ? 1 : m) * L.xs_stride;  // only the live rows are kept
   L.off_sx = off;
   off += round_up(sb_per_split * 8 * ntb * 8, 128);  // {group sum, unscale} per group and column
   L.off_red = off;
   off += red_bufs * warps * ntb * kTileRows * 4;
   L.off_scl = off;
   off += groups ? 0 : warps * kTileRows * kSclRowFloats * 4;
-  L.off_zero = off;  // 64 zero bytes: the B fragment of lanes whose weights feed another column
-  off += 64;
+  L.off_zero = off;  // zero bytes: the B fragments of lanes whose weights feed another column (m == 1)
+  off += 512;        // or whose batch column is past m (one 16-byte load at each of the 8 group offsets)
   L.off_misc = off;  // the factor that undoes the activation scaling
   off += 64;
   L.total = round_up(off, 128);
@@ -1089,6 +1106,8 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
   a.sync = 0;
   a.x16 = nullptr;
   a.x_table = nullptr;
+  a.w2 = nullptr;
+  a.n1 = n;
   a.counters = reinterpret_cast<unsigned int*>(scratch);
   a.partials = reinterpret_cast<float*>(scratch + counter_bytes);
   a.m = m;
@@ -1264,8 +1283,11 @@ bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n,
 
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
-                             cudaStream_t stream, const PeerSync* peers) {
+                             cudaStream_t stream, const PeerSync* peers, const uint8_t* w2, long long n1) {
   if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
+  // a second weight is fetched tile by tile from its own base: K must not be split (the split
+  // path addresses rows through one tensor map) and the first weight must end on a tile boundary
+  if (w2 && (plan.k_splits != 1 || n1 <= 0 || n1 >= n || n1 % kTileRows)) return cudaErrorInvalidValue;
   if (out.count < 1 || out.count > kMaxOutputs || out.ld < n) return cudaErrorInvalidValue;
   GemvArgs a{};
   if (peers && peers->flags) {
@@ -1279,6 +1301,8 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   const int smem_total = fill_args(a, plan, fmt, m, n, k);
   a.x = x;
   a.w = w;
+  a.w2 = w2;
+  a.n1 = w2 ? n1 : n;
   a.n_out = out.count;
   a.out_ld = out.ld;
   a.out_vec = (n & 3) == 0 && (out.ld & 3) == 0;

@@ -82,7 +82,9 @@ struct PeerSync {
 };
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
-                             cudaStream_t stream, const PeerSync* peers = nullptr);
+                             cudaStream_t stream, const PeerSync* peers = nullptr, const uint8_t* w2 = nullptr,
+                             long long n1 = 0);
+constexpr int kGemvTileRows = 16;  // rows per weight tile of the pipelined GEMV (n1 of a grouped launch is a multiple)
 inline cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                                     float* out, long long m, long long n, long long k, void* scratch,
                                     cudaStream_t stream) {

@@ -228,3 +228,37 @@ def peer_sync(pad_ptrs, rank: int, device: torch.device, mode: int = PEER_WAIT |
 def peer_barrier(pad_ptrs, rank: int, device: torch.device, stream=None) -> None:
     """Signal and wait (``tb200_peer_barrier``)."""
     peer_sync(pad_ptrs, rank, device, PEER_WAIT | PEER_SIGNAL, stream)
+
+
+def gemv_pair(x: torch.Tensor, w1: torch.Tensor, n1: int, w2: torch.Tensor, n2: int, encoding, k: int,
+              out: torch.Tensor | None = None, scratch: torch.Tensor | None = None, variant="auto",
+              stream=None) -> torch.Tensor:
+    """Two weights over the same activations in one launch: ``out[m, n1 + n2]`` holds
+    ``x . dequant(w1)^T`` in its first ``n1`` columns and ``x . dequant(w2)^T`` in the rest
+    (``tb200_gguf_gemv_pair``).  ``scratch``: as for :func:`gemv` at the shape ``(m, n1 + n2, k)``."""
+    fmt = get_format(encoding)
+    m = _infer_m(x, k)
+    _require_cuda("x", x)
+    _require_cuda("w1", w1)
+    _require_cuda("w2", w2)
+    for name, w, n in (("w1", w1, n1), ("w2", w2, n2)):
+        if w.dtype != torch.uint8 or w.numel() != fmt.weight_bytes(n, k):
+            raise ValueError(f"{name} must hold the {fmt.weight_bytes(n, k)} raw bytes of [{n}, {k}] in {fmt.name}")
+    try:
+        x_dtype = _X_DTYPE_IDS[x.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported activation dtype {x.dtype}") from None
+    if out is None:
+        out = torch.empty((m, n1 + n2), dtype=torch.float32, device=x.device)
+    _require_cuda("out", out)
+    if out.dtype != torch.float32 or out.numel() != m * (n1 + n2):
+        raise ValueError(f"out must be float32 with {m * (n1 + n2)} elements")
+    device = _same_device(x, w1, w2, out, scratch)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_gguf_gemv_pair(
+            fmt.type_id, x_dtype, x.data_ptr(), w1.data_ptr(), n1, w2.data_ptr(), n2, out.data_ptr(), m, k,
+            scratch.data_ptr() if scratch is not None else None, scratch.numel() if scratch is not None else 0,
+            _VARIANTS[variant], _stream_handle(device, stream), ctypes.byref(error))
+    raise_for_status(status, error)
+    return out

@@ -111,6 +111,42 @@ class QuantLinear:
     __call__ = forward
 
 
+class QuantLinearPair:
+    """Two projections that read the same activations (gate and up of an MLP), applied in ONE kernel
+    launch: ``forward(x)`` returns the ``[m, n1 + n2]`` concatenation, first weight's columns
+    first.  A decode GEMV pays several microseconds of launch, staging and tail whatever its size;
+    the pair pays them once.  Single GPU (N-sharded runs use :class:`FusedGatherGroup`)."""
+
+    def __init__(self, raw1: torch.Tensor, n1: int, raw2: torch.Tensor, n2: int, encoding, k: int, m: int,
+                 variant="auto"):
+        self.format = get_format(encoding)
+        self.n1, self.n2, self.k, self.m = int(n1), int(n2), int(k), int(m)
+        for name, raw, n in (("raw1", raw1, n1), ("raw2", raw2, n2)):
+            if not raw.is_cuda or raw.dtype != torch.uint8 or raw.numel() != self.format.weight_bytes(n, k):
+                raise ValueError(f"{name} must be the uint8 CUDA tensor of a [{n}, {k}] {self.format.name} weight")
+        if raw1.device != raw2.device:
+            raise ValueError("both weights must live on the same device")
+        self.raw1, self.raw2 = raw1.contiguous(), raw2.contiguous()
+        self.device = raw1.device
+        self.variant = variant
+        self.out = torch.empty((self.m, self.n1 + self.n2), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            need = ops.gemv_scratch_bytes(self.format, self.m, self.n1 + self.n2, self.k)
+        self._scratch = torch.zeros(need, dtype=torch.uint8, device=self.device) if need else None
+
+    @property
+    def weight_bytes_total(self) -> int:
+        return self.raw1.numel() + self.raw2.numel()
+
+    def forward(self, x: torch.Tensor, raw1: torch.Tensor | None = None, raw2: torch.Tensor | None = None):
+        """Enqueue on the current stream; ``raw1`` / ``raw2`` substitute other weights of the same shapes."""
+        return ops.gemv_pair(x, self.raw1 if raw1 is None else raw1, self.n1,
+                             self.raw2 if raw2 is None else raw2, self.n2, self.format, self.k,
+                             out=self.out, scratch=self._scratch, variant=self.variant)
+
+    __call__ = forward
+
+
 class GatherGroup:
     """Several projections that consume the same step's activations and whose outputs are needed
     together (e.g. gate and up of one MLP): their local outputs live back to back in one buffer and
@@ -235,5 +271,5 @@ class HostProjection:
         return self.y_host
 
 
-__all__ = ["FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "all_gather_columns", "shard_rows",
+__all__ = ["FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "QuantLinearPair", "all_gather_columns", "shard_rows",
            "shard_weight_bytes"]

@@ -137,6 +137,36 @@ def test_gemv_fast_q4k_config_shapes(m, n, k):
     assert torch.count_nonzero(out).item() == 0
 
 
+@pytest.mark.parametrize("name,m,n1,n2,k", [
+    ("q4_k", 1, 18944, 18944, 3584),   # gate + up: one launch over both weights
+    ("q4_k", 4, 2048, 1024, 3584),
+    ("q4_k", 16, 1024, 2048, 2048),
+    ("q4_k", 1, 40, 72, 512),          # first weight does not end on a 16-row tile: two launches
+    ("q4_k", 4, 1792, 1792, 18944),    # K is split across CTAs: two launches
+    ("q6_k", 2, 48, 80, 512),          # served by the fallback kernel
+])
+def test_gemv_pair_equals_two_gemvs(name, m, n1, n2, k):
+    from tensor_b200 import ops, synth
+    from tensor_b200.projection import QuantLinearPair
+
+    w1 = synth.make_weights(name, n1, k, seed=1, device=dev())
+    w2 = synth.make_weights(name, n2, k, seed=2, device=dev())
+    x = synth.make_activations(m, k, seed=3, device=dev())
+    pair = QuantLinearPair(w1, n1, w2, n2, name, k, m)
+    pair.out.fill_(float("nan"))
+    got = pair.forward(x)
+    want = torch.cat([tb.gguf(m, n1, k, name, op="gemv")(x, w1), tb.gguf(m, n2, k, name, op="gemv")(x, w2)], dim=1)
+    assert not torch.isnan(got).any()
+    assert oracle.rel_frobenius(got.cpu().numpy(), want.cpu().numpy()) < 2e-5
+    # against the oracle as well (first weight's columns first)
+    ref = np.concatenate([c_oracle.gemv(x.float().cpu().numpy(), w.cpu().numpy(), name, n, k)
+                          for w, n in ((w1, n1), (w2, n2))], axis=1)
+    assert oracle.rel_frobenius(got.cpu().numpy(), ref) < TOL
+    # twice on the same scratch
+    got2 = pair.forward(x).clone()
+    assert torch.equal(got2, got)
+
+
 def test_gemv_fast_without_scratch_still_correct():
     _gemv_case("q4_k", 1, 512, 18944, "bf16", "auto", scratch=False)
 

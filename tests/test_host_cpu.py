@@ -211,3 +211,22 @@ def test_bump_allocator_gives_every_rank_the_same_offsets():
     assert [a.take(s) for s in sizes] == [b.take(s) for s in sizes] == [0, 256, 512, 768]
     with pytest.raises(MemoryError):
         a.take(4096)
+
+
+def test_gemv_pair_validates_before_touching_a_device():
+    import ctypes
+
+    from tensor_b200 import abi
+    from tensor_b200._native import lib
+
+    err = abi.TensorErrorV1()
+
+    def call(fmt=12, n1=32, n2=32, k=256, variant=0):
+        return lib().tb200_gguf_gemv_pair(fmt, 13, 0x1000, 0x1000, n1, 0x2000, n2, 0x3000, 1, k, None, 0, variant,
+                                          None, ctypes.byref(err))
+
+    assert call(fmt=7) == 2
+    assert call(k=100) == 2
+    assert call(n2=-1) == 2
+    assert call(variant=5) == 2
+    assert call() == 3  # well-formed: stops at the missing device, never computes on the CPU
