@@ -235,7 +235,7 @@ def run_gpu(args):
             for b in BATCHES}
     lins = {b: [QuantLinear(weights[0][j], fmt, n, k, b, rank=rank, world=world, variant="auto")
                 for j, (_, n, k) in enumerate(SHAPES)] for b in BATCHES}
-    grouped = world == 1 and not args.separate_gate_up   # gate + up as one launch
+    grouped = not args.separate_gate_up and (world == 1 or args.gather in ("fused", "fused-barrier"))  # gate + up as one launch
     launches_per_step = len(BATCHES) * (len(SHAPES) - 1 if grouped else len(SHAPES))
     barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused-barrier" else 0
     # batches above 8 run a small activation-conversion kernel ahead of each GEMV
@@ -246,8 +246,9 @@ def run_gpu(args):
         out_bytes = sum(b * n * 4 + 256 for b in BATCHES for _, n, _ in SHAPES)
         arena = PeerArena(out_bytes + (1 << 16), device, rank, world)
         fold = args.gather == "fused"  # ordering inside the GEMV launches; else one barrier kernel per group
-        groups = {b: [FusedGatherGroup(lins[b][0:2], arena, fold), FusedGatherGroup(lins[b][2:3], arena, fold)]
-                  for b in BATCHES}
+        share = not args.separate_gate_up  # gate and up read the same activations: one grouped launch
+        groups = {b: [FusedGatherGroup(lins[b][0:2], arena, fold, shared_input=share),
+                      FusedGatherGroup(lins[b][2:3], arena, fold)] for b in BATCHES}
     else:
         groups = {b: [GatherGroup(lins[b][0:2]), GatherGroup(lins[b][2:3])] for b in BATCHES}
 

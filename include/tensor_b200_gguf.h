@@ -208,6 +208,20 @@ int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void
                                      uint32_t *const *pads, int32_t rank, int32_t world,
                                      int32_t sync, void *stream, TensorErrorV1 *error);
 
+/* tb200_gguf_gemv_pair for an N-sharded rank: this rank's n1 rows of the first weight and n2 rows of
+ * the second (same format, K and activations) in one launch; the first weight's columns go to
+ * outs1[i][row * out_ld + col_offset1 + col], the second's to outs2[i][row * out_ld + col_offset2 +
+ * col], for every destination i (own buffers first, then the peers').  pads / rank / world / sync as
+ * in tb200_gguf_gemv_sharded_sync.  Falls back to two sharded launches (wait on the first, signal on
+ * the second) where the pair cannot share a launch. */
+int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const void *x, const void *w1,
+                                          int64_t n1, const void *w2, int64_t n2, float *const *outs1,
+                                          float *const *outs2, int32_t out_count, int64_t out_ld,
+                                          int64_t col_offset1, int64_t col_offset2, int64_t m, int64_t k,
+                                          void *scratch, int64_t scratch_bytes, int32_t variant,
+                                          uint32_t *const *pads, int32_t rank, int32_t world,
+                                          int32_t sync, void *stream, TensorErrorV1 *error);
+
 /* Barrier between the GPUs of one box over peer-mapped signal pads.  pads is a HOST array of
  * `world` device addresses: pads[i] is rank i's pad (TB200_SIGNAL_PAD_BYTES, 4-byte aligned,
  * zero-filled once before the first use) as mapped into this process.  The kernel announces on

@@ -17,7 +17,7 @@ EXPORTS = (
     "tb200_gguf_gemm_launch_config", "tb200_gguf_dequant", "tb200_gguf_gemv", "tb200_gguf_gemm",
     "tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1",
     "tb200_gguf_gemv_static", "tb200_gguf_gemv_sharded", "tb200_gguf_gemv_sharded_sync", "tb200_peer_barrier",
-    "tb200_peer_sync", "tb200_gguf_gemv_pair",
+    "tb200_peer_sync", "tb200_gguf_gemv_pair", "tb200_gguf_gemv_pair_sharded_sync",
     "tb200_peer_export", "tb200_peer_open", "tb200_peer_close",
 )
 
@@ -80,6 +80,10 @@ def lib():
                                                     vp, i64, i32, ctypes.POINTER(vp), i32, i32, i32, vp, err]
     handle.tb200_gguf_gemv_pair.restype = i32
     handle.tb200_gguf_gemv_pair.argtypes = [i32, i32, vp, vp, i64, vp, i64, vp, i64, i64, vp, i64, i32, vp, err]
+    handle.tb200_gguf_gemv_pair_sharded_sync.restype = i32
+    handle.tb200_gguf_gemv_pair_sharded_sync.argtypes = [
+        i32, i32, vp, vp, i64, vp, i64, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i64, i64, i64, i64, i64, vp, i64,
+        i32, ctypes.POINTER(vp), i32, i32, i32, vp, err]
     handle.tb200_peer_sync.restype = i32
     handle.tb200_peer_sync.argtypes = [ctypes.POINTER(vp), i32, i32, i32, vp, err]
     handle.tb200_peer_barrier.restype = i32

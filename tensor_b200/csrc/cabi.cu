@@ -374,7 +374,9 @@ int32_t tb200_gguf_gemv_pair(int32_t format, int32_t x_dtype, const void* x, con
     if (int32_t s = require_device(error, &dev)) return s;
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
     if (plan.supported && plan.k_splits == 1 && n1 % kGemvTileRows == 0) {
-      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), single_output(out, n), m,
+      OutSpec both = single_output(out, n);
+      both.ptr2[0] = out + n1;
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), both, m,
                                        n, k, scratch, static_cast<cudaStream_t>(stream), nullptr,
                                        static_cast<const uint8_t*>(w2), n1);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch (two weights)", e);
@@ -390,6 +392,65 @@ int32_t tb200_gguf_gemv_pair(int32_t format, int32_t x_dtype, const void* x, con
     if (int32_t s = gemv_common(format, x_dtype, x, w2, second, m, n2, k, scratch, scratch_bytes, variant, stream, error))
       return s;
   return ok(error);
+}
+
+int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w1, int64_t n1,
+                                          const void* w2, int64_t n2, float* const* outs1, float* const* outs2,
+                                          int32_t out_count, int64_t out_ld, int64_t col_offset1, int64_t col_offset2,
+                                          int64_t m, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant,
+                                          uint32_t* const* pads, int32_t rank, int32_t world, int32_t sync,
+                                          void* stream, TensorErrorV1* error) {
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n1, k, variant)) return s;
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n2, k, variant)) return s;
+  if (!outs1 || !outs2) return fail(error, TENSOR_ERROR_ARGUMENT, "outs1 and outs2 are required");
+  if (out_count < 1 || out_count > TB200_MAX_PEERS)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "out_count %d is not in 1..%d", out_count, TB200_MAX_PEERS);
+  if (col_offset1 < 0 || col_offset2 < 0 || out_ld < col_offset1 + n1 || out_ld < col_offset2 + n2)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "column windows %lld+%lld / %lld+%lld do not fit a row of %lld",
+                (long long)col_offset1, (long long)n1, (long long)col_offset2, (long long)n2, (long long)out_ld);
+  if (sync & ~(TB200_PEER_WAIT | TB200_PEER_SIGNAL)) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown sync bits 0x%x", sync);
+  for (int i = 0; i < out_count; ++i)
+    if (!outs1[i] || !outs2[i]) return fail(error, TENSOR_ERROR_ARGUMENT, "a destination of rank slot %d is null", i);
+  const int64_t n = n1 + n2;
+  if (m > 0 && n1 > 0 && n2 > 0 && variant != TB200_VARIANT_SIMPLE) {
+    PeerSync peers{};
+    if (sync) {
+      if (int32_t s = check_pads(error, pads, rank, world)) return s;
+      for (int i = 0; i < world; ++i) peers.pads[i] = pads[i];
+      peers.rank = rank;
+      peers.world = world;
+      peers.flags = world > 1 ? sync : 0;
+    }
+    if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
+    if (int32_t s = check_pointer(error, "w1", w1, 16, k > 0)) return s;
+    if (int32_t s = check_pointer(error, "w2", w2, 16, k > 0)) return s;
+    if (int32_t s = check_pointer(error, "scratch", scratch, 256, false)) return s;
+    if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
+    const DeviceInfo* dev;
+    if (int32_t s = require_device(error, &dev)) return s;
+    GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
+    if (plan.supported && plan.k_splits == 1 && n1 % kGemvTileRows == 0) {
+      OutSpec spec{};
+      spec.count = out_count;
+      spec.ld = out_ld;
+      for (int i = 0; i < out_count; ++i) {
+        spec.ptr[i] = outs1[i] + col_offset1;
+        spec.ptr2[i] = outs2[i] + col_offset2;
+      }
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), spec, m, n, k, scratch,
+                                       static_cast<cudaStream_t>(stream), peers.flags ? &peers : nullptr,
+                                       static_cast<const uint8_t*>(w2), n1);
+      if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch (two weights, sharded)", e);
+      return ok(error);
+    }
+  }
+  // two launches: the first waits for the peers, the second signals them
+  if (int32_t s = tb200_gguf_gemv_sharded_sync(format, x_dtype, x, w1, outs1, out_count, out_ld, col_offset1, m, n1, k,
+                                               scratch, scratch_bytes, variant, pads, rank, world,
+                                               sync & TB200_PEER_WAIT, stream, error))
+    return s;
+  return tb200_gguf_gemv_sharded_sync(format, x_dtype, x, w2, outs2, out_count, out_ld, col_offset2, m, n2, k, scratch,
+                                      scratch_bytes, variant, pads, rank, world, sync & TB200_PEER_SIGNAL, stream, error);
 }
 
 int32_t tb200_peer_sync(uint32_t* const* pads, int32_t rank, int32_t world, int32_t mode, void* stream,

@@ -56,6 +56,7 @@ struct GemvArgs {
   const uint8_t* w2;
   long long n1;
   float* outs[kMaxOutputs];  // destinations of the result (own buffer first, then peer-mapped ones)
+  float* outs2[kMaxOutputs]; // grouped launch: destinations of the second weight's columns
   int n_out;
   int out_vec;               // every destination takes 16-byte stores
   long long out_ld;          // elements between the batch rows of a destination
@@ -833,7 +834,10 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
         if (f >= kQuads || col >= a.m || grow >= a.n) continue;
         const float4 v = make_float4(sum[j].x * unscale, sum[j].y * unscale, sum[j].z * unscale, sum[j].w * unscale);
         for (int d = 0; d < dests; ++d) {
-          float* p = (final_out ? a.outs[d] : part) + (long long)col * ld + grow;
+          float* p;
+          if (!final_out) p = part + (long long)col * ld + grow;
+          else if (a.w2 != nullptr && grow >= a.n1) p = a.outs2[d] + (long long)col * ld + (grow - a.n1);
+          else p = a.outs[d] + (long long)col * ld + grow;
           if (vec) {
             *reinterpret_cast<float4*>(p) = v;
           } else {
@@ -1176,10 +1180,13 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
       int stages = 0, red_bufs = 2;
       const int warps = choose_warps(per, per_sm == 1 ? kMaxConsumerWarps : kNarrowWarps);
       Layout L{};
-      for (int rbufs = 2; rbufs >= 1 && !stages; --rbufs)
-        for (int s = kMaxStages; s >= 2; --s) {
-          L = make_layout(fmt, (int)m, per, s, splits == 1 || tma_ok(fmt, per), warps, rbufs);
-          if (L.total <= smem_limit) {
+      // two partial-sum buffers when that still leaves a ring of four stages, else whichever
+      // choice gives the deeper ring
+      for (int rbufs = 2; rbufs >= 1 && stages < 4; --rbufs)
+        for (int s = kMaxStages; s > stages && s >= 2; --s) {
+          const Layout cand = make_layout(fmt, (int)m, per, s, splits == 1 || tma_ok(fmt, per), warps, rbufs);
+          if (cand.total <= smem_limit) {
+            L = cand;
             stages = s;
             red_bufs = rbufs;
             break;
@@ -1288,7 +1295,8 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   // a second weight is fetched tile by tile from its own base: K must not be split (the split
   // path addresses rows through one tensor map) and the first weight must end on a tile boundary
   if (w2 && (plan.k_splits != 1 || n1 <= 0 || n1 >= n || n1 % kTileRows)) return cudaErrorInvalidValue;
-  if (out.count < 1 || out.count > kMaxOutputs || out.ld < n) return cudaErrorInvalidValue;
+  if (out.count < 1 || out.count > kMaxOutputs) return cudaErrorInvalidValue;
+  if (out.ld < (w2 ? (n1 > n - n1 ? n1 : n - n1) : n)) return cudaErrorInvalidValue;
   GemvArgs a{};
   if (peers && peers->flags) {
     if (peers->world < 1 || peers->world > kMaxOutputs || peers->rank < 0 || peers->rank >= peers->world)
@@ -1309,6 +1317,11 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   for (int d = 0; d < out.count; ++d) {
     a.outs[d] = out.ptr[d];
     if (reinterpret_cast<uintptr_t>(out.ptr[d]) & 15) a.out_vec = 0;
+    if (w2) {
+      if (!out.ptr2[d]) return cudaErrorInvalidValue;
+      a.outs2[d] = out.ptr2[d];
+      if (reinterpret_cast<uintptr_t>(out.ptr2[d]) & 15) a.out_vec = 0;
+    }
   }
 #ifdef TB200_GEMV_TRACE
   {

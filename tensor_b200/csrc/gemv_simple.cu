@@ -22,18 +22,18 @@ __global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__
   float acc[NB];
 #pragma unroll
   for (int b = 0; b < NB; ++b) acc[b] = 0.f;
-  const int groups = k >> 5;
-  for (int g = lane; g < groups; g += 32) {
-#pragma unroll 4
-    for (int i = 0; i < 32; ++i) {
-      int c = (g << 5) + i;
-      float wv = decode_one<FMT>(wrow, c);
-      if (weights_bf16) wv = __bfloat162float(__float2bfloat16_rn(wv));
+  // Lane l takes weights l, l + 32, ... of the row: the 32 lanes of a step read neighbouring bytes
+  // of one block (coalesced), its scale is a broadcast load, and the activations are contiguous.
+  // (One lane per 32-weight block, the obvious alternative, strides the lanes by the block size:
+  // every load instruction then touches 32 different sectors.)
+#pragma unroll 8
+  for (int c = lane; c < k; c += 32) {
+    float wv = decode_one<FMT>(wrow, c);
+    if (weights_bf16) wv = __bfloat162float(__float2bfloat16_rn(wv));
 #pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        int bb = b0 + b < m ? b0 + b : m - 1;
-        acc[b] = fmaf(to_f32<XT>(x[(long long)bb * k + c]), wv, acc[b]);
-      }
+    for (int b = 0; b < NB; ++b) {
+      int bb = b0 + b < m ? b0 + b : m - 1;
+      acc[b] = fmaf(to_f32<XT>(x[(long long)bb * k + c]), wv, acc[b]);
     }
   }
 #pragma unroll
@@ -46,12 +46,80 @@ __global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__
   }
 }
 
+// The same arithmetic with everything staged in shared memory first: the CTA converts the
+// activations to fp32 once, and every warp copies its weight row with coalesced 16-byte loads before
+// it decodes it (lane l takes weights l, l + 32, ...: consecutive bytes of a block, no bank
+// conflicts, the block scale a broadcast).  Decode GEMVs of the formats the pipelined kernel does not
+// cover spend their time here at batch 1; it needs rows that are a multiple of 16 bytes and
+// activations plus eight rows that fit in shared memory twice per SM.
+constexpr int kRowWarps = 8;
+template <int FMT, typename XT, int MB>
+__global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __restrict__ x,
+                                                                  const uint8_t* __restrict__ w, const OutSpec out,
+                                                                  int m, long long n, int k, int row_bytes_) {
+  extern __shared__ __align__(16) uint8_t smem_rows[];
+  float* xs = reinterpret_cast<float*>(smem_rows);                       // [MB][k]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* mine = smem_rows + (size_t)MB * k * 4 + (size_t)warp * row_bytes_;
+  const int b0 = blockIdx.y * MB;
+  for (int i = threadIdx.x; i < MB * k; i += blockDim.x) {
+    const int b = i / k, c = i - b * k;
+    xs[i] = b0 + b < m ? to_f32<XT>(x[(long long)(b0 + b) * k + c]) : 0.f;
+  }
+  __syncthreads();
+  const int chunks = row_bytes_ >> 4;
+  for (long long row = (long long)blockIdx.x * kRowWarps + warp; row < n; row += (long long)gridDim.x * kRowWarps) {
+    const uint4* src = reinterpret_cast<const uint4*>(w + row * row_bytes_);
+    for (int i = lane; i < chunks; i += 32) reinterpret_cast<uint4*>(mine)[i] = __ldg(src + i);
+    __syncwarp();
+    float acc[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) acc[b] = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < k; c += 32) {
+      const float wv = decode_one<FMT>(mine, c);
+#pragma unroll
+      for (int b = 0; b < MB; ++b) acc[b] = fmaf(xs[b * k + c], wv, acc[b]);
+    }
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      float v = acc[b];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && b0 + b < m)
+        for (int d = 0; d < out.count; ++d) out.ptr[d][(long long)(b0 + b) * out.ld + row] = v;
+    }
+    __syncwarp();  // the row buffer is rewritten by the next iteration
+  }
+}
+
+template <int FMT, typename XT, int MB>
+static cudaError_t launch_rows(const XT* x, const uint8_t* w, const OutSpec& out, long long m, long long n, long long k,
+                               int smem, cudaStream_t stream) {
+  auto kernel = gemv_rows_kernel<FMT, XT, MB>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  const long long row_ctas = (n + kRowWarps - 1) / kRowWarps;
+  const unsigned gx = (unsigned)(row_ctas < 148 * 8 ? row_ctas : 148 * 8);
+  const unsigned gy = (unsigned)((m + MB - 1) / MB);
+  kernel<<<dim3(gx, gy), kRowWarps * 32, smem, stream>>>(x, w, out, (int)m, n, (int)k, (int)row_bytes(FMT, k));
+  return cudaGetLastError();
+}
+
 template <int FMT, typename XT>
 static cudaError_t launch_typed(const void* x, const uint8_t* w, const OutSpec& out, long long m,
                                 long long n, long long k, bool weights_bf16, cudaStream_t stream) {
+  const XT* xp = static_cast<const XT*>(x);
+  // decode GEMVs (fp32 weights) whose rows and activations fit: the shared-memory staged kernel
+  const long long rb = row_bytes(FMT, k);
+  // (measured: 1.9x faster than the kernel below for Q8_0 / Q4_0 4096 x 4096 at batch 1; at larger
+  // batches, or when the staging leaves room for a single CTA per SM only, it is not)
+  if (!weights_bf16 && m == 1 && rb % 16 == 0) {
+    const long long smem = k * 4 + kRowWarps * rb;
+    if (smem <= 100 * 1024) return launch_rows<FMT, XT, 1>(xp, w, out, m, n, k, (int)smem, stream);
+  }
   const int warps = 8;
   dim3 block(warps * 32);
-  const XT* xp = static_cast<const XT*>(x);
   long long gx = (n + warps - 1) / warps;
   if (m == 1) {
     gemv_simple_kernel<FMT, XT, 1><<<dim3((unsigned)gx, 1), block, 0, stream>>>(

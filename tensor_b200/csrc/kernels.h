@@ -26,6 +26,9 @@ struct OutSpec {
   float* ptr[kMaxOutputs];
   int count;
   long long ld;
+  // grouped launches (two weights): where the second weight's columns go, column 0 of that weight
+  // at ptr2[i][row * ld]; unused (null) for a single weight
+  float* ptr2[kMaxOutputs];
 };
 inline OutSpec single_output(float* out, long long n) {
   OutSpec o{};

@@ -262,3 +262,40 @@ def gemv_pair(x: torch.Tensor, w1: torch.Tensor, n1: int, w2: torch.Tensor, n2: 
             _VARIANTS[variant], _stream_handle(device, stream), ctypes.byref(error))
     raise_for_status(status, error)
     return out
+
+
+def gemv_pair_sharded(x: torch.Tensor, w1: torch.Tensor, n1: int, w2: torch.Tensor, n2: int, encoding, k: int,
+                      out1_ptrs, out2_ptrs, out_ld: int, col_offset1: int, col_offset2: int,
+                      scratch: torch.Tensor | None = None, variant="auto", stream=None, pad_ptrs=None,
+                      rank: int = 0, sync: int = 0) -> None:
+    """:func:`gemv_pair` for one rank of an N-sharded pair of projections: the two weights' columns go
+    to their own windows of every rank's two outputs (``tb200_gguf_gemv_pair_sharded_sync``)."""
+    fmt = get_format(encoding)
+    m = _infer_m(x, k)
+    for name, t in (("x", x), ("w1", w1), ("w2", w2)):
+        _require_cuda(name, t)
+    for name, w, n in (("w1", w1, n1), ("w2", w2, n2)):
+        if w.dtype != torch.uint8 or w.numel() != fmt.weight_bytes(n, k):
+            raise ValueError(f"{name} must hold the {fmt.weight_bytes(n, k)} raw bytes of [{n}, {k}] in {fmt.name}")
+    try:
+        x_dtype = _X_DTYPE_IDS[x.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported activation dtype {x.dtype}") from None
+    if len(out1_ptrs) != len(out2_ptrs):
+        raise ValueError("both outputs need the same number of destinations")
+    if sync and pad_ptrs is None:
+        raise ValueError("sync needs the signal pads")
+    device = _same_device(x, w1, w2, scratch)
+    count = len(out1_ptrs)
+    table1 = (ctypes.c_void_p * max(count, 1))(*[int(p) for p in out1_ptrs])
+    table2 = (ctypes.c_void_p * max(count, 1))(*[int(p) for p in out2_ptrs])
+    pads = [int(p) for p in (pad_ptrs or [])]
+    pad_table = (ctypes.c_void_p * max(len(pads), 1))(*pads)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_gguf_gemv_pair_sharded_sync(
+            fmt.type_id, x_dtype, x.data_ptr(), w1.data_ptr(), n1, w2.data_ptr(), n2, table1, table2, count, out_ld,
+            col_offset1, col_offset2, m, k, scratch.data_ptr() if scratch is not None else None,
+            scratch.numel() if scratch is not None else 0, _VARIANTS[variant], pad_table if pads else None, rank,
+            max(len(pads), 1), sync, _stream_handle(device, stream), ctypes.byref(error))
+    raise_for_status(status, error)

@@ -203,10 +203,13 @@ class FusedGatherGroup:
     a rank's next write to a peer's buffer comes after it has seen that peer's following signal,
     which the peer sends after it has consumed the buffer."""
 
-    def __init__(self, linears, arena, fold_sync: bool = True):
+    def __init__(self, linears, arena, fold_sync: bool = True, shared_input: bool = False):
+        """``shared_input``: the first two projections read the same activations (``xs[0]``; gate and
+        up) and go out as one grouped launch."""
         self.linears = list(linears)
         self.arena = arena
         self.fold_sync = fold_sync
+        self.shared_input = bool(shared_input) and len(self.linears) >= 2
         first = self.linears[0]
         self.world, self.rank, self.device = first.world, first.rank, first.device
         if arena.world != self.world or arena.rank != self.rank or arena.device != self.device:
@@ -221,6 +224,15 @@ class FusedGatherGroup:
             l.out = arena.view(offset, (l.m, l.n))
             self._targets.append(arena.ptrs(offset))
         self._pads = arena.pad_ptrs()
+        self._pair_scratch = None
+        if self.shared_input:
+            a, b = self.linears[0], self.linears[1]
+            if (a.format, a.k, a.m, a.n) != (b.format, b.k, b.m, b.n):
+                raise ValueError("a grouped launch needs two weights of the same format, shape and batch")
+            with torch.cuda.device(self.device):
+                need = ops.gemv_scratch_bytes(a.format, a.m, a.n_local + b.n_local, a.k)
+            if need:
+                self._pair_scratch = torch.zeros(need, dtype=torch.uint8, device=self.device)
 
     def forward(self, xs, raws=None):
         last = len(self.linears) - 1
@@ -229,6 +241,18 @@ class FusedGatherGroup:
             sync = 0
             if self.fold_sync and self.world > 1:
                 sync = (ops.PEER_WAIT if i == 0 else 0) | (ops.PEER_SIGNAL if i == last else 0)
+            if self.shared_input and i == 1:
+                continue  # went out with projection 0
+            if self.shared_input and i == 0:
+                b = self.linears[1]
+                raw_b = b.raw if raws is None or raws[1] is None else raws[1]
+                if self.fold_sync and self.world > 1 and last == 1:
+                    sync |= ops.PEER_SIGNAL
+                ops.gemv_pair_sharded(xs[0], raw, l.n_local, raw_b, b.n_local, l.format, l.k, self._targets[0],
+                                      self._targets[1], l.n, l.rank * l.n_local, b.rank * b.n_local,
+                                      scratch=self._pair_scratch, variant=l.kernel.variant,
+                                      pad_ptrs=self._pads if sync else None, rank=self.rank, sync=sync)
+                continue
             ops.gemv_sharded(xs[i], raw, l.format, l.n_local, l.k, self._targets[i], l.n, l.rank * l.n_local,
                              scratch=l.kernel._scratch, variant=l.kernel.variant,
                              pad_ptrs=self._pads if sync else None, rank=self.rank, sync=sync)

@@ -34,7 +34,8 @@ import triton.language as tl
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.environ.get("TENSOR_REFERENCE", "/root/reference"))
+# the reference checkout: TENSOR_REFERENCE, else a sibling directory `reference` next to this repository
+sys.path.insert(0, os.environ.get("TENSOR_REFERENCE") or os.path.normpath(os.path.join(ROOT, "..", "reference")))
 
 from benchmarks.kernels.showcase import triton_kernels as ref  # noqa: E402  (the reference)
 from oracle import gguf_oracle as oracle  # noqa: E402

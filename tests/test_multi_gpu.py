@@ -68,6 +68,24 @@ def _rank_main(rank, world, port, result_path):
                 torch.cuda.synchronize()
                 for got, ref in zip(outs, want):
                     ok &= bool(torch.equal(got, ref))
+        # gate and up as one grouped launch per rank (both read xs[0])
+        kern = tb.gguf(m, shapes[1][0] // world, shapes[1][1], "q4_k", op="gemv", device=dev)
+        want_up = torch.cat([kern(xs[0], shard_weight_bytes(fulls[1], "q4_k", shapes[1][0], shapes[1][1], r, world).clone())
+                             for r in range(world)], dim=1)
+        shared = FusedGatherGroup(lins[0:2], arena, fold_sync=True, shared_input=True)
+        for _ in range(2):
+            for lin in lins[0:2]:
+                lin.out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            outs = shared.forward([xs[0], xs[0]])
+            shared.wait()
+            torch.cuda.synchronize()
+            # (the grouped launch plans for twice the rows, so its K split, and with it the summation
+            # order, may differ from the single projection's: close, not bit-identical)
+            for got, ref in ((outs[0], want[0]), (outs[1], want_up)):
+                ok &= not bool(torch.isnan(got).any())
+                ok &= float((got - ref).norm() / ref.norm()) < 2e-5
         ok &= tb.device_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -16,7 +16,9 @@ import pytest
 
 from tensor_b200 import tbin
 
-REFERENCE = os.environ.get("TENSOR_REFERENCE", "/root/reference")
+# the reference checkout: TENSOR_REFERENCE, else a sibling directory `reference` next to this repository
+REFERENCE = os.environ.get("TENSOR_REFERENCE") or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
 
 
 def _check_envelope(path):
