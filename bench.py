@@ -58,6 +58,11 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def is_grouped(args, world: int) -> bool:
+    """Gate and up go out as one grouped launch (they share their activations)."""
+    return not args.separate_gate_up and (world == 1 or args.gather in ("fused", "fused-barrier"))
+
+
 def workload_config(world: int, gather: str = "fused", grouped: bool = False):
     return {
         "workload": "q4_k decode GEMV: gate/up 18944x3584 + down 3584x18944, batch 1/4/16 (9 GEMVs per step)",
@@ -126,7 +131,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(args.gpus),
+        # the same config object as the GPU arm prints for these arguments
+        "data": "synthetic", "config": workload_config(args.gpus, args.gather, is_grouped(args, args.gpus)),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": c_oracle.threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -235,7 +241,7 @@ def run_gpu(args):
             for b in BATCHES}
     lins = {b: [QuantLinear(weights[0][j], fmt, n, k, b, rank=rank, world=world, variant="auto")
                 for j, (_, n, k) in enumerate(SHAPES)] for b in BATCHES}
-    grouped = not args.separate_gate_up and (world == 1 or args.gather in ("fused", "fused-barrier"))  # gate + up as one launch
+    grouped = is_grouped(args, world)  # gate + up as one launch
     launches_per_step = len(BATCHES) * (len(SHAPES) - 1 if grouped else len(SHAPES))
     barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused-barrier" else 0
     # batches above 8 run a small activation-conversion kernel ahead of each GEMV
@@ -265,6 +271,8 @@ def run_gpu(args):
             else:
                 groups[b][0].forward(acts[b][0:2], raws=weights[slot][0:2])
             groups[b][1].forward(acts[b][2:3], raws=weights[slot][2:3])
+            if world > 1 and args.gather == "fused":
+                groups[b][1].wait()  # the peers' columns of the last projection have landed
 
     # ---- CUDA graphs: one per ring slot (launch-bound otherwise: a GEMV is a few microseconds) ----
     stream = torch.cuda.Stream(device)
@@ -376,26 +384,57 @@ def run_gpu(args):
     h2d = sum(t.numel() * t.element_size() for b in BATCHES for t in x_host[b])
     d2h = sum(t.numel() * 4 for b in BATCHES for t in y_host[b])
 
+    # Every step copies every activation in from pinned host memory and every output back out.  The
+    # copies ride on two side streams and are ordered by events per batch: the largest batch runs
+    # first, so its outputs travel while the smaller batches compute, and the inputs of the next
+    # step's batch b go in as soon as this step's batch b has been computed.  Buffers are single:
+    # the compute of batch b waits until its previous outputs have left and its inputs have arrived.
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    order = sorted(BATCHES, reverse=True)
+    ev_in = {b: torch.cuda.Event() for b in BATCHES}
+    ev_out = {b: torch.cuda.Event() for b in BATCHES}
+    ev_done = {b: torch.cuda.Event() for b in BATCHES}
+
+    def copy_in(b):
+        with torch.cuda.stream(s_in):
+            for dst, src in zip(live_acts[b], x_host[b]):
+                dst.copy_(src, non_blocking=True)
+            ev_in[b].record(s_in)
+
     def e2e_step(i):
-        with torch.cuda.stream(stream):
-            for b in BATCHES:
-                for dst, src in zip(live_acts[b], x_host[b]):
-                    dst.copy_(src, non_blocking=True)
-            if use_graphs:
-                graphs["all"][i % ring].replay()
-            else:
-                step(i % ring)
-            for b in BATCHES:
+        for b in order:
+            stream.wait_event(ev_in[b])
+            stream.wait_event(ev_out[b])
+            with torch.cuda.stream(stream):
+                if use_graphs:
+                    graphs[b][i % ring].replay()
+                else:
+                    step(i % ring, (b,))
+                ev_done[b].record(stream)
+            s_out.wait_event(ev_done[b])
+            with torch.cuda.stream(s_out):
                 for dst, src in zip(y_host[b], live_outs[b]):
                     dst.copy_(src, non_blocking=True)
-        stream.synchronize()
+                ev_out[b].record(s_out)
+            s_in.wait_event(ev_done[b])
+            copy_in(b)  # the next step's inputs of this batch
 
+    def e2e_drain():
+        for st in (stream, s_in, s_out):
+            st.synchronize()
+
+    torch.cuda.synchronize(device)
+    for b in BATCHES:
+        ev_out[b].record(s_out)
+        copy_in(b)
     for i in range(3):
         e2e_step(i)
+    e2e_drain()
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(i)
+    e2e_drain()
     e2e_s = time.perf_counter() - t0
     if world > 1:
         t = torch.tensor([e2e_s], device=device)
@@ -403,7 +442,8 @@ def run_gpu(args):
         e2e_s = float(t.item())
     e2e = {"value": step_bytes_total * args.steps / e2e_s / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "note": "activations from pinned host memory and outputs back to it every step; weights resident"}
+           "note": "activations from pinned host memory and outputs back to it every step, on copy streams "
+                   "ordered by events per batch (largest batch first); weights resident"}
 
     # ---- prefill GEMM (single GPU numbers; N-sharded when world > 1) ----
     prefill = []

@@ -72,6 +72,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int FMT> struct Decoder;
 
 template <> struct Decoder<kQ4_K> {
+  static constexpr int kShare = 1;  // k-blocks served by one fetch
   // thread t -> row t/2, half h = t%2: 32 weights of group 2p+h (p = kb%4), i.e. the low / high
   // nibbles of quant bytes 32p .. 32p+31 of super-block kb/4.
   struct Ctx {
@@ -163,13 +164,18 @@ template <> struct Decoder<kQ6_K> {
   // word, both with the same qh word.  Misaligned words are rebuilt from two aligned ones, the
   // second taken from the neighbouring lane (lane 7 loads its own).
   static constexpr int kPasses = 4;
+  // Two consecutive k-blocks read the same words (the even one their low nibbles / low qh bit pairs,
+  // the odd one the high ones), so the words are fetched once per pair.
+  static constexpr int kShare = 2;
   struct Ctx {
     const uint8_t* wrow[kPasses];
     int row0, i;  // first row of the thread (pass p adds 32 p), word index 0..7
   };
   struct Raw {
     uint32_t lo[kPasses], hi[kPasses], qh[kPasses];
-    uint32_t meta[kPasses];  // scale of the low quarter | scale of the high quarter << 8 | d << 16
+    // int8 scales: low quarter | high quarter << 8 of the even k-block, the same << 16 of the odd one
+    uint32_t meta[kPasses];
+    uint32_t dbits[kPasses];  // fp16 d
   };
   struct Out {
     uint2 a[kPasses], b[kPasses];  // bf16 x 4 of the low / high quarter
@@ -191,7 +197,7 @@ template <> struct Decoder<kQ6_K> {
     return __funnelshift_r(w0, w1, sh);
   }
   __device__ static __forceinline__ Raw fetch(const Ctx& c, int kb) {
-    const int j = kb & 3, half = j >> 1, nib = j & 1;
+    const int half = (kb & 3) >> 1;  // kb and kb ^ 1 share everything fetched here
     Raw r;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
@@ -199,9 +205,10 @@ template <> struct Decoder<kQ6_K> {
       r.lo[p] = word_at(blk + 64 * half + 4 * c.i, c.i);
       r.hi[p] = word_at(blk + 64 * half + 32 + 4 * c.i, c.i);
       r.qh[p] = word_at(blk + 128 + 32 * half + 4 * c.i, c.i);
-      const uint8_t* sc = blk + 192 + 8 * half + 4 * nib + (c.i >> 2);
-      r.meta[p] = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 2) << 8) |
-                  ((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(blk + 208)) << 16);
+      const uint8_t* sc = blk + 192 + 8 * half + (c.i >> 2);
+      r.meta[p] = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 2) << 8) | ((uint32_t)__ldg(sc + 4) << 16) |
+                  ((uint32_t)__ldg(sc + 6) << 24);
+      r.dbits[p] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(blk + 208));
     }
     return r;
   }
@@ -210,9 +217,10 @@ template <> struct Decoder<kQ6_K> {
     const int lsh = 4 * nib;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
-      const float d = __half2float(__ushort_as_half((unsigned short)(r.meta[p] >> 16)));
-      const float dsa = d * (float)(int)(int8_t)(r.meta[p] & 0xFF);
-      const float dsb = d * (float)(int)(int8_t)((r.meta[p] >> 8) & 0xFF);
+      const float d = __half2float(__ushort_as_half((unsigned short)r.dbits[p]));
+      const uint32_t scales = r.meta[p] >> (16 * nib);
+      const float dsa = d * (float)(int)(int8_t)(scales & 0xFF);
+      const float dsb = d * (float)(int)(int8_t)((scales >> 8) & 0xFF);
       const uint32_t qa = ((r.lo[p] >> lsh) & 0x0F0F0F0Fu) | (((r.qh[p] >> lsh) & 0x03030303u) << 4);
       const uint32_t qb = ((r.hi[p] >> lsh) & 0x0F0F0F0Fu) | (((r.qh[p] >> (lsh + 2)) & 0x03030303u) << 4);
       float fa[4], fb[4];
@@ -320,8 +328,10 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
     typename D::Raw raw = D::fetch(ctx, 0);
     for (int kb = 0; kb < k_blocks; ++kb) {
       const int s = kb % kStages;
-      // start the loads of the next k-block before decoding this one (clamped on the last)
-      const typename D::Raw next = D::fetch(ctx, min(kb + 1, k_blocks - 1));
+      // start the loads of the next k-block (or group of k-blocks that share their words) before
+      // decoding this one (clamped on the last)
+      typename D::Raw next = raw;
+      if ((kb + 1) % D::kShare == 0) next = D::fetch(ctx, min(kb + 1, k_blocks - 1));
       typename D::Out decoded;
       D::decode(ctx, raw, kb, decoded);
       raw = next;
