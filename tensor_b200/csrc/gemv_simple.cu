@@ -62,24 +62,79 @@ __global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* mine = smem_rows + (size_t)MB * k * 4 + (size_t)warp * row_bytes_;
   const int b0 = blockIdx.y * MB;
-  for (int i = threadIdx.x; i < MB * k; i += blockDim.x) {
-    const int b = i / k, c = i - b * k;
-    xs[i] = b0 + b < m ? to_f32<XT>(x[(long long)(b0 + b) * k + c]) : 0.f;
+  // activations -> fp32, 16 bytes per load and several loads in flight per thread (a scalar loop
+  // here pays one L2 round trip per element and dominates the kernel)
+  constexpr int kPer = 16 / (int)sizeof(XT);
+  const int vecs = (MB * k) / kPer;  // K is a multiple of 32
+#pragma unroll 4
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    const int i = v * kPer, b = i / k, c = i - b * k;
+    XT tmp[kPer];
+    if (b0 + b < m) {
+      *reinterpret_cast<uint4*>(tmp) = __ldg(reinterpret_cast<const uint4*>(x + (long long)(b0 + b) * k + c));
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) xs[i + j] = to_f32<XT>(tmp[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) xs[i + j] = 0.f;
+    }
   }
   __syncthreads();
   const int chunks = row_bytes_ >> 4;
   for (long long row = (long long)blockIdx.x * kRowWarps + warp; row < n; row += (long long)gridDim.x * kRowWarps) {
     const uint4* src = reinterpret_cast<const uint4*>(w + row * row_bytes_);
+#pragma unroll 4
     for (int i = lane; i < chunks; i += 32) reinterpret_cast<uint4*>(mine)[i] = __ldg(src + i);
     __syncwarp();
     float acc[MB];
 #pragma unroll
     for (int b = 0; b < MB; ++b) acc[b] = 0.f;
-#pragma unroll 4
-    for (int c = lane; c < k; c += 32) {
-      const float wv = decode_one<FMT>(mine, c);
+    if constexpr (FMT == kQ8_0) {
+      // Lane l takes 8 consecutive weights of block l / 4 (+ 8 per step): four 2-byte loads (blocks
+      // are 34 bytes, so nothing wider is aligned), one scale conversion per 8 weights, activations
+      // as two 16-byte loads.  A byte b becomes the float 2^23 + (b ^ 0x80) = 2^23 + 128 + q with one
+      // logic op (after a byte permute for the odd bytes); subtracting 2^23 + 128 gives q exactly.
+      const int blocks = k >> 5;
+      for (int blk = lane >> 2; blk < blocks; blk += 8) {
+        const uint8_t* bp = mine + blk * 34;
+        const float d = f16_at(bp);
+        const unsigned short* q = reinterpret_cast<const unsigned short*>(bp + 2 + 8 * (lane & 3));
+        const int c0 = blk * 32 + 8 * (lane & 3);
+        float part[MB];
 #pragma unroll
-      for (int b = 0; b < MB; ++b) acc[b] = fmaf(xs[b * k + c], wv, acc[b]);
+        for (int b = 0; b < MB; ++b) part[b] = 0.f;
+        float wq[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t h = q[j];
+          const uint32_t lo = (h & 0xFFu) ^ 0x4B000080u;
+          const uint32_t hi = __byte_perm(h, 0x4B000000u, 0x7541u) ^ 0x80u;
+          wq[2 * j] = __uint_as_float(lo) - 8388736.f;
+          wq[2 * j + 1] = __uint_as_float(hi) - 8388736.f;
+        }
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+          const float4 x0 = *reinterpret_cast<const float4*>(xs + b * k + c0);
+          const float4 x1 = *reinterpret_cast<const float4*>(xs + b * k + c0 + 4);
+          // the reference contract multiplies d * q first (exact), then by x: keep that rounding
+          part[b] = fmaf(__fmul_rn(d, wq[0]), x0.x, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[1]), x0.y, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[2]), x0.z, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[3]), x0.w, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[4]), x1.x, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[5]), x1.y, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[6]), x1.z, part[b]);
+          part[b] = fmaf(__fmul_rn(d, wq[7]), x1.w, part[b]);
+          acc[b] += part[b];
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int c = lane; c < k; c += 32) {
+        const float wv = decode_one<FMT>(mine, c);
+#pragma unroll
+        for (int b = 0; b < MB; ++b) acc[b] = fmaf(xs[b * k + c], wv, acc[b]);
+      }
     }
 #pragma unroll
     for (int b = 0; b < MB; ++b) {
