@@ -202,9 +202,24 @@ template <> struct Decoder<kQ6_K> {
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
       const uint8_t* blk = c.wrow[p] + (kb >> 2) * 210;
-      r.lo[p] = word_at(blk + 64 * half + 4 * c.i, c.i);
-      r.hi[p] = word_at(blk + 64 * half + 32 + 4 * c.i, c.i);
-      r.qh[p] = word_at(blk + 128 + 32 * half + 4 * c.i, c.i);
+      // the three words sit at multiples of 4 bytes from one another: one aligned base, one
+      // misalignment, constant word offsets
+      const uintptr_t first = reinterpret_cast<uintptr_t>(blk) + 64 * half + 4 * c.i;
+      const uint32_t* base = reinterpret_cast<const uint32_t*>(first & ~uintptr_t(3));
+      const uint32_t sh = (uint32_t)(first & 2) * 8;
+      const int qh_words = 32 - 8 * half;  // (128 + 32 half) - 64 half bytes further
+      const uint32_t l0 = __ldg(base), h0 = __ldg(base + 8), q0 = __ldg(base + qh_words);
+      uint32_t l1 = __shfl_down_sync(0xffffffffu, l0, 1, 8);
+      uint32_t h1 = __shfl_down_sync(0xffffffffu, h0, 1, 8);
+      uint32_t q1 = __shfl_down_sync(0xffffffffu, q0, 1, 8);
+      if (c.i == 7) {  // the last lane of a row group has no neighbour to take the next word from
+        l1 = __ldg(base + 1);
+        h1 = __ldg(base + 9);
+        q1 = __ldg(base + qh_words + 1);
+      }
+      r.lo[p] = __funnelshift_r(l0, l1, sh);
+      r.hi[p] = __funnelshift_r(h0, h1, sh);
+      r.qh[p] = __funnelshift_r(q0, q1, sh);
       const uint8_t* sc = blk + 192 + 8 * half + (c.i >> 2);
       r.meta[p] = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 2) << 8) | ((uint32_t)__ldg(sc + 4) << 16) |
                   ((uint32_t)__ldg(sc + 6) << 24);
@@ -326,23 +341,26 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
     const typename D::Ctx ctx = D::context(w, row_bytes_, n0, N, (int)threadIdx.x - 64);
     bool ok = true;
     typename D::Raw raw = D::fetch(ctx, 0);
-    for (int kb = 0; kb < k_blocks; ++kb) {
-      const int s = kb % kStages;
-      // start the loads of the next k-block (or group of k-blocks that share their words) before
-      // decoding this one (clamped on the last)
-      typename D::Raw next = raw;
-      if ((kb + 1) % D::kShare == 0) next = D::fetch(ctx, min(kb + 1, k_blocks - 1));
-      typename D::Out decoded;
-      D::decode(ctx, raw, kb, decoded);
-      raw = next;
-      if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
-        report_timeout(0x30000u | (unsigned)kb);
-        ok = false;
-        break;
+    // K is a multiple of 256, so the k-blocks come in whole groups that share one fetch
+    for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += D::kShare) {
+      // start the loads of the next group before decoding this one (clamped on the last)
+      const typename D::Raw next = D::fetch(ctx, min(kb0 + D::kShare, k_blocks - 1));
+#pragma unroll
+      for (int j = 0; j < D::kShare; ++j) {
+        const int kb = kb0 + j;
+        const int s = kb % kStages;
+        typename D::Out decoded;
+        D::decode(ctx, raw, kb, decoded);
+        if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+          report_timeout(0x30000u | (unsigned)kb);
+          ok = false;
+          break;
+        }
+        D::store(ctx, a_tiles + s * kABytes, decoded);
+        ptx::fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
+        ptx::mbar_arrive(&full_a[s]);
       }
-      D::store(ctx, a_tiles + s * kABytes, decoded);
-      ptx::fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
-      ptx::mbar_arrive(&full_a[s]);
+      raw = next;
     }
     if (ok) {
       if (!ptx::mbar_wait(acc_full, 0)) {
