@@ -18,6 +18,8 @@
 // decode / epilogue overlaps the other's MMAs.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -26,16 +28,36 @@ namespace tb200 {
 namespace {
 
 constexpr int kTileN = 128;    // weight rows per tile (MMA M)
-constexpr int kTileTok = 256;  // tokens per tile (MMA N)
+constexpr int kMmaTok = 256;   // tokens per MMA (MMA N)
 constexpr int kBlockK = 64;    // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kStages = 2;
-constexpr int kDecodeWarps = 8;
-constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kDecodeThreads = 256;              // threads that decode one [128 x 64] weight tile
 constexpr int kABytes = kTileN * kBlockK * 2;    // 16 KB
-constexpr int kBBytes = kTileTok * kBlockK * 2;  // 32 KB
-constexpr int kTmemCols = 256;
-constexpr int kSmemBytes = kStages * (kABytes + kBBytes) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kHalfBBytes = kMmaTok * kBlockK * 2;  // 32 KB: the activation tile of one MMA
+
+// Shapes of CTA.  TT = 1: 256 tokens per tile.  TT = 2 (M above 256): 512 tokens per
+// tile, i.e. every decoded weight tile feeds two MMAs (decoding is what bounds this kernel, and
+// it is paid per weight tile, not per token), all 512 TMEM columns, one CTA per SM, and two groups
+// of decode warps that work on alternate k-blocks so that the SM keeps as many decode warps busy
+// as two narrow CTAs would.
+// G = decode warp groups (8 warps each, on alternate k-blocks).  <1, 1> is the two-CTAs-per-SM shape;
+// <1, 2> serves small M, where there are fewer CTAs than SMs anyway and a lone CTA needs all the
+// decode warps the SM can hold; <2, 2> is the 512-token shape.
+template <int TT, int G> struct Cfg {
+  static constexpr int kTileTok = kMmaTok * TT;
+  static constexpr int kGroups = G;
+  static constexpr int kAStages = 2 * G;
+  static constexpr int kBStages = 2;
+  static constexpr int kDecodeWarps = 8 * kGroups;
+  static constexpr int kThreads = (2 + kDecodeWarps) * 32;
+  static constexpr int kBBytes = kHalfBBytes * TT;
+  static constexpr int kTmemCols = kMmaTok * TT;
+  static constexpr int kCtasPerSm = (TT == 1 && G == 1) ? 2 : 1;
+  static constexpr int kEpilogueCols = kTileTok / (kDecodeWarps / 4);  // token columns per four decode warps
+  static constexpr int kSmemBytes = kAStages * kABytes + kBStages * kBBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+constexpr int kTileTok = Cfg<1, 1>::kTileTok;
+constexpr int kThreads = Cfg<1, 1>::kThreads;
+constexpr int kSmemBytes = Cfg<1, 1>::kSmemBytes;
 
 // tcgen05 shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 bytes, eight
 // rows form a 1024-byte swizzle atom (stride byte offset), version 1 (sm_100), layout type 2.
@@ -50,7 +72,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
 }
 
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 256.
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileTok >> 3) << 17) |
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kMmaTok >> 3) << 17) |
                                 ((uint32_t)(kTileN >> 4) << 24);
 
 // 2^23 + v for byte j of `bytes`
@@ -260,39 +282,44 @@ template <> struct Decoder<kQ6_K> {
   }
 };
 
-template <int FMT>
+template <int FMT, int TT, int G>
 __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, const uint8_t* __restrict__ w,
                                                   float* __restrict__ out, int M, int N, int K,
                                                   long long row_bytes_) {
+  using C = Cfg<TT, G>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = smem;
-  uint8_t* b_tiles = smem + kStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (kABytes + kBBytes));
-  uint64_t* full_a = bars;               // decode warps -> MMA
-  uint64_t* full_b = bars + kStages;     // TMA -> MMA
-  uint64_t* empty = bars + 2 * kStages;  // MMA -> producers
-  uint64_t* acc_full = bars + 3 * kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+  uint8_t* b_tiles = smem + C::kAStages * kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kAStages * kABytes + C::kBStages * C::kBBytes);
+  uint64_t* full_a = bars;                               // decode warps -> MMA
+  uint64_t* empty_a = full_a + C::kAStages;              // MMA -> decode warps
+  uint64_t* full_b = empty_a + C::kAStages;              // TMA -> MMA
+  uint64_t* empty_b = full_b + C::kBStages;              // MMA -> TMA
+  uint64_t* acc_full = empty_b + C::kBStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * kTileTok;
+  const int m0 = blockIdx.x * C::kTileTok;
   const int n0 = blockIdx.y * kTileN;
   const int k_blocks = K / kBlockK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < C::kAStages; ++s) {
       ptx::mbar_init(&full_a[s], kDecodeThreads);
+      ptx::mbar_init(&empty_a[s], 1);
+    }
+    for (int s = 0; s < C::kBStages; ++s) {
       ptx::mbar_init(&full_b[s], 1);
-      ptx::mbar_init(&empty[s], 1);
+      ptx::mbar_init(&empty_b[s], 1);
     }
     ptx::mbar_init(acc_full, 1);
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_x);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_alloc(tmem_slot, C::kTmemCols);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -301,16 +328,19 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer: activations ----------------
+    // ---------------- TMA producer: activations (one 256-token box per MMA) ----------------
     if (lane == 0) {
       for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % kStages;
-        if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+        const int s = kb % C::kBStages;
+        if (kb >= C::kBStages && !ptx::mbar_wait(&empty_b[s], ((kb / C::kBStages) - 1) & 1)) {
           report_timeout(0x10000u | (unsigned)kb);
           break;
         }
-        ptx::mbar_arrive_expect_tx(&full_b[s], kBBytes);
-        ptx::tma_load_2d(b_tiles + s * kBBytes, &tmap_x, kb * kBlockK, m0, &full_b[s]);
+        ptx::mbar_arrive_expect_tx(&full_b[s], C::kBBytes);
+#pragma unroll
+        for (int h = 0; h < TT; ++h)
+          ptx::tma_load_2d(b_tiles + s * C::kBBytes + h * kHalfBBytes, &tmap_x, kb * kBlockK, m0 + h * kMmaTok,
+                           &full_b[s]);
       }
     }
   } else if (warp == 1) {
@@ -318,40 +348,47 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
     if (lane == 0) {
       bool ok = true;
       for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t parity = (kb / kStages) & 1;
-        if (!ptx::mbar_wait(&full_a[s], parity) || !ptx::mbar_wait(&full_b[s], parity)) {
+        const int sa = kb % C::kAStages, sb = kb % C::kBStages;
+        if (!ptx::mbar_wait(&full_a[sa], (kb / C::kAStages) & 1) || !ptx::mbar_wait(&full_b[sb], (kb / C::kBStages) & 1)) {
           report_timeout(0x20000u | (unsigned)kb);
           ok = false;
           break;
         }
         ptx::tc_fence_after();
-        const uint64_t a_desc = smem_desc_sw128(ptx::smem_addr(a_tiles + s * kABytes));
-        const uint64_t b_desc = smem_desc_sw128(ptx::smem_addr(b_tiles + s * kBBytes));
+        const uint64_t a_desc = smem_desc_sw128(ptx::smem_addr(a_tiles + sa * kABytes));
 #pragma unroll
-        for (int i = 0; i < kBlockK / 16; ++i)  // advance 16 bf16 = 32 bytes = 2 descriptor units
-          ptx::umma_f16(tmem_base, a_desc + 2 * i, b_desc + 2 * i, kInstrDesc, (kb | i) ? 1u : 0u);
-        ptx::umma_commit(&empty[s]);
+        for (int h = 0; h < TT; ++h) {
+          const uint64_t b_desc = smem_desc_sw128(ptx::smem_addr(b_tiles + sb * C::kBBytes + h * kHalfBBytes));
+#pragma unroll
+          for (int i = 0; i < kBlockK / 16; ++i)  // advance 16 bf16 = 32 bytes = 2 descriptor units
+            ptx::umma_f16(tmem_base + (uint32_t)(h * kMmaTok), a_desc + 2 * i, b_desc + 2 * i, kInstrDesc,
+                          (kb | i) ? 1u : 0u);
+        }
+        ptx::umma_commit(&empty_a[sa]);
+        ptx::umma_commit(&empty_b[sb]);
       }
       ptx::umma_commit(acc_full);
     }
   } else {
     // ---------------- decode warps, then epilogue ----------------
     using D = Decoder<FMT>;
-    const typename D::Ctx ctx = D::context(w, row_bytes_, n0, N, (int)threadIdx.x - 64);
+    const int group = (warp - 2) >> 3;  // which decode group; groups take alternate fetch units
+    const typename D::Ctx ctx = D::context(w, row_bytes_, n0, N, (int)threadIdx.x - 64 - group * kDecodeThreads);
     bool ok = true;
-    typename D::Raw raw = D::fetch(ctx, 0);
-    // K is a multiple of 256, so the k-blocks come in whole groups that share one fetch
-    for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += D::kShare) {
-      // start the loads of the next group before decoding this one (clamped on the last)
-      const typename D::Raw next = D::fetch(ctx, min(kb0 + D::kShare, k_blocks - 1));
+    constexpr int kStep = C::kGroups * D::kShare;
+    // K is a multiple of 256, so the k-blocks come in whole units of kShare that share one fetch,
+    // and in whole rounds of one unit per group
+    typename D::Raw raw = D::fetch(ctx, group * D::kShare);
+    for (int kb0 = group * D::kShare; kb0 < k_blocks && ok; kb0 += kStep) {
+      // start the loads of this group's next unit before decoding this one (clamped on the last)
+      const typename D::Raw next = D::fetch(ctx, min(kb0 + kStep, k_blocks - 1));
 #pragma unroll
       for (int j = 0; j < D::kShare; ++j) {
         const int kb = kb0 + j;
-        const int s = kb % kStages;
+        const int s = kb % C::kAStages;
         typename D::Out decoded;
         D::decode(ctx, raw, kb, decoded);
-        if (kb >= kStages && !ptx::mbar_wait(&empty[s], ((kb / kStages) - 1) & 1)) {
+        if (kb >= C::kAStages && !ptx::mbar_wait(&empty_a[s], ((kb / C::kAStages) - 1) & 1)) {
           report_timeout(0x30000u | (unsigned)kb);
           ok = false;
           break;
@@ -371,11 +408,11 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
     if (ok) {
       ptx::tc_fence_after();
       const int quarter = warp & 3;            // TMEM lanes this warp may read
-      const int col_half = (warp - 2) >> 2;    // warps 2..5 take tokens 0..127, warps 6..9 128..255
+      const int col_group = (warp - 2) >> 2;   // every four decode warps take a band of token columns
       const int n = n0 + quarter * 32 + lane;  // output column (weight row) of this thread
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        const int col0 = col_half * 128 + c * 32;
+      for (int c = 0; c < C::kEpilogueCols / 32; ++c) {
+        const int col0 = col_group * C::kEpilogueCols + c * 32;
         if (m0 + col0 >= M) break;
         uint32_t acc[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col0, acc);
@@ -394,29 +431,46 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
-template <int FMT>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int FMT, int TT, int G>
+__global__ void __launch_bounds__(Cfg<TT, G>::kThreads, Cfg<TT, G>::kCtasPerSm)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ w,
                         float* __restrict__ out, int M, int N, int K, long long row_bytes_) {
-  gemm_tcgen05_body<FMT>(tmap_x, w, out, M, N, K, row_bytes_);
+  gemm_tcgen05_body<FMT, TT, G>(tmap_x, w, out, M, N, K, row_bytes_);
 }
 
 // ---- host side -------------------------------------------------------------------------------------
 #ifndef TB200_TBIN_WRAPPER
 
+template <int FMT, int TT, int G>
+cudaError_t launch_shape(const CUtensorMap& tmap, const uint8_t* w, float* out, long long m, long long n,
+                         long long k, cudaStream_t stream) {
+  using C = Cfg<TT, G>;
+  auto kernel = gemm_tcgen05_kernel<FMT, TT, G>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((unsigned)((m + C::kTileTok - 1) / C::kTileTok), (unsigned)((n + kTileN - 1) / kTileN));
+  kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, w, out, (int)m, (int)n, (int)k, row_bytes(FMT, k));
+  return cudaGetLastError();
+}
+
+// TB200_GEMM_SHAPE=11|12|22 pins <token tiles, decode groups> (tuning experiments); otherwise 512
+// tokens per tile above M = 256 and one 256-token CTA with two decode groups up to there.
 template <int FMT>
 cudaError_t launch_fmt(const CUtensorMap& tmap, const uint8_t* w, float* out, long long m, long long n,
-                       long long k, cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<FMT>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (e != cudaSuccess) return e;
-  dim3 grid((unsigned)((m + kTileTok - 1) / kTileTok), (unsigned)((n + kTileN - 1) / kTileN));
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, w, out, (int)m, (int)n, (int)k, row_bytes(FMT, k));
-  return cudaGetLastError();
+                       long long k, cudaStream_t stream, bool big_ok) {
+  static const int forced = [] {
+    const char* v = getenv("TB200_GEMM_SHAPE");
+    return v ? atoi(v) : 0;
+  }();
+  int shape = !big_ok ? 11 : (m > 256 ? 22 : 12);
+  if (forced == 11 || (big_ok && (forced == 12 || forced == 22))) shape = forced;
+  if (shape == 22) return launch_shape<FMT, 2, 2>(tmap, w, out, m, n, k, stream);
+  if (shape == 12) return launch_shape<FMT, 1, 2>(tmap, w, out, m, n, k, stream);
+  return launch_shape<FMT, 1, 1>(tmap, w, out, m, n, k, stream);
 }
 
 #endif  // TB200_TBIN_WRAPPER
@@ -427,7 +481,7 @@ constexpr int kGemmThreads = kThreads;
 template <int FMT>
 __device__ __forceinline__ void gemm_static_entry(const CUtensorMap& x, const uint8_t* w, float* out, int m, int n,
                                                   int k) {
-  gemm_tcgen05_body<FMT>(x, w, out, m, n, k, row_bytes(FMT, k));
+  gemm_tcgen05_body<FMT, 1, 1>(x, w, out, m, n, k, row_bytes(FMT, k));
 }
 
 #ifndef TB200_TBIN_WRAPPER
@@ -460,9 +514,13 @@ cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* ou
     if (detail) *detail = "cuTensorMapEncodeTiled is unavailable or rejected the activation layout";
     return cudaErrorNotSupported;
   }
+  int dev = 0, optin = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  const bool wide_ok = optin >= Cfg<2, 2>::kSmemBytes;
   switch (fmt) {
-    case kQ4_K: return launch_fmt<kQ4_K>(tmap, w, out, m, n, k, stream);
-    case kQ6_K: return launch_fmt<kQ6_K>(tmap, w, out, m, n, k, stream);
+    case kQ4_K: return launch_fmt<kQ4_K>(tmap, w, out, m, n, k, stream, wide_ok);
+    case kQ6_K: return launch_fmt<kQ6_K>(tmap, w, out, m, n, k, stream, wide_ok);
   }
   return cudaErrorInvalidValue;
 }

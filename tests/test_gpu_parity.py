@@ -219,6 +219,14 @@ def test_gemm_tcgen05_small(name, m, n, k):
 
 
 @pytest.mark.parametrize("name", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("m,n,k", [(1024, 128, 256), (1100, 200, 1024), (2048, 384, 512), (1537, 128, 2048)])
+def test_gemm_tcgen05_wide_token_tiles(name, m, n, k):
+    # M >= 1024 runs 512 tokens per tile (two MMAs per decoded weight tile, two decode groups)
+    err = _gemm_case(name, m, n, k, "fast")
+    assert err < 1e-4, err
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k"])
 def test_gemm_tcgen05_config_shape(name):
     _gemm_case(name, 256, 12288, 4096, "fast")
 
