@@ -244,8 +244,8 @@ def run_gpu(args):
     grouped = is_grouped(args, world)  # gate + up as one launch
     launches_per_step = len(BATCHES) * (len(SHAPES) - 1 if grouped else len(SHAPES))
     barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused-barrier" else 0
-    # batches above 8 run a small activation-conversion kernel ahead of each GEMV
-    barriers_per_step += sum(launches_per_step // len(BATCHES) for b in BATCHES if b > 8)
+    # batches above 1 run a small activation-conversion kernel ahead of each GEMV
+    barriers_per_step += sum(launches_per_step // len(BATCHES) for b in BATCHES if b > 1)
     if world > 1 and args.gather == "fused":
         barriers_per_step += len(BATCHES)  # the wait kernel that closes each batch
     # gate and up are needed together (one collective for both); down follows

@@ -1157,9 +1157,13 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
   // converted activations + table, placed after the counters and the partial sums
   const int ntb = m <= 8 ? 8 : 16;
   const long long prep_x_bytes = (m * k * 2 + 255) / 256 * 256;
-  // (worth a launch of its own only for the larger batches: up to 8 rows the CTAs convert faster than
-  // an extra kernel takes to come and go)
-  const long long prep_bytes = (allow_prep && m > 8) ? prep_x_bytes + ((k / 32) * ntb * 8 + 255) / 256 * 256 : 0;
+  // (measured at batch 4 and 8 as well: the extra launch, which starts while the previous kernel
+  // drains, costs less than every CTA converting its K range: 48.6 -> 46.9 us for gate+up and down)
+  static const int prep_min = [] {  // TB200_GEMV_PREP_MIN: smallest batch that uses it (tuning experiments)
+    const char* v = getenv("TB200_GEMV_PREP_MIN");
+    return v ? atoi(v) : 2;
+  }();
+  const long long prep_bytes = (allow_prep && m >= prep_min && m > 1) ? prep_x_bytes + ((k / 32) * ntb * 8 + 255) / 256 * 256 : 0;
   double best_cost = 1e300;
   // TB200_GEMV_FORCE="<k splits>:<CTAs per SM>" pins the plan search (tuning experiments only).
   static const char* forced = getenv("TB200_GEMV_FORCE");

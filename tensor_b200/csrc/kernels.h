@@ -62,7 +62,7 @@ struct GemvPlan {
   int ctas_per_sm = 1;
   int consumer_warps = 8;
   int red_bufs = 2;
-  // Batch plans (8 < m <= 16) with scratch to spare: a small kernel ahead of the GEMV converts the
+  // Batch plans (1 < m <= 16) with scratch to spare: a small kernel ahead of the GEMV converts the
   // activations once (fp16, scaled per 32-value group, fragment order) and every CTA copies the
   // result, instead of every CTA converting all of them.  Offsets into the scratch buffer; 0 = the
   // CTAs convert on their own.
