@@ -67,7 +67,8 @@ struct GemvArgs {
   int rank, world, sync;
   // batch plans: activations converted ahead of this launch (see gemv_prepare_kernel); null = convert here
   const uint16_t* x16;
-  const float2* x_table;
+  const float* x_table;    // [K / 32][NTB] group sums
+  const float* x_unscale;  // [K / 256][NTB] one factor per super-block and activation row
   float* partials;
   unsigned int* counters;
   int m;
@@ -230,15 +231,19 @@ __device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* sm
   return true;
 }
 
-// The same conversion done ONCE per GEMV by a small kernel of its own, into global scratch, in
-// exactly the layout the CTAs keep in shared memory: x16[b][k] (fp16, each aligned group of four
-// stored as [x0, x2, x1, x3]) and table[k / 32][NTB] = {sum of the staged values, unscale}, with
-// {0, 1} for the columns past m.  One thread per 8 values; K / 8 is a multiple of 32, so a warp is
-// all-valid or all-invalid and the quad shuffles are safe.
+// The conversion done ONCE per GEMV by a small kernel of its own, into global scratch, in the
+// layout the CTAs keep in shared memory: x16[b][k] (fp16, each aligned group of four stored as
+// [x0, x2, x1, x3]), table[k / 32][NTB] = sum of the staged values of a 32-value group and
+// unscale[k / 256][NTB] (zero sums / unit factors for the columns past m).  One thread per 8 values,
+// so a warp holds exactly one 256-value super-block of one row (K / 8 is a multiple of 32): the
+// power-of-two scale is one per (row, super-block) (largest magnitude -> [2^14, 2^15); bf16 -> fp16
+// is exact for every value within 2^-29 of it), found with warp shuffles alone, and the GEMV undoes
+// it once per item instead of once per group.
 #ifndef TB200_TBIN_WRAPPER
 template <bool F16>
 __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
-                                                           float2* __restrict__ table, int m, int k, int ntb) {
+                                                           float* __restrict__ table, float* __restrict__ unscale_out,
+                                                           int m, int k, int ntb) {
   // Let the GEMV behind this kernel start at once (it fills its weight ring, then waits for this
   // kernel to complete, which in turn has waited for the kernel before): the trigger must come
   // before the wait, or the GEMV could not be scheduled until the previous kernel has drained.
@@ -256,9 +261,9 @@ __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __res
       uint32_t mx = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const int e = (int)(mx >> 7);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const int e = (int)(mx >> 7);  // biased bf16 exponent of the super-block's largest magnitude
       if (e > 0 && e < 255) {
         int sh = 141 - e;
         sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
@@ -276,13 +281,15 @@ __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __res
     p.z = __byte_perm(v.z, v.w, 0x5410);
     p.w = __byte_perm(v.z, v.w, 0x7632);
     *reinterpret_cast<uint4*>(x16 + (long long)b * k + (c << 3)) = p;
-    if ((c & 3) == 0) table[(long long)(c >> 2) * ntb + b] = make_float2(sum, unscale);
+    if ((c & 3) == 0) table[(long long)(c >> 2) * ntb + b] = sum;
+    if ((c & 31) == 0) unscale_out[(long long)(c >> 5) * ntb + b] = unscale;
   }
-  // columns past m: zero sums
+  // columns past m: zero sums, unit factors
   const int groups = k >> 5, spare = ntb - m;
   for (int i = tid; i < groups * spare; i += gridDim.x * blockDim.x) {
     const int g = i / spare, b = m + (i - g * spare);
-    table[(long long)g * ntb + b] = make_float2(0.f, 1.f);
+    table[(long long)g * ntb + b] = 0.f;
+    if ((g & 7) == 0) unscale_out[(long long)(g >> 3) * ntb + b] = 1.f;
   }
 }
 #endif  // TB200_TBIN_WRAPPER
@@ -404,7 +411,8 @@ __device__ __forceinline__ Nibbles split_nibbles(uint32_t w, const NibbleConsts&
 // Shared-memory addresses (32-bit, shared window) a consumer warp needs; computed once per CTA.
 struct SmemMap {
   uint32_t xs, sx, scl;  // staged activations, group sums, this warp's scale scratch
-  uint32_t zero;         // 64 zero bytes (B fragments of batch columns past m)
+  uint32_t zero;         // zero bytes (B fragments of batch columns past m)
+  uint32_t su;           // prepared activations: unscale factors [super-block][column]
   int m;
   int stride_s, xs_stride;
   NibbleConsts nc;
@@ -414,7 +422,10 @@ struct SmemMap {
 // Shared memory holds only the m live activation rows.  PARTIAL (m below the columns of the MMA
 // tiles): a lane whose batch column is past m loads its B fragments from a block of zeros instead
 // (address and stride picked per lane), so no zero rows are stored.
-template <int NT, bool PARTIAL>
+// UNIFORM (activations prepared ahead of the launch): one unscale factor per (super-block, activation
+// row), applied once per item, so the table holds the group sums alone and a value costs two FMAs
+// per group.
+template <int NT, bool PARTIAL, bool UNIFORM>
 __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage, int sbl, int lane,
                                                float (&acc)[NT][4]) {
   constexpr int NTB = NT * 8;
@@ -448,8 +459,13 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
     const bool live = !PARTIAL || 8 * t + gid < sm.m;
     xlive[t] = live ? xrow + 8 * t * sm.xs_stride : sm.zero;  // the zero block spans all eight group offsets
   }
-  const uint32_t sxp = sm.sx + ((sbl * 8) * NTB + 2 * tig) * 8;
+  const uint32_t sxp = sm.sx + ((sbl * 8) * NTB + 2 * tig) * (UNIFORM ? 4 : 8);
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+  float item[NT][4];  // UNIFORM: this item's sums before the super-block's unscale factor
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) item[t][j] = 0.f;
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
     const uint2 wa = ptx::lds64(rowA + p * 32);
@@ -472,14 +488,32 @@ __device__ __forceinline__ void q4k_item_batch(const SmemMap& sm, uint32_t stage
           ptx::mma16816<true>(c, ax.hi02, bx.hi02, ax.hi13, bx.hi13, xb.x, xb.y, zero);
           ptx::mma16816<true>(c, ay.hi02, by.hi02, ay.hi13, by.hi13, xb.z, xb.w, c);
         }
-        const uint4 su = ptx::lds128(sxp + (g * NTB + 8 * t) * 8);  // {Sx, u} of columns 2*tig, 2*tig+1
-        const float sx0 = __uint_as_float(su.x), u0 = __uint_as_float(su.y);
-        const float sx1 = __uint_as_float(su.z), u1 = __uint_as_float(su.w);
-        acc[t][0] = fmaf(u0, fmaf(sA.x, c[0], -sA.y * sx0), acc[t][0]);
-        acc[t][1] = fmaf(u1, fmaf(sA.x, c[1], -sA.y * sx1), acc[t][1]);
-        acc[t][2] = fmaf(u0, fmaf(sB.x, c[2], -sB.y * sx0), acc[t][2]);
-        acc[t][3] = fmaf(u1, fmaf(sB.x, c[3], -sB.y * sx1), acc[t][3]);
+        if constexpr (UNIFORM) {
+          const float2 sx = ptx::lds64f(sxp + (g * NTB + 8 * t) * 4);  // group sums of columns 2*tig, 2*tig+1
+          item[t][0] = fmaf(sA.x, c[0], fmaf(-sA.y, sx.x, item[t][0]));
+          item[t][1] = fmaf(sA.x, c[1], fmaf(-sA.y, sx.y, item[t][1]));
+          item[t][2] = fmaf(sB.x, c[2], fmaf(-sB.y, sx.x, item[t][2]));
+          item[t][3] = fmaf(sB.x, c[3], fmaf(-sB.y, sx.y, item[t][3]));
+        } else {
+          const uint4 su = ptx::lds128(sxp + (g * NTB + 8 * t) * 8);  // {Sx, u} of columns 2*tig, 2*tig+1
+          const float sx0 = __uint_as_float(su.x), u0 = __uint_as_float(su.y);
+          const float sx1 = __uint_as_float(su.z), u1 = __uint_as_float(su.w);
+          acc[t][0] = fmaf(u0, fmaf(sA.x, c[0], -sA.y * sx0), acc[t][0]);
+          acc[t][1] = fmaf(u1, fmaf(sA.x, c[1], -sA.y * sx1), acc[t][1]);
+          acc[t][2] = fmaf(u0, fmaf(sB.x, c[2], -sB.y * sx0), acc[t][2]);
+          acc[t][3] = fmaf(u1, fmaf(sB.x, c[3], -sB.y * sx1), acc[t][3]);
+        }
       }
+    }
+  }
+  if constexpr (UNIFORM) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const float2 u = ptx::lds64f(sm.su + (sbl * NTB + 8 * t + 2 * tig) * 4);  // columns 2*tig, 2*tig+1
+      acc[t][0] = fmaf(u.x, item[t][0], acc[t][0]);
+      acc[t][1] = fmaf(u.y, item[t][1], acc[t][1]);
+      acc[t][2] = fmaf(u.x, item[t][2], acc[t][2]);
+      acc[t][3] = fmaf(u.y, item[t][3], acc[t][3]);
     }
   }
 }
@@ -728,15 +762,19 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       } else {
         asm volatile("fence.proxy.async.global;" ::: "memory");  // the copies below read through the async proxy
         const uint32_t x_row_bytes = (uint32_t)nsb_local * 512;
-        const uint32_t table_bytes = a.x16 ? (uint32_t)nsb_local * 8 * NTB * 8 : 0u;
+        const uint32_t table_bytes = a.x16 ? (uint32_t)nsb_local * 8 * NTB * 4 : 0u;
+        const uint32_t unscale_bytes = a.x16 ? (uint32_t)nsb_local * NTB * 4 : 0u;
         const uint16_t* src = a.x16 ? a.x16 : static_cast<const uint16_t*>(a.x);
-        if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes + table_bytes);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(xbar, (uint32_t)a.m * x_row_bytes + table_bytes + unscale_bytes);
         __syncwarp();
         if (lane < a.m)
           ptx::bulk_g2s(smem + a.off_xs + (size_t)lane * a.xs_stride, src + (long long)lane * a.k + sb0 * 256,
                         x_row_bytes, xbar);
         if (a.x16 && lane == 31)
           ptx::bulk_g2s(smem + a.off_sx, a.x_table + (long long)sb0 * 8 * NTB, table_bytes, xbar);
+        if (a.x16 && lane == 30)  // the factors sit behind the (half-size) table of group sums
+          ptx::bulk_g2s(smem + a.off_sx + (size_t)a.sb_per_split * 8 * NTB * 4, a.x_unscale + (long long)sb0 * NTB,
+                        unscale_bytes, xbar);
       }
     };
     int i = 0;
@@ -916,6 +954,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   sm.sx = pin(smem_base + a.off_sx);
   sm.scl = pin(smem_base + a.off_scl + cw * (kTileRows * kSclRowFloats * 4));
   sm.zero = pin(smem_base + a.off_zero);
+  sm.su = pin(smem_base + a.off_sx + a.sb_per_split * 8 * NTB * 4);
   sm.m = pin(a.m);
   sm.stride_s = pin(a.stride_s);
   sm.xs_stride = pin(a.xs_stride);
@@ -981,13 +1020,19 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     } else {
       float acc[NT][4];
       const bool partial_batch = sm.m < NTB;
+      const bool uniform_scale = a.x16 != nullptr;
 #pragma unroll
       for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
       for (int sbl = cw; sbl < nsb_l; sbl += Wp)
-        if (partial_batch) q4k_item_batch<NT, true>(sm, stage, sbl, lane, acc);
-        else q4k_item_batch<NT, false>(sm, stage, sbl, lane, acc);
+        if (uniform_scale) {
+          if (partial_batch) q4k_item_batch<NT, true, true>(sm, stage, sbl, lane, acc);
+          else q4k_item_batch<NT, false, true>(sm, stage, sbl, lane, acc);
+        } else {
+          if (partial_batch) q4k_item_batch<NT, true, false>(sm, stage, sbl, lane, acc);
+          else q4k_item_batch<NT, false, false>(sm, stage, sbl, lane, acc);
+        }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);
       if (ruse >= 1 && !ptx::mbar_wait(&red_empty[rb], (ruse - 1) & 1)) {
@@ -1110,6 +1155,7 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
   a.sync = 0;
   a.x16 = nullptr;
   a.x_table = nullptr;
+  a.x_unscale = nullptr;
   a.w2 = nullptr;
   a.n1 = n;
   a.counters = reinterpret_cast<unsigned int*>(scratch);
@@ -1357,8 +1403,9 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   if (plan.prep_x_offset) {
     if (!scratch || m < 2) return cudaErrorInvalidValue;
     uint16_t* x16 = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(scratch) + plan.prep_x_offset);
-    float2* table = reinterpret_cast<float2*>(static_cast<uint8_t*>(scratch) + plan.prep_table_offset);
+    float* table = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + plan.prep_table_offset);
     const int ntb = m <= 8 ? 8 : 16;
+    float* unscale = table + (k / 32) * ntb;  // behind the group sums (the region is sized for pairs)
     const long long threads = m * (k / 8);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
@@ -1370,11 +1417,13 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
     const uint16_t* xin = static_cast<const uint16_t*>(x);
-    cudaError_t e = xt == kF16 ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, (int)m, (int)k, ntb)
-                               : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, (int)m, (int)k, ntb);
+    cudaError_t e = xt == kF16
+                        ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m, (int)k, ntb)
+                        : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, unscale, (int)m, (int)k, ntb);
     if (e != cudaSuccess) return e;
     a.x16 = x16;
     a.x_table = table;
+    a.x_unscale = unscale;
   }
   const int grid = plan.k_splits * plan.row_groups;
   const bool f16 = xt == kF16;
