@@ -608,7 +608,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
   uint64_t* red_full = cbar + 1;        // [2] consumers -> reducer: partial sums of a tile are in place
   uint64_t* red_empty = red_full + 2;   // [2] reducer -> consumers: buffer may be overwritten
   uint64_t* xbar = red_empty + 2;       // activation rows have landed in shared memory
-  uint64_t* fin = xbar + 1;             // reducer -> consumers: verdict on who adds the K ranges
+  uint64_t* fin = xbar + 1;             // reducer -> consumers: whether this CTA adds the K ranges
   __shared__ int s_last;
   __shared__ int s_exit;  // warps of this CTA that have stored everything they will store
 
@@ -900,7 +900,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
       if (lane == 0) {
         s_last = (int)last;
         __threadfence_block();
-        ptx::mbar_arrive(fin);  // the consumer warps are waiting for the verdict
+        ptx::mbar_arrive(fin);  // the consumer warps are waiting for this decision
       }
       if (last) add_partials(W, W + 1);
     }
