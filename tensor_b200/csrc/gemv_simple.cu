@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __r
   extern __shared__ __align__(16) uint8_t smem_rows[];
   float* xs = reinterpret_cast<float*>(smem_rows);                       // [MB][k]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint8_t* mine = smem_rows + (size_t)MB * k * 4 + (size_t)warp * row_bytes_;
+  // two row buffers per warp: the next row is copied (cp.async) while this one is decoded
+  uint8_t* bufs = smem_rows + (size_t)MB * k * 4 + (size_t)warp * 2 * row_bytes_;
   const int b0 = blockIdx.y * MB;
   // activations -> fp32, 16 bytes per load and several loads in flight per thread (a scalar loop
   // here pays one L2 round trip per element and dominates the kernel)
@@ -81,10 +82,22 @@ __global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __r
   }
   __syncthreads();
   const int chunks = row_bytes_ >> 4;
-  for (long long row = (long long)blockIdx.x * kRowWarps + warp; row < n; row += (long long)gridDim.x * kRowWarps) {
-    const uint4* src = reinterpret_cast<const uint4*>(w + row * row_bytes_);
-#pragma unroll 4
-    for (int i = lane; i < chunks; i += 32) reinterpret_cast<uint4*>(mine)[i] = __ldg(src + i);
+  const long long row_step = (long long)gridDim.x * kRowWarps;
+  auto copy_row = [&](long long row, uint8_t* dst) {
+    if (row < n) {
+      const uint8_t* src = w + row * row_bytes_;
+      const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(dst);
+      for (int i = lane; i < chunks; i += 32)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + 16u * i), "l"(src + 16 * i) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  int cur = 0;
+  copy_row((long long)blockIdx.x * kRowWarps + warp, bufs);
+  for (long long row = (long long)blockIdx.x * kRowWarps + warp; row < n; row += row_step, cur ^= 1) {
+    const uint8_t* mine = bufs + (size_t)cur * row_bytes_;
+    copy_row(row + row_step, bufs + (size_t)(cur ^ 1) * row_bytes_);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the copy just issued has landed
     __syncwarp();
     float acc[MB];
 #pragma unroll
@@ -128,6 +141,74 @@ __global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __r
           acc[b] += part[b];
         }
       }
+    } else if constexpr (FMT == kQ6_K) {
+      // Lane l takes the 16 weights of scale group l % 16 of super-block l / 16 (+ 2 per step): their
+      // low nibbles are 16 consecutive bytes of ql (one nibble of each), their high bit pairs 16
+      // consecutive bytes of qh (one bit pair of each), read as eight 2-byte loads each (blocks are
+      // 210 bytes, so nothing wider is aligned).  (q - 32) * sc * d is exact in fp32 in any order
+      // (6 + 7 + 11 bits), so d * sc is formed once per group.
+      const int sbs = k >> 8;
+      const int g = lane & 15, half = g >> 3, quarter = (g & 7) >> 1, odd = g & 1;
+      const int nsh = (quarter >> 1) * 4, hsh = quarter * 2;
+      for (int sb = lane >> 4; sb < sbs; sb += 2) {
+        const uint8_t* bp = mine + sb * 210;
+        const unsigned short* lo = reinterpret_cast<const unsigned short*>(bp + half * 64 + (quarter & 1) * 32 + odd * 16);
+        const unsigned short* hi = reinterpret_cast<const unsigned short*>(bp + 128 + half * 32 + odd * 16);
+        const float dsc = __fmul_rn(f16_at(bp + 208), (float)(int)(int8_t)bp[192 + g]);
+        float wv[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t l16 = lo[j], h16 = hi[j];
+          const uint32_t t = ((l16 >> nsh) & 0x0F0Fu) | (((h16 >> hsh) & 0x0303u) << 4);
+          wv[2 * j] = __fmul_rn(__uint_as_float((t & 0xFFu) | 0x4B000000u) - 8388640.f, dsc);      // 2^23 + 32
+          wv[2 * j + 1] = __fmul_rn(__uint_as_float((t >> 8) | 0x4B000000u) - 8388640.f, dsc);
+        }
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+          const float4* xp = reinterpret_cast<const float4*>(xs + b * k + sb * 256 + 16 * g);
+          float part = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 xv = xp[j];
+            part = fmaf(wv[4 * j], xv.x, part);
+            part = fmaf(wv[4 * j + 1], xv.y, part);
+            part = fmaf(wv[4 * j + 2], xv.z, part);
+            part = fmaf(wv[4 * j + 3], xv.w, part);
+          }
+          acc[b] += part;
+        }
+      }
+    } else if constexpr (FMT == kQ4_0) {
+      // Lane l takes bytes 4 (l % 4) .. + 3 of block l / 4 (+ 8 per step): their low nibbles are
+      // weights 4 (l % 4) .. + 3 of the block, their high nibbles the same positions + 16.
+      const int blocks = k >> 5, qtr = lane & 3;
+      for (int blk = lane >> 2; blk < blocks; blk += 8) {
+        const uint8_t* bp = mine + blk * 18;
+        const float d = f16_at(bp);
+        const unsigned short* q16 = reinterpret_cast<const unsigned short*>(bp + 2 + 4 * qtr);
+        const uint32_t w32 = (uint32_t)q16[0] | ((uint32_t)q16[1] << 16);
+        const uint32_t lo = w32 & 0x0F0F0F0Fu, hi = (w32 >> 4) & 0x0F0F0F0Fu;
+        float wl[4], wh[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          wl[j] = __fmul_rn(__uint_as_float(((lo >> (8 * j)) & 0xFFu) | 0x4B000000u) - 8388616.f, d);  // 2^23 + 8
+          wh[j] = __fmul_rn(__uint_as_float(((hi >> (8 * j)) & 0xFFu) | 0x4B000000u) - 8388616.f, d);
+        }
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+          const float4 x0 = *reinterpret_cast<const float4*>(xs + b * k + blk * 32 + 4 * qtr);
+          const float4 x1 = *reinterpret_cast<const float4*>(xs + b * k + blk * 32 + 16 + 4 * qtr);
+          float part = fmaf(wl[0], x0.x, 0.f);
+          part = fmaf(wl[1], x0.y, part);
+          part = fmaf(wl[2], x0.z, part);
+          part = fmaf(wl[3], x0.w, part);
+          part = fmaf(wh[0], x1.x, part);
+          part = fmaf(wh[1], x1.y, part);
+          part = fmaf(wh[2], x1.z, part);
+          part = fmaf(wh[3], x1.w, part);
+          acc[b] += part;
+        }
+      }
     } else {
 #pragma unroll 4
       for (int c = lane; c < k; c += 32) {
@@ -144,8 +225,9 @@ __global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __r
       if (lane == 0 && b0 + b < m)
         for (int d = 0; d < out.count; ++d) out.ptr[d][(long long)(b0 + b) * out.ld + row] = v;
     }
-    __syncwarp();  // the row buffer is rewritten by the next iteration
+    __syncwarp();  // this buffer is the target of the copy the next iteration issues
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 template <int FMT, typename XT, int MB>
@@ -154,8 +236,11 @@ static cudaError_t launch_rows(const XT* x, const uint8_t* w, const OutSpec& out
   auto kernel = gemv_rows_kernel<FMT, XT, MB>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
+  // persistent-ish: a few CTAs per SM, every warp walking its rows with the next one in flight
   const long long row_ctas = (n + kRowWarps - 1) / kRowWarps;
-  const unsigned gx = (unsigned)(row_ctas < 148 * 8 ? row_ctas : 148 * 8);
+  const int per_sm = 232448 / (smem + 1024) < 1 ? 1 : 232448 / (smem + 1024);  // what shared memory allows
+  const long long resident = 148LL * (per_sm > 4 ? 4 : per_sm);
+  const unsigned gx = (unsigned)(row_ctas < resident ? row_ctas : resident);
   const unsigned gy = (unsigned)((m + MB - 1) / MB);
   kernel<<<dim3(gx, gy), kRowWarps * 32, smem, stream>>>(x, w, out, (int)m, n, (int)k, (int)row_bytes(FMT, k));
   return cudaGetLastError();
@@ -170,8 +255,8 @@ static cudaError_t launch_typed(const void* x, const uint8_t* w, const OutSpec& 
   // (measured: 1.9x faster than the kernel below for Q8_0 / Q4_0 4096 x 4096 at batch 1; at larger
   // batches, or when the staging leaves room for a single CTA per SM only, it is not)
   if (!weights_bf16 && m == 1 && rb % 16 == 0) {
-    const long long smem = k * 4 + kRowWarps * rb;
-    if (smem <= 100 * 1024) return launch_rows<FMT, XT, 1>(xp, w, out, m, n, k, (int)smem, stream);
+    const long long smem = k * 4 + 2 * kRowWarps * rb;  // activations + two row buffers per warp
+    if (smem <= 110 * 1024) return launch_rows<FMT, XT, 1>(xp, w, out, m, n, k, (int)smem, stream);
   }
   const int warps = 8;
   dim3 block(warps * 32);
