@@ -4,6 +4,8 @@
 // not a multiple of 16 bytes, K not a multiple of 256, m > 16 for the GEMV).  Contract:
 // benchmarks/kernels/showcase/triton_kernels.py:213-222 (fp32 weight x fp32 activation); with
 // weights_bf16 the decoded weight is rounded to bf16 first (the GEMM contract, :201-207).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -50,8 +52,8 @@ __global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__
 // activations to fp32 once, and every warp copies its weight row with coalesced 16-byte loads before
 // it decodes it (lane l takes weights l, l + 32, ...: consecutive bytes of a block, no bank
 // conflicts, the block scale a broadcast).  Decode GEMVs of the formats the pipelined kernel does not
-// cover spend their time here at batch 1; it needs rows that are a multiple of 16 bytes and
-// activations plus eight rows that fit in shared memory twice per SM.
+// cover spend their time here at batches up to 4; it needs rows that are a multiple of 16 bytes and
+// activations plus sixteen rows that fit in shared memory.
 constexpr int kRowWarps = 8;
 template <int FMT, typename XT, int MB>
 __global__ void __launch_bounds__(kRowWarps * 32) gemv_rows_kernel(const XT* __restrict__ x,
@@ -252,11 +254,20 @@ static cudaError_t launch_typed(const void* x, const uint8_t* w, const OutSpec& 
   const XT* xp = static_cast<const XT*>(x);
   // decode GEMVs (fp32 weights) whose rows and activations fit: the shared-memory staged kernel
   const long long rb = row_bytes(FMT, k);
-  // (measured: 1.9x faster than the kernel below for Q8_0 / Q4_0 4096 x 4096 at batch 1; at larger
-  // batches, or when the staging leaves room for a single CTA per SM only, it is not)
-  if (!weights_bf16 && m == 1 && rb % 16 == 0) {
-    const long long smem = k * 4 + 2 * kRowWarps * rb;  // activations + two row buffers per warp
-    if (smem <= 110 * 1024) return launch_rows<FMT, XT, 1>(xp, w, out, m, n, k, (int)smem, stream);
+  // (measured against the kernel below at 4096 x 4096: Q8_0 4x faster at batch 1, 2.5x at batch 2,
+  // 1.4x at batch 3-4; from batch 5 on, where the weights are decoded once per four rows, it loses)
+  static const int rows_max_m = [] {  // TB200_ROWS_MAX_M: largest batch the staged kernel takes (tuning)
+    const char* v = getenv("TB200_ROWS_MAX_M");
+    return v ? atoi(v) : 4;
+  }();
+  if (!weights_bf16 && m <= rows_max_m && m <= 16 && rb % 16 == 0) {
+    const int mb = m == 1 ? 1 : (m == 2 ? 2 : 4);
+    const long long smem = (long long)mb * k * 4 + 2 * kRowWarps * rb;  // activations + two row buffers per warp
+    if (smem <= (m == 1 ? 110 : 200) * 1024) {
+      if (mb == 1) return launch_rows<FMT, XT, 1>(xp, w, out, m, n, k, (int)smem, stream);
+      if (mb == 2) return launch_rows<FMT, XT, 2>(xp, w, out, m, n, k, (int)smem, stream);
+      return launch_rows<FMT, XT, 4>(xp, w, out, m, n, k, (int)smem, stream);
+    }
   }
   const int warps = 8;
   dim3 block(warps * 32);
