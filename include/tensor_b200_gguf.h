@@ -105,9 +105,10 @@ int32_t tb200_gguf_version(void);
  * format id is unknown.  Row stride is k / block * bytes (triton_kernels.py:136,144,164). */
 int64_t tb200_gguf_weight_bytes(int32_t format, int64_t n, int64_t k);
 
-/* Scratch bytes the GEMV may use for its split-K partial sums at this shape on the current
- * device (0 when the chosen kernel never splits K).  Passing less (or NULL) is legal: the
- * library then picks a kernel that needs none. */
+/* Scratch bytes the GEMV can use at this shape on the current device: arrival counters and
+ * split-K partial sums where K is split across CTAs, and for 1 < m <= 16 the activations converted
+ * once per call (fp16 in fragment order, group sums, scale factors).  0 when neither applies.
+ * Passing less (or NULL) is legal: the library then picks a plan that fits what it is given. */
 int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int64_t k);
 
 /* The launch plan the pipelined GEMV would use with `scratch_bytes` of scratch available:
@@ -145,7 +146,8 @@ int32_t tb200_gguf_dequant(int32_t format, const void *w, float *out, int64_t n,
  * accumulation, 1 <= m.  Replaces `gemv_packed` (showcase/kernels.py:116-119; contract
  * showcase/benchmark.py:468-470, triton_kernels.py:213-222).  x_dtype is TENSOR_FLOAT16,
  * TENSOR_BFLOAT16 or TENSOR_FLOAT32.  If scratch is used, it must start zeroed before the first
- * call; every call leaves it zeroed again.  Calls that share scratch must not overlap. */
+ * call; every call leaves its counters zeroed again (the rest is overwritten before it is read).
+ * Calls that share scratch must not overlap. */
 int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
                         int64_t m, int64_t n, int64_t k, void *scratch, int64_t scratch_bytes,
                         int32_t variant, void *stream, TensorErrorV1 *error);
