@@ -210,14 +210,6 @@ template <> struct Decoder<kQ6_K> {
     for (int p = 0; p < kPasses; ++p) c.wrow[p] = w + (long long)min(n0 + c.row0 + 32 * p, N - 1) * row_bytes_;
     return c;
   }
-  __device__ static __forceinline__ uint32_t word_at(const uint8_t* p, int i) {
-    const uint32_t* a = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(p) & ~uintptr_t(3));
-    const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 2) * 8;
-    const uint32_t w0 = __ldg(a);
-    uint32_t w1 = __shfl_down_sync(0xffffffffu, w0, 1, 8);
-    if (i == 7) w1 = __ldg(a + 1);
-    return __funnelshift_r(w0, w1, sh);
-  }
   __device__ static __forceinline__ Raw fetch(const Ctx& c, int kb) {
     const int half = (kb & 3) >> 1;  // kb and kb ^ 1 share everything fetched here
     Raw r;
