@@ -42,6 +42,12 @@ constexpr int kMaxConsumerWarps = 16;
 constexpr int kNarrowWarps = 8;
 constexpr int kThreadsNarrow = (kNarrowWarps + 2) * 32;
 constexpr int kThreadsWide = (kMaxConsumerWarps + 2) * 32;
+// Weight tiles a CTA requests before it waits for the kernel before it (programmatic dependent
+// launch).  Whatever is requested earlier arrives earlier, but the activations, which can only be
+// requested after that wait, come back behind every weight byte this SM has asked for by then, and
+// nothing is decoded before they are staged.  One tile measured best at every batch (two: +4 % at
+// batch 1; the whole ring: +4..8 %).
+constexpr int kTilesBeforeWait = 1;
 constexpr int kTileRows = 16;
 constexpr int kMaxStages = 8;
 constexpr int kCounterBytes = 4096;  // one arrival counter per group of CTAs that share row tiles (<= 1024)
@@ -780,11 +786,8 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
     int i = 0;
     for (int rt = rg; rt < a.row_tiles; rt += a.row_groups, ++i) {
       const int s = i % S;
-      // Batch mode: the ring is filled first (nothing frees a stage before the activations arrive).
-      // m == 1: the decode warps load x themselves and their loads would come back behind every
-      // weight byte already requested by this SM, so one stage is held back until the dependency
-      // has resolved and those loads are on their way.
-      if (i == (GROUPS && S > 2 ? S - 1 : S)) fetch_activations();
+      // the dependency wait and the activation requests come after the first tile(s), see kTilesBeforeWait
+      if (i == min(S, kTilesBeforeWait)) fetch_activations();
       if (i >= S && !ptx::mbar_wait(&empty[s], ((i / S) - 1) & 1)) {
         report_timeout(0x10000u | (unsigned)s);
         break;
@@ -817,7 +820,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
           ptx::bulk_g2s(dst + (size_t)lane * a.stride_s, wsrc + (wrow0 + lane) * a.row_bytes, range_bytes, &full[s]);
       }
     }
-    if (i <= (GROUPS && S > 2 ? S - 1 : S)) fetch_activations();
+    if (i <= min(S, kTilesBeforeWait)) fetch_activations();
     cta_done();
     return;
   }
