@@ -78,6 +78,15 @@ def workload_config(world: int, gather: str = "fused", grouped: bool = False):
     }
 
 
+def reference_config(cores: int):
+    gpu = workload_config(1)
+    return {"workload": gpu["workload"], "format": gpu["format"], "batches": gpu["batches"],
+            "activations": "bf16 values widened to fp32", "output": "fp32",
+            "launches": "nine GEMV calls per step, one after another",
+            "l2": "one resident set of weights (115 MB, larger than the host caches)",
+            "parallelism": f"OpenMP over weight rows, {cores} host threads, rank 0 only"}
+
+
 # ---------------------------------------------------------------------------------------------
 # reference arm / CPU baseline: the C port of the reference arithmetic on the host cores
 # ---------------------------------------------------------------------------------------------
@@ -88,6 +97,7 @@ def cpu_port_gemv_rate(seconds: float, batches=BATCHES):
     from oracle import c_oracle
     from oracle import gguf_oracle as oracle
 
+    c_oracle.use_all_cores()  # process launchers export OMP_NUM_THREADS=1; the baseline uses every host core
     cases = []
     for i, (_, n, k) in enumerate(SHAPES):
         raw = oracle.make_weights(FORMAT, n, k, seed=100 + i)
@@ -131,8 +141,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        # the same config object as the GPU arm prints for these arguments
-        "data": "synthetic", "config": workload_config(args.gpus, args.gather, is_grouped(args, args.gpus)),
+        # the same workload as the GPU arm; the other keys describe how this arm runs it
+        "data": "synthetic", "config": reference_config(c_oracle.threads()),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": c_oracle.threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

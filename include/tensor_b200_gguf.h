@@ -96,7 +96,10 @@ typedef struct TensorErrorV1 {
 /* kernel selection: 0 lets the library choose */
 #define TB200_VARIANT_AUTO 0
 #define TB200_VARIANT_SIMPLE 1 /* SIMT fp32 kernels, any shape */
-#define TB200_VARIANT_FAST 2   /* GEMV: bulk-copy pipeline + mma.sync; GEMM: tcgen05 / TMEM */
+#define TB200_VARIANT_FAST 2   /* a pipelined tensor-core kernel or an error: GEMV bulk-copy ring + mma.sync, GEMM tcgen05 */
+#define TB200_VARIANT_MMA 3    /* GEMV only: the same as FAST */
+#define TB200_VARIANT_TC 4     /* GEMV only: the persistent tcgen05 / TMEM kernel (needs scratch), or an error;
+                                * never chosen by AUTO: measured slower than the mma.sync pipeline on B200 */
 
 /* Library / ABI version: (major << 16) | minor. */
 int32_t tb200_gguf_version(void);
@@ -223,6 +226,43 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
                                           void *scratch, int64_t scratch_bytes, int32_t variant,
                                           uint32_t *const *pads, int32_t rank, int32_t world,
                                           int32_t sync, void *stream, TensorErrorV1 *error);
+
+/* Several independent decode GEMVs in one call: what a decoder layer issues back to back -- q/k/v,
+ * gate/up, or one projection at several batches.  The reference launches one kernel per projection
+ * (showcase/kernels.py:114-119, showcase/benchmark.py:276-290) and pays its host path per launch
+ * (runtime/executable.py:87-149); here the host path is paid once and the launches overlap each
+ * other's tails.  Item i computes outs[d][row * out_ld + col] = x_i . dequant(w_i)^T for every
+ * destination d < out_count (outs[1..] are peer-mapped outputs of other ranks in N-sharded runs, with
+ * the column window already added to the pointers).  Items must not depend on one another.
+ * Neighbouring items with the same x pointer, m, k and format run as one grouped launch.
+ * variant: TB200_VARIANT_AUTO ... as for tb200_gguf_gemv; TB200_VARIANT_TC runs the whole list as ONE
+ * persistent tcgen05 / TMEM launch (Q4_K, 2-byte activations, m <= 16).
+ * scratch: tb200_gguf_gemv_list_scratch_bytes, 256-byte aligned, zeroed before first use, not shared
+ * with a call that may overlap.  pads / rank / world / sync as in tb200_gguf_gemv_sharded_sync (sync 0
+ * on one GPU): the first launch waits, the last one signals. */
+#define TB200_GEMV_LIST_MAX 12
+typedef struct TB200GemvItem {
+  int32_t format;  /* TB200_Q4_K ... */
+  int32_t x_dtype; /* TENSOR_FLOAT16 / TENSOR_BFLOAT16 / TENSOR_FLOAT32 */
+  const void *x;   /* [m, k] */
+  const void *w;   /* [n, k] raw blocks */
+  float *outs[TB200_MAX_PEERS];
+  int32_t out_count;
+  int32_t reserved;
+  int64_t out_ld;
+  int64_t m, n, k;
+} TB200GemvItem;
+int64_t tb200_gguf_gemv_list_scratch_bytes(const TB200GemvItem *items, int32_t count);
+int32_t tb200_gguf_gemv_list(const TB200GemvItem *items, int32_t count, void *scratch,
+                             int64_t scratch_bytes, int32_t variant, uint32_t *const *pads, int32_t rank,
+                             int32_t world, int32_t sync, void *stream, TensorErrorV1 *error);
+
+/* How long a kernel of this library waits for another GPU's signal before it gives up, records
+ * 0x80000 | peer (GEMV) or 0x90000 | peer (barrier) in the status word and returns; 0 restores the
+ * default of two seconds.  Process-wide; applies to launches made after the call.  A rank whose wait
+ * ran out does not signal for that launch, so its peers' waits run out in turn: read
+ * tb200_gguf_device_status on every rank and re-zero the pads before going on. */
+int32_t tb200_peer_set_wait_limit(uint64_t nanoseconds);
 
 /* Barrier between the GPUs of one box over peer-mapped signal pads.  pads is a HOST array of
  * `world` device addresses: pads[i] is rank i's pad (TB200_SIGNAL_PAD_BYTES, 4-byte aligned,

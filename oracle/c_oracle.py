@@ -41,6 +41,7 @@ def lib():
         _lib.gguf_oracle_row_bytes.restype = i64
         _lib.gguf_oracle_row_bytes.argtypes = [ctypes.c_int, i64]
         _lib.gguf_oracle_threads.restype = ctypes.c_int
+        _lib.gguf_oracle_set_threads.argtypes = [ctypes.c_int]
         _lib.gguf_oracle_dequant.argtypes = [ctypes.c_int, u8p, i64, i64, f32p]
         _lib.gguf_oracle_gemv.argtypes = [ctypes.c_int, u8p, i64, i64, f32p, i64, f32p]
         _lib.gguf_oracle_gemm.argtypes = [ctypes.c_int, u8p, i64, i64, f32p, i64, ctypes.c_int, f32p]
@@ -57,6 +58,13 @@ def _f32(a):
 
 def threads() -> int:
     return int(lib().gguf_oracle_threads())
+
+
+def use_all_cores() -> int:
+    """Run on every core this process may be scheduled on, whatever OMP_NUM_THREADS says (process
+    launchers set it to 1 for their children); returns the thread count now in effect."""
+    lib().gguf_oracle_set_threads(len(os.sched_getaffinity(0)))
+    return threads()
 
 
 def _raw(raw, fmt, n, k):

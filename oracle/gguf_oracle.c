@@ -153,6 +153,16 @@ int gguf_oracle_threads(void) {
 #endif
 }
 
+/* Launchers such as torch.distributed.run export OMP_NUM_THREADS=1 to their children; a timed CPU
+ * baseline sets the thread count it wants explicitly (the cores the process may run on). */
+void gguf_oracle_set_threads(int count) {
+#ifdef _OPENMP
+  if (count > 0) omp_set_num_threads(count);
+#else
+  (void)count;
+#endif
+}
+
 /* raw [n, row_bytes] -> out fp32 [n, k] */
 int gguf_oracle_dequant(int fmt, const uint8_t *raw, int64_t n, int64_t k, float *out) {
   int64_t rb = gguf_oracle_row_bytes(fmt, k);

@@ -8,10 +8,11 @@ package does not load the library; the first operation does, and fails loudly if
 from ._native import AbiError, LIB_PATH, TensorRuntimeError
 from .formats import Q4_0, Q4_K, Q6_K, Q8_0, BlockFormat, get_format
 from .kernel import GgufKernel, gguf
-from .ops import dequantize, device_status, gemm, gemv, gemv_plan, gemv_scratch_bytes, weight_bytes
+from .ops import (GemvList, dequantize, device_status, gemm, gemv, gemv_plan, gemv_scratch_bytes,
+                  set_peer_wait_limit, weight_bytes)
 
 __all__ = [
-    "AbiError", "BlockFormat", "GgufKernel", "LIB_PATH", "Q4_0", "Q4_K", "Q6_K", "Q8_0",
+    "AbiError", "BlockFormat", "GemvList", "GgufKernel", "LIB_PATH", "Q4_0", "Q4_K", "Q6_K", "Q8_0",
     "TensorRuntimeError", "dequantize", "device_status", "gemm", "gemv", "gemv_scratch_bytes",
-    "gemv_plan", "get_format", "gguf", "weight_bytes",
+    "gemv_plan", "get_format", "gguf", "set_peer_wait_limit", "weight_bytes",
 ]

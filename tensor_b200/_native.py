@@ -19,6 +19,7 @@ EXPORTS = (
     "tb200_gguf_gemv_static", "tb200_gguf_gemv_sharded", "tb200_gguf_gemv_sharded_sync", "tb200_peer_barrier",
     "tb200_peer_sync", "tb200_gguf_gemv_pair", "tb200_gguf_gemv_pair_sharded_sync",
     "tb200_peer_export", "tb200_peer_open", "tb200_peer_close",
+    "tb200_gguf_gemv_list", "tb200_gguf_gemv_list_scratch_bytes", "tb200_peer_set_wait_limit",
 )
 
 
@@ -94,6 +95,13 @@ def lib():
     handle.tb200_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp), err]
     handle.tb200_peer_close.restype = i32
     handle.tb200_peer_close.argtypes = [vp, err]
+    handle.tb200_gguf_gemv_list_scratch_bytes.restype = i64
+    handle.tb200_gguf_gemv_list_scratch_bytes.argtypes = [ctypes.POINTER(abi.TB200GemvItem), i32]
+    handle.tb200_gguf_gemv_list.restype = i32
+    handle.tb200_gguf_gemv_list.argtypes = [ctypes.POINTER(abi.TB200GemvItem), i32, vp, i64, i32, ctypes.POINTER(vp),
+                                            i32, i32, i32, vp, err]
+    handle.tb200_peer_set_wait_limit.restype = i32
+    handle.tb200_peer_set_wait_limit.argtypes = [ctypes.c_uint64]
     handle.tb200_gguf_gemm.restype = i32
     handle.tb200_gguf_gemm.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, i32, vp, err]
     for name in ("tb200_gguf_dequant_v1", "tb200_gguf_gemv_v1", "tb200_gguf_gemm_v1"):

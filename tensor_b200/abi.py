@@ -46,11 +46,20 @@ class TensorErrorV1(ctypes.Structure):
     _fields_ = [("code", ctypes.c_int32), ("message", ctypes.c_char * 508)]
 
 
+class TB200GemvItem(ctypes.Structure):
+    """One projection of ``tb200_gguf_gemv_list`` (include/tensor_b200_gguf.h)."""
+    _fields_ = [("format", ctypes.c_int32), ("x_dtype", ctypes.c_int32), ("x", ctypes.c_void_p),
+                ("w", ctypes.c_void_p), ("outs", ctypes.c_void_p * 8), ("out_count", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("out_ld", ctypes.c_int64), ("m", ctypes.c_int64),
+                ("n", ctypes.c_int64), ("k", ctypes.c_int64)]
+
+
 assert ctypes.sizeof(TensorBufferV1) == 48
 assert ctypes.sizeof(TensorArgumentV1) == 64
 assert ctypes.sizeof(TensorStreamV1) == 16
 assert ctypes.sizeof(TensorCallV1) == 72
 assert ctypes.sizeof(TensorErrorV1) == 512
+assert ctypes.sizeof(TB200GemvItem) == 128
 
 
 def buffer_argument(address: int, byte_size: int, dtype: int, ordinal: int, shape=None) -> TensorArgumentV1:

@@ -67,13 +67,10 @@ def _compile(name: str) -> tuple[str, str]:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if os.environ.get("TB200_GEMV_TRACE"):
-        # diagnostic build: the GEMV records a per-CTA timeline and prints it at process exit
-        if "-DTB200_GEMV_TRACE" not in COMMON:
-            COMMON.append("-DTB200_GEMV_TRACE")
-    for extra in os.environ.get("TB200_EXTRA_DEFINES", "").split():
-        # experiment switches, e.g. TB200_EXTRA_DEFINES="TB200_SHIFT_BY_MULTIPLY"
-        if f"-D{extra}" not in COMMON:
-            COMMON.append(f"-D{extra}")
+        # diagnostic build: the GEMV kernels record a per-CTA timeline and print it at process exit
+        for flag in ("-DTB200_GEMV_TRACE", "-DTB200_TC_TRACE"):
+            if flag not in COMMON:
+                COMMON.append(flag)
     os.makedirs(LIB_DIR, exist_ok=True)
     stamp = os.path.join(LIB_DIR, "build.sha256")
     fp = _fingerprint()

@@ -10,6 +10,8 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "../../include/tensor_b200_gguf.h"
 #include "common.cuh"
@@ -54,6 +56,25 @@ const DeviceInfo* device_info(cudaError_t* err) {
   }
   if (err) *err = cudaSuccess;
   return &d;
+}
+
+cudaError_t allow_full_shared_memory(const void* kernel) {
+  static std::mutex lock;
+  static std::vector<std::pair<const void*, int>> done;  // (kernel, device) pairs already opted in
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return e;
+  std::lock_guard<std::mutex> guard(lock);
+  for (const auto& entry : done)
+    if (entry.first == kernel && entry.second == dev->ordinal) return cudaSuccess;
+  cudaFuncAttributes attr;
+  e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess) return e;
+  // statically declared shared memory counts against the same limit
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           dev->max_smem_optin - (int)attr.sharedSizeBytes);
+  if (e == cudaSuccess) done.emplace_back(kernel, dev->ordinal);
+  return e;
 }
 
 }  // namespace tb200
@@ -206,10 +227,12 @@ int32_t tb200_gguf_gemm_launch_config(int32_t format, int64_t m, int64_t n, int6
 }
 
 int32_t tb200_gguf_device_status(uint32_t* status, TensorErrorV1* error) {
-  unsigned int a = 0, b = 0, c = 0;
+  unsigned int a = 0, b = 0, c = 0, t = 0;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return cuda_fail(error, "cudaDeviceSynchronize", e);
+  if ((e = read_gemv_tc_status(&t, true)) != cudaSuccess) return cuda_fail(error, "reading GEMV status", e);
   if ((e = read_gemv_status(&a, true)) != cudaSuccess) return cuda_fail(error, "reading GEMV status", e);
+  if (!a) a = t;
   if ((e = read_gemm_status(&b, true)) != cudaSuccess) return cuda_fail(error, "reading GEMM status", e);
   if ((e = read_barrier_status(&c, true)) != cudaSuccess) return cuda_fail(error, "reading barrier status", e);
   if (status) *status = a ? a : (b ? b : c);
@@ -249,6 +272,31 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (int32_t s = require_device(error, &dev)) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint8_t* wp = static_cast<const uint8_t*>(w);
+  // The tensor-memory kernel runs only on request: measured on B200 it is slower than the mma.sync
+  // pipeline at every batch (tcgen05 takes in one 128-row k-slice per 4 cycles whatever the batch).
+  if (variant == TB200_VARIANT_TC) {
+    TcLaunchItem item{};
+    item.fmt = format;
+    item.xt = x_dtype;
+    item.x = x;
+    item.w = wp;
+    item.out = out;
+    item.m = m;
+    item.n = n;
+    item.k = k;
+    item.x_share = -1;
+    const long long need = gemv_tc_scratch_bytes(&item, 1, *dev);  // 0: the shape is not covered
+    if (need && scratch && scratch_bytes >= need) {
+      cudaError_t e = launch_gemv_tc(&item, 1, scratch, scratch_bytes, st, peers);
+      if (e != cudaSuccess) return cuda_fail(error, "tensor-memory GEMV launch", e);
+      return ok(error);
+    }
+    return fail(error, TENSOR_ERROR_ARGUMENT,
+                "the tensor-memory GEMV needs format 12, 2-byte activations, m <= 16 and %lld bytes of scratch "
+                "(format %d, dtype %d, m=%lld, n=%lld, k=%lld, scratch %lld)",
+                need, format, x_dtype, (long long)m, (long long)n, (long long)k,
+                (long long)(scratch ? scratch_bytes : 0));
+  }
   if (variant != TB200_VARIANT_SIMPLE) {
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
     if (plan.supported) {
@@ -256,7 +304,7 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch", e);
       return ok(error);
     }
-    if (variant == TB200_VARIANT_FAST)
+    if (variant == TB200_VARIANT_FAST || variant == TB200_VARIANT_MMA)
       return fail(error, TENSOR_ERROR_ARGUMENT,
                   "the pipelined GEMV does not cover format %d, dtype %d, m=%lld, n=%lld, k=%lld", format, x_dtype,
                   (long long)m, (long long)n, (long long)k);
@@ -289,8 +337,19 @@ int32_t check_gemv_scalars(TensorErrorV1* error, int32_t format, int32_t x_dtype
   if (int32_t s = check_shape(error, format, m, n, k)) return s;
   if (x_dtype != TENSOR_FLOAT16 && x_dtype != TENSOR_BFLOAT16 && x_dtype != TENSOR_FLOAT32)
     return fail(error, TENSOR_ERROR_ARGUMENT, "activation dtype %d is not float16, bfloat16 or float32", x_dtype);
-  if (variant < 0 || variant > 2) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (variant < 0 || variant > TB200_VARIANT_TC) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
   return TENSOR_OK;
+}
+
+// Several projections as ONE persistent launch of the tensor-memory kernel; false if the list does
+// not qualify (the caller then launches them one by one).
+bool try_list(const TcLaunchItem* items, int count, void* scratch, int64_t scratch_bytes, const DeviceInfo& dev,
+              cudaStream_t st, const PeerSync* peers, cudaError_t* launch_error) {
+  *launch_error = cudaSuccess;
+  const long long need = gemv_tc_scratch_bytes(items, count, dev);
+  if (!need || !scratch || scratch_bytes < need) return false;
+  *launch_error = launch_gemv_tc(items, count, scratch, scratch_bytes, st, peers);
+  return true;
 }
 }  // namespace
 
@@ -372,6 +431,28 @@ int32_t tb200_gguf_gemv_pair(int32_t format, int32_t x_dtype, const void* x, con
     if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
     const DeviceInfo* dev;
     if (int32_t s = require_device(error, &dev)) return s;
+    if (variant == TB200_VARIANT_TC) {
+      TcLaunchItem pair[2]{};
+      for (int i = 0; i < 2; ++i) {
+        pair[i].fmt = format;
+        pair[i].xt = x_dtype;
+        pair[i].x = x;
+        pair[i].m = m;
+        pair[i].k = k;
+        pair[i].x_share = i - 1;
+      }
+      pair[0].w = static_cast<const uint8_t*>(w1);
+      pair[0].n = n1;
+      pair[0].out = single_output(out, n);
+      pair[1].w = static_cast<const uint8_t*>(w2);
+      pair[1].n = n2;
+      pair[1].out = single_output(out + n1, n);
+      cudaError_t e;
+      if (try_list(pair, 2, scratch, scratch_bytes, *dev, static_cast<cudaStream_t>(stream), nullptr, &e)) {
+        if (e != cudaSuccess) return cuda_fail(error, "tensor-memory GEMV launch (two weights)", e);
+        return ok(error);
+      }
+    }
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
     if (plan.supported && plan.k_splits == 1 && n1 % kGemvTileRows == 0) {
       OutSpec both = single_output(out, n);
@@ -428,6 +509,33 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
     if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
     const DeviceInfo* dev;
     if (int32_t s = require_device(error, &dev)) return s;
+    if (variant == TB200_VARIANT_TC) {
+      TcLaunchItem pair[2]{};
+      for (int i = 0; i < 2; ++i) {
+        pair[i].fmt = format;
+        pair[i].xt = x_dtype;
+        pair[i].x = x;
+        pair[i].m = m;
+        pair[i].k = k;
+        pair[i].x_share = i - 1;
+        pair[i].out.count = out_count;
+        pair[i].out.ld = out_ld;
+      }
+      pair[0].w = static_cast<const uint8_t*>(w1);
+      pair[0].n = n1;
+      pair[1].w = static_cast<const uint8_t*>(w2);
+      pair[1].n = n2;
+      for (int i = 0; i < out_count; ++i) {
+        pair[0].out.ptr[i] = outs1[i] + col_offset1;
+        pair[1].out.ptr[i] = outs2[i] + col_offset2;
+      }
+      cudaError_t e;
+      if (try_list(pair, 2, scratch, scratch_bytes, *dev, static_cast<cudaStream_t>(stream),
+                   peers.flags ? &peers : nullptr, &e)) {
+        if (e != cudaSuccess) return cuda_fail(error, "tensor-memory GEMV launch (two weights, sharded)", e);
+        return ok(error);
+      }
+    }
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
     if (plan.supported && plan.k_splits == 1 && n1 % kGemvTileRows == 0) {
       OutSpec spec{};
@@ -507,7 +615,7 @@ int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void* x, const vo
   if (int32_t s = check_shape(error, format, m, n, k)) return s;
   if (x_dtype != TENSOR_BFLOAT16)
     return fail(error, TENSOR_ERROR_ARGUMENT, "the GEMM takes bfloat16 activations (dtype 13), got %d", x_dtype);
-  if (variant < 0 || variant > 2) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (variant < 0 || variant > TB200_VARIANT_FAST) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
   if (m == 0 || n == 0) return ok(error);
   if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
   if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
@@ -530,6 +638,136 @@ int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void* x, const vo
   cudaError_t e = launch_gemv_simple(format, x_dtype, x, wp, out, m, n, k, true, st);
   if (e != cudaSuccess) return cuda_fail(error, "GEMM launch", e);
   return ok(error);
+}
+
+namespace {
+int32_t check_list(TensorErrorV1* error, const TB200GemvItem* items, int32_t count) {
+  if (!items) return fail(error, TENSOR_ERROR_ARGUMENT, "items is null");
+  if (count < 1 || count > TB200_GEMV_LIST_MAX)
+    return fail(error, TENSOR_ERROR_ARGUMENT, "a list holds 1..%d projections, got %d", TB200_GEMV_LIST_MAX, count);
+  for (int i = 0; i < count; ++i) {
+    const TB200GemvItem& it = items[i];
+    if (int32_t s = check_gemv_scalars(error, it.format, it.x_dtype, it.m, it.n, it.k, TB200_VARIANT_AUTO)) return s;
+    if (it.m < 1 || it.n < 1) return fail(error, TENSOR_ERROR_ARGUMENT, "item %d: empty projection", i);
+    if (it.out_count < 1 || it.out_count > TB200_MAX_PEERS)
+      return fail(error, TENSOR_ERROR_ARGUMENT, "item %d: out_count %d is not in 1..%d", i, it.out_count, TB200_MAX_PEERS);
+    if (it.out_ld < it.n) return fail(error, TENSOR_ERROR_ARGUMENT, "item %d: out_ld %lld < n %lld", i, (long long)it.out_ld, (long long)it.n);
+  }
+  return TENSOR_OK;
+}
+void to_launch_items(const TB200GemvItem* items, int count, TcLaunchItem* out) {
+  for (int i = 0; i < count; ++i) {
+    const TB200GemvItem& it = items[i];
+    TcLaunchItem& o = out[i];
+    o = TcLaunchItem{};
+    o.fmt = it.format;
+    o.xt = it.x_dtype;
+    o.x = it.x;
+    o.w = static_cast<const uint8_t*>(it.w);
+    o.m = it.m;
+    o.n = it.n;
+    o.k = it.k;
+    o.out.count = it.out_count;
+    o.out.ld = it.out_ld;
+    for (int d = 0; d < it.out_count && d < kMaxOutputs; ++d) o.out.ptr[d] = it.outs[d];
+    o.x_share = -1;
+    for (int j = 0; j < i; ++j)
+      if (items[j].x == it.x && items[j].m == it.m && items[j].k == it.k && items[j].x_dtype == it.x_dtype) {
+        o.x_share = out[j].x_share >= 0 ? out[j].x_share : j;
+        break;
+      }
+  }
+}
+}  // namespace
+
+int64_t tb200_gguf_gemv_list_scratch_bytes(const TB200GemvItem* items, int32_t count) {
+  if (!items || count < 1 || count > TB200_GEMV_LIST_MAX) return 0;
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return 0;
+  TcLaunchItem list[kTcMaxItems];
+  to_launch_items(items, count, list);
+  long long need = gemv_tc_scratch_bytes(list, count, *dev);
+  // launched one by one (or two by two) the projections share the scratch: the largest need counts
+  for (int i = 0; i < count; ++i) {
+    long long single = tb200_gguf_gemv_scratch_bytes(items[i].format, items[i].m, items[i].n, items[i].k);
+    if (i + 1 < count && list[i + 1].x_share == i && items[i + 1].format == items[i].format) {
+      const long long both = tb200_gguf_gemv_scratch_bytes(items[i].format, items[i].m, items[i].n + items[i + 1].n, items[i].k);
+      if (both > single) single = both;
+    }
+    if (single > need) need = single;
+  }
+  return need;
+}
+
+int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* scratch, int64_t scratch_bytes,
+                             int32_t variant, uint32_t* const* pads, int32_t rank, int32_t world, int32_t sync,
+                             void* stream, TensorErrorV1* error) {
+  static_assert(TB200_GEMV_LIST_MAX == kTcMaxItems, "list length");
+  if (int32_t s = check_list(error, items, count)) return s;
+  if (variant < 0 || variant > TB200_VARIANT_TC) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (int32_t s = check_pointer(error, "scratch", scratch, 256, false)) return s;
+  if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
+  if (sync & ~(TB200_PEER_WAIT | TB200_PEER_SIGNAL)) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown sync bits 0x%x", sync);
+  for (int i = 0; i < count; ++i) {
+    if (int32_t s = check_pointer(error, "x", items[i].x, 16, true)) return s;
+    if (int32_t s = check_pointer(error, "w", items[i].w, 16, true)) return s;
+    for (int d = 0; d < items[i].out_count; ++d)
+      if (int32_t s = check_pointer(error, "out", items[i].outs[d], 4, true)) return s;
+  }
+  PeerSync peers{};
+  if (sync) {
+    if (int32_t s = check_pads(error, pads, rank, world)) return s;
+    for (int i = 0; i < world; ++i) peers.pads[i] = pads[i];
+    peers.rank = rank;
+    peers.world = world;
+    peers.flags = world > 1 ? sync : 0;
+  }
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  TcLaunchItem list[kTcMaxItems];
+  to_launch_items(items, count, list);
+  if (variant == TB200_VARIANT_TC) {
+    cudaError_t e;
+    if (!try_list(list, count, scratch, scratch_bytes, *dev, st, peers.flags ? &peers : nullptr, &e))
+      return fail(error, TENSOR_ERROR_ARGUMENT,
+                  "the persistent tensor-memory kernel takes Q4_K lists with 2-byte activations, m <= 16 and %lld "
+                  "bytes of scratch", (long long)gemv_tc_scratch_bytes(list, count, *dev));
+    if (e != cudaSuccess) return cuda_fail(error, "tensor-memory GEMV launch (list)", e);
+    return ok(error);
+  }
+  // Pipelined launches back to back (each overlaps its predecessor's tail); neighbours that share
+  // their activations go out as one grouped launch.  The first launch waits for the peers, the last
+  // one signals them.
+  for (int i = 0; i < count;) {
+    const bool pair = i + 1 < count && list[i + 1].x_share == i && items[i + 1].format == items[i].format &&
+                      items[i + 1].out_count == items[i].out_count && items[i + 1].out_ld == items[i].out_ld &&
+                      variant != TB200_VARIANT_SIMPLE;
+    const int step = pair ? 2 : 1;
+    const int flags = (i == 0 ? peers.flags & kPeerWait : 0) | (i + step >= count ? peers.flags & kPeerSignal : 0);
+    if (pair) {
+      if (int32_t s = tb200_gguf_gemv_pair_sharded_sync(
+              items[i].format, items[i].x_dtype, items[i].x, items[i].w, items[i].n, items[i + 1].w, items[i + 1].n,
+              items[i].outs, items[i + 1].outs, items[i].out_count, items[i].out_ld, 0, 0, items[i].m, items[i].k,
+              scratch, scratch_bytes, variant, pads, rank, world > 0 ? world : 1, flags, stream, error))
+        return s;
+    } else {
+      PeerSync each = peers;
+      each.flags = flags;
+      if (int32_t s = gemv_common(items[i].format, items[i].x_dtype, items[i].x, items[i].w, list[i].out, items[i].m,
+                                  items[i].n, items[i].k, scratch, scratch_bytes, variant, stream, error,
+                                  each.flags ? &each : nullptr))
+        return s;
+    }
+    i += step;
+  }
+  return ok(error);
+}
+
+int32_t tb200_peer_set_wait_limit(uint64_t nanoseconds) {
+  set_peer_wait_limit_ns(nanoseconds);
+  return TENSOR_OK;
 }
 
 // ---- descriptor forms ----------------------------------------------------------------------------

@@ -442,7 +442,7 @@ cudaError_t launch_shape(const CUtensorMap& tmap, const uint8_t* w, float* out, 
                          long long k, cudaStream_t stream) {
   using C = Cfg<TT, G>;
   auto kernel = gemm_tcgen05_kernel<FMT, TT, G>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  cudaError_t e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)((m + C::kTileTok - 1) / C::kTileTok), (unsigned)((n + kTileN - 1) / kTileN));
   kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, w, out, (int)m, (int)n, (int)k, row_bytes(FMT, k));

@@ -50,7 +50,7 @@ constexpr int kThreadsWide = (kMaxConsumerWarps + 2) * 32;
 constexpr int kTilesBeforeWait = 1;
 constexpr int kTileRows = 16;
 constexpr int kMaxStages = 8;
-constexpr int kCounterBytes = 4096;  // one arrival counter per group of CTAs that share row tiles (<= 1024)
+constexpr int kCounterBytes = kGemvCounterBytes;  // one arrival counter per group of CTAs that share row tiles (<= 1024)
 constexpr int kSclRowFloats = 18;  // 8 x (scale, offset) pairs + 2 floats of padding (bank spread)
 
 struct GemvArgs {
@@ -71,6 +71,7 @@ struct GemvArgs {
   // rank has; bit 1: signal every peer once all CTAs of this launch have stored their outputs.
   unsigned int* pads[kMaxOutputs];
   int rank, world, sync;
+  unsigned long long wait_limit_ns;
   // batch plans: activations converted ahead of this launch (see gemv_prepare_kernel); null = convert here
   const uint16_t* x16;
   const float* x_table;    // [K / 32][NTB] group sums
@@ -716,7 +717,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvArgs& a, const CUtensorM
         unsigned int seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + lane) : "memory");
         if ((int)(seen - expected) >= 0) break;
-        if (ptx::global_timer_ns() - t0 > ptx::kWaitLimitNs) {
+        if (ptx::global_timer_ns() - t0 > a.wait_limit_ns) {
           report_timeout(0x80000u | (unsigned)lane);
           break;
         }
@@ -1299,7 +1300,7 @@ static bool overlap_launches() {
 template <int FMT, bool F16, int NT, bool GROUPS, bool WIDE>
 static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t stream) {
   auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS, WIDE>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
   alignas(64) CUtensorMap wmap;
   memset(&wmap, 0, sizeof(wmap));
@@ -1359,6 +1360,7 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     a.world = peers->world;
     a.sync = peers->flags;
   }
+  a.wait_limit_ns = peer_wait_limit_ns();
   const int smem_total = fill_args(a, plan, fmt, m, n, k);
   a.x = x;
   a.w = w;

@@ -236,12 +236,14 @@ template <int FMT, typename XT, int MB>
 static cudaError_t launch_rows(const XT* x, const uint8_t* w, const OutSpec& out, long long m, long long n, long long k,
                                int smem, cudaStream_t stream) {
   auto kernel = gemv_rows_kernel<FMT, XT, MB>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return e;
   // persistent-ish: a few CTAs per SM, every warp walking its rows with the next one in flight
   const long long row_ctas = (n + kRowWarps - 1) / kRowWarps;
-  const int per_sm = 232448 / (smem + 1024) < 1 ? 1 : 232448 / (smem + 1024);  // what shared memory allows
-  const long long resident = 148LL * (per_sm > 4 ? 4 : per_sm);
+  const int per_sm = dev->max_smem_optin / (smem + 1024) < 1 ? 1 : dev->max_smem_optin / (smem + 1024);  // what shared memory allows
+  const long long resident = (long long)dev->sm_count * (per_sm > 4 ? 4 : per_sm);
   const unsigned gx = (unsigned)(row_ctas < resident ? row_ctas : resident);
   const unsigned gy = (unsigned)((m + MB - 1) / MB);
   kernel<<<dim3(gx, gy), kRowWarps * 32, smem, stream>>>(x, w, out, (int)m, n, (int)k, (int)row_bytes(FMT, k));
@@ -256,10 +258,7 @@ static cudaError_t launch_typed(const void* x, const uint8_t* w, const OutSpec& 
   const long long rb = row_bytes(FMT, k);
   // (measured against the kernel below at 4096 x 4096: Q8_0 4x faster at batch 1, 2.5x at batch 2,
   // 1.4x at batch 3-4; from batch 5 on, where the weights are decoded once per four rows, it loses)
-  static const int rows_max_m = [] {  // TB200_ROWS_MAX_M: largest batch the staged kernel takes (tuning)
-    const char* v = getenv("TB200_ROWS_MAX_M");
-    return v ? atoi(v) : 4;
-  }();
+  constexpr int rows_max_m = 4;
   if (!weights_bf16 && m <= rows_max_m && m <= 16 && rb % 16 == 0) {
     const int mb = m == 1 ? 1 : (m == 2 ? 2 : 4);
     const long long smem = (long long)mb * k * 4 + 2 * kRowWarps * rb;  // activations + two row buffers per warp

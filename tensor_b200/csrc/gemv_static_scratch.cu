@@ -27,7 +27,7 @@
 namespace {
 
 constexpr size_t kStaticScratchBytes = TB200_GEMV_STATIC_SCRATCH_BYTES;  // 4 MiB: Q4_K 3584 x 18944 at batch 16 needs 1.6 MB
-constexpr size_t kCounterRegionBytes = 4096;      // the part of the scratch that must start at zero
+constexpr size_t kCounterRegionBytes = tb200::kGemvCounterBytes;  // the part of the scratch that must start at zero
 
 // In host code this name is only a handle for the runtime, never a device address.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];

@@ -1,0 +1,953 @@
+// Decode GEMV for batch 1..16 on the 5th-generation tensor cores of sm_100a, as ONE persistent launch
+// over a list of projections: out_i[m_i, n_i] = x_i[m_i, k_i] . dequant(w_i[n_i, k_i])^T.
+//
+// Replaces the reference's `gemv_packed` (benchmarks/kernels/showcase/kernels.py:116-119) with its
+// fp32-weight x fp32-activation contract (benchmarks/kernels/showcase/benchmark.py:468-470); a list
+// is what a decoder layer launches back to back (q/k/v, gate/up, ...): the reference launches them
+// one kernel each.
+//
+// Regime: HBM-bound, so the whole design serves one goal: keep weight bytes streaming.
+//
+//  * Work unit = 128 weight rows x one 256-weight column of blocks.  The units of all projections
+//    of the list form one sequence that is cut into equal contiguous ranges, one per CTA (one CTA
+//    per SM).  A CTA streams its units through a shared-memory ring (one 2-D TMA copy of the raw
+//    blocks + one bulk copy of the matching activation tile per unit), so ring fill, barrier set-up
+//    and tail are paid once per list, not once per projection.  Where a range ends inside a row
+//    tile the partial sums go to scratch and the last CTA to arrive adds them in K order
+//    (deterministic).
+//  * 16 decode warps: thread (row r, quarter p) reads its 64 weights of the unit from the ring,
+//    turns nibble pairs into the fp16 numbers 1024 + q (or 1024 + 16 q for a high nibble) with one
+//    logic op per pair -- exact -- and stores them straight into tensor memory as the A operand
+//    (tcgen05.st).  No decoded weight ever touches shared memory.
+//  * One thread issues tcgen05.mma (M = 128 rows, N = 16 activation rows, K = 16) with A from tensor
+//    memory and the fp16 activations from the ring.  Each 32-weight scale group accumulates into
+//    its own block of accumulator columns; the block scales are applied to those 32-weight sums in
+//    fp32 by the decode threads when they drain the accumulators (tcgen05.ld):
+//        sum_k (d*sc*q - dmin*mn) x = d*sc*(S - 1024*Sx) - dmin*mn*Sx,   S = sum (1024 + q) x.
+//    The two Sx terms are themselves contractions over the 8 groups, done by two more MMAs against
+//    a tile of group sums (each split into an fp16 high and low part).
+//  * Activations are converted once per list by a small kernel ahead of this one: fp16 after one
+//    power-of-two scale per activation row (largest magnitude -> [2^9, 2^10), so bf16 -> fp16 is exact
+//    for every value within 2^-26 of the row's largest), laid out as the K-major core matrices the
+//    MMA reads, k permuted the way the decode threads emit weights.
+//  * Every wait is bounded and sets a status word; tensor memory is released on every path.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <type_traits>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kRows = 128;                    // weight rows per tile = TMEM lanes
+constexpr int kParts = 4;                     // threads per row; each owns a quarter of a unit
+constexpr int kDecodeWarps = 4 * kParts;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kProducerWarp = kDecodeWarps, kMmaWarp = kDecodeWarps + 1;
+constexpr int kThreads = (kDecodeWarps + 2) * 32;
+constexpr int kUnitK = 256;                   // weights per row and unit
+constexpr int kXMainBytes = 16 * kUnitK * 2;  // activation tile: 16 rows x 256 k, fp16
+constexpr int kXTileBytes = kXMainBytes + 512;  // + fp32 sums of the 8 scale groups of each of the 16 rows
+constexpr int kMaxStagesTc = 8;
+constexpr int kSlotFloats = 16 * kRows;       // one partial-sum slot
+constexpr int kSmemHeader = 1024;
+// tensor memory columns: two A buffers (256 fp16 weights per lane each) and two accumulator sets
+// (8 scale groups x 16 activation rows each)
+constexpr uint32_t kColA = 0, kColD = 256, kBufCols = 128, kTmemCols = 512;
+// kind::f16 instruction descriptor: fp32 accumulate, fp16 x fp16, both K-major, M = 128, N = 16
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+
+struct TcItem {
+  const uint8_t* xprep;      // converted activations: one kXTileBytes tile per 256-weight column
+  const float* unscale;      // [16] factor that undoes the activation scaling of each row
+  float* outs[kMaxOutputs];  // destinations (own output first, then peer-mapped ones)
+  long long n, out_ld;
+  int n_out, m, nb;          // nb: m rounded up to 1, 2, 4, 8 or 16
+  int nsb, row_tiles;
+  int unit_base, tile_base;  // first unit / first row tile of this projection in the list
+};
+
+struct alignas(64) TcParams {
+  CUtensorMap wmap[kTcMaxItems];  // weights as [n rows] x [row bytes / 8] 8-byte words, box = one unit
+  TcItem item[kTcMaxItems];
+  int n_items, total_units, stages, stage_bytes, red_floats;
+  float* partials;
+  unsigned int* counters;
+  unsigned int* pads[kMaxOutputs];
+  int rank, world, sync;
+  unsigned long long wait_limit_ns;
+#ifdef TB200_TC_TRACE
+  long long* trace;  // diagnostic timeline of CTA 0 (trace builds only): 8 stamps per unit
+  int debug;         // experiment switches (trace builds only)
+#endif
+};
+#ifdef TB200_TC_TRACE
+#define TC_STAMP(cond, idx, slot) do { if (p.trace && blockIdx.x == 0 && (cond) && (idx) < 64) p.trace[(idx) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TC_STAMP(cond, idx, slot) do { } while (0)
+#endif
+#ifdef TB200_TC_TRACE
+#define TC_DEBUG(bit) (p.debug & (bit))
+#else
+#define TC_DEBUG(bit) 0
+#endif
+
+struct Cursor {
+  int item, tile, sb;
+};
+__device__ __forceinline__ Cursor locate(const TcParams& p, int unit) {
+  Cursor c;
+  c.item = 0;
+  while (c.item + 1 < p.n_items && unit >= p.item[c.item + 1].unit_base) ++c.item;
+  const int rem = unit - p.item[c.item].unit_base;
+  c.tile = rem / p.item[c.item].nsb;
+  c.sb = rem - c.tile * p.item[c.item].nsb;
+  return c;
+}
+__device__ __forceinline__ void advance(const TcParams& p, Cursor& c) {
+  if (++c.sb == p.item[c.item].nsb) {
+    c.sb = 0;
+    if (++c.tile == p.item[c.item].row_tiles) {
+      c.tile = 0;
+      ++c.item;
+    }
+  }
+}
+
+// One probe of an mbarrier phase without a suspend-time hint (the waits of this kernel sit on its
+// critical path: a waiting warp should see the completing arrival at once).
+__device__ __forceinline__ bool try_wait_now(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(ptx::smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait that also gives up when another warp of the CTA has given up.  The clock is only
+// consulted after a few thousand failed probes: a wait of this kernel normally ends within a
+// microsecond, and reading the global timer costs about as much as such a wait.
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort, unsigned code) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (try_wait_now(bar, parity)) return true;
+  const uint64_t start = ptx::global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (try_wait_now(bar, parity)) return true;
+    if (*abort) return false;
+    if (ptx::global_timer_ns() - start > ptx::kWaitLimitNs) {
+      *abort = 1;
+      report_timeout(code);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  // no swizzle, K-major: core matrices of 8 rows x 16 bytes; the two core matrices of a k-step are
+  // 256 bytes apart (16 rows x 16 bytes), 8-row groups 128 bytes apart
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(256 >> 4) << 16;
+  d |= (uint64_t)(128 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  if constexpr (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[N]) {
+  if constexpr (N == 1) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v[0]) : "r"(taddr) : "memory");
+  } else if constexpr (N == 2) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(v[0]), "=r"(v[1]) : "r"(taddr) : "memory");
+  } else if constexpr (N == 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr)
+                 : "memory");
+  } else if constexpr (N == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+  } else {
+    static_assert(N == 16, "accumulator blocks are 1, 2, 4, 8 or 16 columns");
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+  }
+}
+
+// N consecutive floats of shared memory that every lane of the warp reads alike (a broadcast)
+template <int N>
+__device__ __forceinline__ void lds_floats(uint32_t addr, float (&v)[N]) {
+  if constexpr (N == 1) {
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(addr));
+  } else if constexpr (N == 2) {
+    const float2 t = ptx::lds64f(addr);
+    v[0] = t.x;
+    v[1] = t.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const uint4 t = ptx::lds128(addr + 16 * i);
+      v[4 * i] = __uint_as_float(t.x);
+      v[4 * i + 1] = __uint_as_float(t.y);
+      v[4 * i + 2] = __uint_as_float(t.z);
+      v[4 * i + 3] = __uint_as_float(t.w);
+    }
+  }
+}
+
+// (a & mask) | bits in one logic op, constants in registers (with immediates the compiler emits two)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t bits) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(bits));
+  return d;
+}
+
+// What a decode thread keeps of a unit: the scales of its two groups.  With S_g = sum (1024 + f q) x
+// (f = 1 for the even group, 16 for the odd one) and Sx_g = sum x over the group,
+//   sum_k (d sc q - dmin mn) x = s_g S_g - e_g Sx_g,   s_g = d sc_g / f,   e_g = 1024 s_g + dmin mn_g.
+struct UnitScales {
+  float s_lo, s_hi, e_lo, e_hi;
+};
+
+// ---- Q4_K: 144-byte blocks; quarter p = quant bytes 32p .. 32p+31 = groups 2p (low nibbles) and
+// 2p+1 (high nibbles).  Word w of the quarter gives cells 2w = bytes (4w, 4w+2) and 2w+1 = bytes
+// (4w+1, 4w+3): position 4w + 2e + h of a group holds byte 4w + e + 2h, and the activation tiles
+// are written in the same order. ------------------------------------------------------------------
+template <int FMT> struct TcFormat;
+template <> struct TcFormat<kQ4_K> {
+  static constexpr int kBoxBytes = 144;    // bytes of a row inside a unit's ring stage
+  static constexpr int kBoxStep = 144;     // bytes between consecutive units of a row
+  __device__ static __forceinline__ void decode(uint32_t wrow, int part, uint32_t tmem_a, UnitScales& out) {
+    const uint4 hdr = ptx::lds128(wrow);
+    const uint4 q0 = ptx::lds128(wrow + 16 + 32 * part), q1 = ptx::lds128(wrow + 32 + 32 * part);
+    const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    uint32_t mlo, mhi, bits;
+    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mlo));
+    asm volatile("mov.b32 %0, 0x00F000F0;" : "=r"(mhi));
+    asm volatile("mov.b32 %0, 0x64006400;" : "=r"(bits));
+    uint32_t lo[16], hi[16];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t v = words[w], v8 = v >> 8;
+      lo[2 * w] = and_or(v, mlo, bits);
+      hi[2 * w] = and_or(v, mhi, bits);
+      lo[2 * w + 1] = and_or(v8, mlo, bits);
+      hi[2 * w + 1] = and_or(v8, mhi, bits);
+    }
+    tmem_st16(tmem_a + 32 * part, lo);
+    tmem_st16(tmem_a + 32 * part + 16, hi);
+    // 6-bit scales / mins of groups 2p, 2p+1 (bytes 4..15 of the block: hdr.y, hdr.z, hdr.w)
+    uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+    if (part < 2) {
+      const int sh = 16 * part;
+      sc_lo = (hdr.y >> sh) & 63u;
+      sc_hi = (hdr.y >> (sh + 8)) & 63u;
+      mn_lo = (hdr.z >> sh) & 63u;
+      mn_hi = (hdr.z >> (sh + 8)) & 63u;
+    } else {
+      const int sh = 16 * (part - 2);
+      sc_lo = ((hdr.w >> sh) & 15u) | (((hdr.y >> (sh + 6)) & 3u) << 4);
+      sc_hi = ((hdr.w >> (sh + 8)) & 15u) | (((hdr.y >> (sh + 14)) & 3u) << 4);
+      mn_lo = ((hdr.w >> (sh + 4)) & 15u) | (((hdr.z >> (sh + 6)) & 3u) << 4);
+      mn_hi = ((hdr.w >> (sh + 12)) & 15u) | (((hdr.z >> (sh + 14)) & 3u) << 4);
+    }
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // d, dmin
+    out.s_lo = dd.x * (float)sc_lo;
+    out.s_hi = dd.x * (float)sc_hi * 0.0625f;  // the odd group's MMAs sum 1024 + 16 q
+    out.e_lo = fmaf(1024.f, out.s_lo, dd.y * (float)mn_lo);
+    out.e_hi = fmaf(1024.f, out.s_hi, dd.y * (float)mn_hi);
+  }
+};
+
+// accumulators of one unit -> this thread's running sums (its two groups, NB activation rows)
+template <int NB>
+__device__ __forceinline__ void drain(uint32_t tmem_d, int part, const UnitScales& sc, float (&acc)[16]) {
+  uint32_t lo[NB], hi[NB];
+  tmem_ld<NB>(tmem_d + 32 * part, lo);
+  tmem_ld<NB>(tmem_d + 32 * part + 16, hi);
+  ptx::tmem_ld_wait();
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    acc[b] = fmaf(sc.s_lo, __uint_as_float(lo[b]), acc[b]);
+    acc[b] = fmaf(sc.s_hi, __uint_as_float(hi[b]), acc[b]);
+  }
+}
+// the e_g Sx_g terms of a unit, from the group sums that travel with its activation tile
+template <int NB>
+__device__ __forceinline__ void correct(uint32_t sums, int part, const UnitScales& sc, float (&acc)[16]) {
+  float sx_lo[NB], sx_hi[NB];
+  lds_floats<NB>(sums + (2 * part) * 64, sx_lo);
+  lds_floats<NB>(sums + (2 * part + 1) * 64, sx_hi);
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    acc[b] = fmaf(-sc.e_lo, sx_lo[b], acc[b]);
+    acc[b] = fmaf(-sc.e_hi, sx_hi[b], acc[b]);
+  }
+}
+
+// State the decode warps share when they meet among themselves.
+struct DecodeSync {
+  uint64_t* cbar;
+  volatile int* abort;
+  volatile int* s_last;
+  uint32_t phase;
+  __device__ __forceinline__ bool sync() {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) ptx::mbar_arrive(cbar);
+    const bool ok = wait_bar(cbar, phase & 1, abort, 0x50000u);
+    ++phase;
+    return ok;
+  }
+};
+
+// A segment = the units of one row tile that this CTA owns (columns sb0 .. at.sb).  The decode
+// threads have put their sums into `red` ([quarter][activation row][weight row]).  All of K: add the
+// four quarters and store.  Part of K: the sum goes to this CTA's scratch slot and the last CTA of the
+// tile to arrive adds the slots in K order (deterministic).
+__device__ __noinline__ bool finish_segment(const TcParams& p, const Cursor at, int sb0, int u0, const float* red,
+                                            DecodeSync& ds) {
+  const TcItem& it = p.item[at.item];
+  const int nb = it.nb, tid = threadIdx.x;
+  if (!ds.sync()) return false;
+  const bool whole = sb0 == 0 && at.sb == it.nsb - 1;
+  const long long tile_unit0 = (long long)it.unit_base + (long long)at.tile * it.nsb;
+  const bool from_range_start = tile_unit0 + sb0 == u0;
+  float* slot = p.partials + ((size_t)2 * blockIdx.x + (from_range_start ? 0 : 1)) * kSlotFloats;
+  for (int i = tid; i < nb * kRows; i += kDecodeThreads) {
+    const int b = i >> 7, r = i & (kRows - 1);
+    float v = red[b * kRows + r];
+#pragma unroll
+    for (int q = 1; q < kParts; ++q) v += red[(q * nb + b) * kRows + r];
+    if (whole) {
+      const long long grow = (long long)at.tile * kRows + r;
+      if (b < it.m && grow < it.n) {
+        v *= __ldg(it.unscale + b);
+        for (int d = 0; d < it.n_out; ++d) it.outs[d][(long long)b * it.out_ld + grow] = v;
+      }
+    } else {
+      slot[i] = v;
+    }
+  }
+  if (!whole) {
+    __threadfence();
+    if (!ds.sync()) return false;
+    // CTAs that own a part of this tile: those whose ranges meet [tile_unit0, tile_unit0 + nsb)
+    const long long G = gridDim.x, U = p.total_units;
+    const int c_first = (int)(((tile_unit0 + 1) * G - 1) / U);
+    const int c_last = (int)(((tile_unit0 + it.nsb) * G - 1) / U);
+    if (tid == 0) {
+      unsigned int* counter = p.counters + it.tile_base + at.tile;
+      const unsigned int old = atomicAdd(counter, 1u);
+      const bool last = old == (unsigned)(c_last - c_first);
+      if (last) *counter = 0u;  // everybody else has arrived: ready for the next launch
+      *ds.s_last = last ? 1 : 0;
+    }
+    if (!ds.sync()) return false;
+    if (*ds.s_last) {
+      __threadfence();
+      for (int i = tid; i < nb * kRows; i += kDecodeThreads) {
+        const int b = i >> 7, r = i & (kRows - 1);
+        const long long grow = (long long)at.tile * kRows + r;
+        if (b >= it.m || grow >= it.n) continue;
+        float v = 0.f;
+        for (int c = c_first; c <= c_last; ++c) {
+          const long long range0 = (long long)c * U / G;
+          const float* theirs = p.partials + ((size_t)2 * c + (range0 < tile_unit0 ? 1 : 0)) * kSlotFloats;
+          v += __ldcg(theirs + i);
+        }
+        v *= __ldg(it.unscale + b);
+        for (int d = 0; d < it.n_out; ++d) it.outs[d][(long long)b * it.out_ld + grow] = v;
+      }
+    }
+  }
+  return ds.sync();  // the staging buffer may be overwritten by the next segment
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
+  using F = TcFormat<FMT>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kMaxStagesTc;     // the MMAs of a unit have completed and the decode warps are done with its stage
+  uint64_t* a_ready = empty + kMaxStagesTc;  // [2] decode warps -> MMA: an A buffer is complete
+  uint64_t* d_ready = a_ready + 2;           // [2] MMA -> decode warps: a unit's accumulators are final
+  uint64_t* d_free = d_ready + 2;            // [2] decode warps -> MMA: the accumulators have been read
+  uint64_t* cbar = d_free + 2;               // decode warps among themselves
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
+  volatile int* abort = reinterpret_cast<volatile int*>(smem + 516);
+  volatile int* s_last = reinterpret_cast<volatile int*>(smem + 520);
+  const uint32_t stage0 = ptx::smem_addr(smem) + kSmemHeader;
+  float* red = reinterpret_cast<float*>(smem + kSmemHeader + p.stages * p.stage_bytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  const int u0 = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
+  const int u1 = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
+  const int count = u1 - u0;
+  constexpr int kWTileBytes = kRows * F::kBoxBytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], 1 + kDecodeWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&a_ready[b], kDecodeWarps);
+      ptx::mbar_init(&d_ready[b], 1);
+      ptx::mbar_init(&d_free[b], kDecodeWarps);
+    }
+    ptx::mbar_init(cbar, kDecodeWarps);
+    *abort = 0;
+    *s_last = 0;
+    ptx::fence_mbar_init();
+    // the next kernel on the stream (the conversion of the next list's activations) may start early
+    ptx::grid_launch_dependents();
+  }
+  if (warp == kMmaWarp) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == kProducerWarp) {
+    // ---------------- producer: one TMA box of raw blocks + one activation tile per unit ----------------
+    if (lane == 0 && count > 0) {
+      for (int i = 0; i < p.n_items; ++i) ptx::prefetch_tensormap(&p.wmap[i]);
+      const Cursor first = locate(p, u0);
+      // Weights never depend on the kernel before this one, activations do: fill the ring with
+      // weights, then wait for that kernel, then fetch the activation tiles of those stages.
+      const int pre = count < S ? count : S;
+      Cursor c = first;
+      for (int i = 0; i < pre; ++i) {
+        ptx::mbar_arrive_expect_tx(&full[i], (uint32_t)(kWTileBytes + kXTileBytes));
+        ptx::tma_load_2d(smem + kSmemHeader + i * p.stage_bytes, &p.wmap[c.item], c.sb * (F::kBoxStep / 8),
+                         c.tile * kRows, &full[i]);
+        advance(p, c);
+      }
+      ptx::grid_dependency_wait();
+      if (p.sync & kPeerWait) {
+        // until every peer has signalled as often as this rank has (their stores into buffers this
+        // list reads have landed); bounded
+        const unsigned int* mine = p.pads[p.rank];
+        const unsigned int expected = *reinterpret_cast<const volatile unsigned int*>(mine + 32);
+        const unsigned long long t0 = ptx::global_timer_ns();
+        for (int peer = 0; peer < p.world; ++peer) {
+          if (peer == p.rank) continue;
+          for (;;) {
+            unsigned int seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + peer) : "memory");
+            if ((int)(seen - expected) >= 0) break;
+            if (ptx::global_timer_ns() - t0 > p.wait_limit_ns) {
+              report_timeout(0x80000u | (unsigned)peer);
+              break;
+            }
+            __nanosleep(100);
+          }
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
+      Cursor c2 = first;
+      for (int i = 0; i < pre; ++i) {
+        ptx::bulk_g2s(smem + kSmemHeader + i * p.stage_bytes + kWTileBytes,
+                      p.item[c2.item].xprep + (size_t)c2.sb * kXTileBytes, kXTileBytes, &full[i]);
+        advance(p, c2);
+      }
+      for (int idx = pre; idx < count; ++idx) {
+        const int s = idx % S;
+        if (!wait_bar(&empty[s], ((idx / S) - 1) & 1, abort, 0x10000u | (unsigned)s)) break;
+        TC_STAMP(true, idx, 0);
+        uint8_t* dst = smem + kSmemHeader + s * p.stage_bytes;
+        ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)(kWTileBytes + kXTileBytes));
+        ptx::tma_load_2d(dst, &p.wmap[c.item], c.sb * (F::kBoxStep / 8), c.tile * kRows, &full[s]);
+        ptx::bulk_g2s(dst + kWTileBytes, p.item[c.item].xprep + (size_t)c.sb * kXTileBytes, kXTileBytes, &full[s]);
+        advance(p, c);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t idesc;
+      asm volatile("mov.b32 %0, %1;" : "=r"(idesc) : "n"(kIdesc));
+      for (int idx = 0; idx < count; ++idx) {
+        const int s = idx % S, buf = idx & 1, use = idx >> 1;
+        if (!wait_bar(&full[s], (idx / S) & 1, abort, 0x20000u | (unsigned)s)) break;
+        if (!wait_bar(&a_ready[buf], use & 1, abort, 0x30000u)) break;
+        if (use > 0 && !wait_bar(&d_free[buf], (use - 1) & 1, abort, 0x40000u)) break;
+        TC_STAMP(true, idx, 1);
+        ptx::tc_fence_after();
+        const uint32_t a = tmem + kColA + buf * kBufCols;
+        const uint32_t d = tmem + kColD + buf * kBufCols;
+        const uint64_t xdesc = desc_kmajor(stage0 + s * p.stage_bytes + kWTileBytes);
+        if (!TC_DEBUG(1)) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          // two k-steps of 16 per 32-weight group; a k-step's activations are 512 bytes (32 descriptor units)
+          umma_ts<false>(d + 16 * g, a + 16 * g, xdesc + 64 * g, idesc);
+          umma_ts<true>(d + 16 * g, a + 16 * g + 8, xdesc + 64 * g + 32, idesc);
+        }
+        }
+        ptx::umma_commit(&empty[s]);
+        ptx::umma_commit(&d_ready[buf]);
+        TC_STAMP(true, idx, 2);
+      }
+    }
+  } else {
+    // ---------------- decode warps ----------------
+    const int part = warp >> 2, quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int tid = threadIdx.x;  // 0 .. 511
+    ptx::grid_dependency_wait();  // outputs and scratch may still be in use by the kernel before
+    DecodeSync ds{cbar, abort, s_last, 0u};
+    float acc[16];
+#pragma unroll
+    for (int b = 0; b < 16; ++b) acc[b] = 0.f;
+
+    // the accumulators of unit `idx` (its MMAs ran while the unit after it was decoded)
+    auto drain_unit = [&](int nb, int idx, const UnitScales& sc) -> bool {
+      const int buf = idx & 1;
+      if (!wait_bar(&d_ready[buf], (idx >> 1) & 1, abort, 0x60000u)) return false;
+      TC_STAMP(tid == 0, idx, 5);
+      ptx::tc_fence_after();
+      const uint32_t d = tmem + lane_base + kColD + buf * kBufCols;
+      switch (nb) {
+        case 1: drain<1>(d, part, sc, acc); break;
+        case 2: drain<2>(d, part, sc, acc); break;
+        case 4: drain<4>(d, part, sc, acc); break;
+        case 8: drain<8>(d, part, sc, acc); break;
+        default: drain<16>(d, part, sc, acc); break;
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&d_free[buf]);
+      TC_STAMP(tid == 0, idx, 6);
+      return true;
+    };
+    // this thread's sums of the segment that ended -> staging buffer, then the CTA-wide part
+    auto end_segment = [&](const Cursor& at, int sb0) -> bool {
+      const int nb = p.item[at.item].nb;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) {
+        if (b < nb) red[(part * nb + b) * kRows + row] = acc[b];
+        acc[b] = 0.f;
+      }
+      return finish_segment(p, at, sb0, u0, red, ds);
+    };
+
+    Cursor cur = count > 0 ? locate(p, u0) : Cursor{0, 0, 0};
+    Cursor prev = cur;
+    int seg_sb0 = cur.sb;
+    UnitScales sc_prev{};
+    bool ok = true;
+    for (int idx = 0; idx < count && ok; ++idx) {
+      const int s = idx % S;
+      if (!wait_bar(&full[s], (idx / S) & 1, abort, 0x70000u | (unsigned)s)) {
+        ok = false;
+        break;
+      }
+      TC_STAMP(tid == 0, idx, 3);
+      TC_STAMP(lane == 0 && warp == 5, idx, 12);
+      TC_STAMP(lane == 0 && warp == 15, idx, 13);
+      const uint32_t stage = stage0 + s * p.stage_bytes;
+      UnitScales sc_cur{};
+      if (!TC_DEBUG(2)) F::decode(stage + row * F::kBoxBytes, part, tmem + lane_base + kColA + (idx & 1) * kBufCols, sc_cur);
+      tmem_st_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&a_ready[idx & 1]);
+      TC_STAMP(tid == 0, idx, 4);
+      TC_STAMP(lane == 0 && warp == 5, idx, 8);
+      TC_STAMP(lane == 0 && warp == 10, idx, 9);
+      TC_STAMP(lane == 0 && warp == 15, idx, 10);
+      TC_STAMP(lane == 0 && warp == 13, idx, 11);
+      if (idx > 0) {
+        ok = drain_unit(p.item[prev.item].nb, idx - 1, sc_prev);
+        if (ok && (cur.item != prev.item || cur.tile != prev.tile)) {
+          ok = end_segment(prev, seg_sb0);
+          seg_sb0 = cur.sb;
+        }
+      }
+      // the Sx terms of this unit need nothing from the tensor core
+      const uint32_t sums = stage + kWTileBytes + kXMainBytes;
+      switch (p.item[cur.item].nb) {
+        case 1: correct<1>(sums, part, sc_cur, acc); break;
+        case 2: correct<2>(sums, part, sc_cur, acc); break;
+        case 4: correct<4>(sums, part, sc_cur, acc); break;
+        case 8: correct<8>(sums, part, sc_cur, acc); break;
+        default: correct<16>(sums, part, sc_cur, acc); break;
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty[s]);  // this warp is done with the stage
+      sc_prev = sc_cur;
+      prev = cur;
+      advance(p, cur);
+    }
+    if (ok && count > 0) {
+      ok = drain_unit(p.item[prev.item].nb, count - 1, sc_prev);
+      if (ok) ok = end_segment(prev, seg_sb0);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    if (*abort && lane == 0) {
+      // a wait gave up: let copies that may still be in flight land before the CTA's memory is reused
+      const unsigned long long t = ptx::global_timer_ns();
+      while (ptx::global_timer_ns() - t < 50000ull) {
+      }
+    }
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0 && (p.sync & kPeerSignal)) {
+    // every warp of this CTA has stored what it will store; the last CTA of the grid tells the peers
+    unsigned int* mine = p.pads[p.rank];
+    __threadfence();
+    if (atomicAdd(mine + 34, 1u) == gridDim.x - 1) {
+      __threadfence_system();
+      mine[34] = 0u;
+      const unsigned int epoch = mine[32] + 1u;
+      mine[32] = epoch;
+      for (int peer = 0; peer < p.world; ++peer)
+        if (peer != p.rank)
+          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.pads[peer] + p.rank), "r"(epoch) : "memory");
+    }
+  }
+}
+
+// ---- activation conversion ----------------------------------------------------------------------
+// One CTA per (activation matrix, row b of 16).  Rows below m: find the row's largest magnitude,
+// scale by the power of two that puts it in [2^9, 2^10), convert to fp16 and scatter into the tiles
+// the GEMV copies; rows from m on are written as zeros.  A tile: [32 core columns of 8 k][16 rows][8 k]
+// fp16, then the sums of the converted values over each 32-value scale group as fp32 [8 groups][16 rows].
+struct PrepX {
+  const uint16_t* x;
+  uint8_t* xprep;
+  float* unscale;
+  int m, k;
+};
+struct PrepArgs {
+  PrepX x[kTcMaxItems];
+};
+
+template <int FMT, bool F16>
+__global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) {
+  __shared__ uint32_t s_max[8];
+  const PrepX px = a.x[blockIdx.y];
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  if (tid == 0) ptx::grid_launch_dependents();  // the GEMV behind fills its weight ring meanwhile
+  ptx::grid_dependency_wait();                   // the GEMV before may still read these tiles
+  const int chunks = px.k >> 3;                  // 8 values = 16 bytes; a multiple of 32
+  if (b >= px.m) {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int c = tid; c < chunks; c += 256) {
+      const int j = c >> 5, k8 = c & 31;
+      *reinterpret_cast<uint4*>(px.xprep + (size_t)j * kXTileBytes + k8 * 256 + b * 16) = zero;
+      if (k8 < 8) *reinterpret_cast<float*>(px.xprep + (size_t)j * kXTileBytes + kXMainBytes + k8 * 64 + b * 4) = 0.f;
+    }
+    if (tid == 0) px.unscale[b] = 1.f;
+    return;
+  }
+  const uint16_t* xr = px.x + (size_t)b * px.k;
+  uint32_t mx = 0;
+  for (int c = tid; c < chunks; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + (c << 3));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) s_max[tid >> 5] = mx;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx = max(mx, s_max[i]);
+  // biased exponent of the largest magnitude -> shift that lands it in [2^9, 2^10)
+  const int e = F16 ? (int)(mx >> 10) : (int)(mx >> 7);
+  const int bias = F16 ? 15 : 127, emax = F16 ? 31 : 255;
+  int sh = 0;
+  if (e > 0 && e < emax) sh = bias + 9 - e;
+  sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+  const float scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+  if (tid == 0) px.unscale[b] = __uint_as_float((uint32_t)(127 - sh) << 23);
+
+  for (int c = tid; c < chunks; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + (c << 3));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (F16) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = t.x * scale;
+        f[2 * i + 1] = t.y * scale;
+      } else {
+        f[2 * i] = __uint_as_float(w[i] << 16) * scale;
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * scale;
+      }
+    }
+    __half h[8];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      h[i] = __float2half_rn(f[i]);
+      sum += __half2float(h[i]);
+    }
+    // the four chunks of a 32-value scale group sit in four neighbouring lanes
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    // where the chunk goes: unit j, scale group g, core column k8; order inside each 4-value word
+    // [x0, x2, x1, x3] (see TcFormat<kQ4_K>)
+    const int j = c >> 5, cc = c & 31;         // chunk inside the unit: 8 cc .. 8 cc + 7
+    const int quarter = cc >> 3, nib = (cc >> 2) & 1, i8 = cc & 3;
+    const int g = 2 * quarter + nib;
+    const int k8 = 4 * g + i8;
+    auto pack = [&](int lo, int hi) { return (uint32_t)__half_as_ushort(h[lo]) | ((uint32_t)__half_as_ushort(h[hi]) << 16); };
+    const uint4 o = make_uint4(pack(0, 2), pack(1, 3), pack(4, 6), pack(5, 7));
+    uint8_t* tile = px.xprep + (size_t)j * kXTileBytes;
+    *reinterpret_cast<uint4*>(tile + k8 * 256 + b * 16) = o;
+    if (i8 == 0) *reinterpret_cast<float*>(tile + kXMainBytes + g * 64 + b * 4) = sum;
+  }
+}
+
+inline long long round_up_ll(long long v, long long to) { return (v + to - 1) / to * to; }
+inline int batch_columns(long long m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16; }
+
+unsigned long long g_peer_wait_limit_ns = 2000000000ull;
+
+}  // namespace
+
+TB200_DEFINE_STATUS_READER(read_gemv_tc_status)
+
+void set_peer_wait_limit_ns(unsigned long long ns) { g_peer_wait_limit_ns = ns ? ns : 2000000000ull; }
+unsigned long long peer_wait_limit_ns() { return g_peer_wait_limit_ns; }
+
+bool gemv_tc_supported(int fmt, int xt, long long m, long long n, long long k) {
+  if (fmt != kQ4_K) return false;
+  if (xt != kBF16 && xt != kF16) return false;
+  if (m < 1 || m > 16 || n < 1 || k < kUnitK || k % kUnitK) return false;
+  if (row_bytes(fmt, k) % 16) return false;
+  if (n > (1ll << 30) || k > (1ll << 24)) return false;
+  return true;
+}
+
+// Scratch layout of a list: arrival counters (one per row tile), partial-sum slots (two per CTA),
+// then per distinct activation matrix its tiles and its 16 unscale factors.
+struct TcLayout {
+  long long counters = 0, partials = 0, x_base = 0, total = 0;
+  long long x_offset[kTcMaxItems], unscale_offset[kTcMaxItems];
+  int grid = 0, total_units = 0, total_tiles = 0;
+};
+static bool tc_layout(const TcLaunchItem* items, int count, const DeviceInfo& dev, TcLayout& L) {
+  if (count < 1 || count > kTcMaxItems) return false;
+  long long units = 0, tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    const TcLaunchItem& it = items[i];
+    if (!gemv_tc_supported(it.fmt, it.xt, it.m, it.n, it.k) || it.fmt != items[0].fmt) return false;
+    if (it.x_share >= i) return false;
+    if (it.x_share >= 0 && (items[it.x_share].k != it.k || items[it.x_share].m != it.m || items[it.x_share].xt != it.xt))
+      return false;
+    const long long rt = (it.n + kRows - 1) / kRows;
+    units += rt * (it.k / kUnitK);
+    tiles += rt;
+  }
+  if (units > 0x7fffffffLL) return false;
+  L.total_units = (int)units;
+  L.total_tiles = (int)tiles;
+  L.grid = (int)(units < dev.sm_count ? units : dev.sm_count);
+  L.counters = 0;
+  L.partials = round_up_ll(tiles * 4, 256);
+  long long off = L.partials + (long long)L.grid * 2 * kSlotFloats * 4;
+  for (int i = 0; i < count; ++i) {
+    if (items[i].x_share >= 0) {
+      L.x_offset[i] = L.x_offset[items[i].x_share];
+      L.unscale_offset[i] = L.unscale_offset[items[i].x_share];
+      continue;
+    }
+    L.x_offset[i] = off;
+    off += round_up_ll(items[i].k / kUnitK * (long long)kXTileBytes, 256);
+    L.unscale_offset[i] = off;
+    off += 256;
+  }
+  L.total = off;
+  return true;
+}
+
+long long gemv_tc_scratch_bytes(const TcLaunchItem* items, int count, const DeviceInfo& dev) {
+  TcLayout L;
+  return tc_layout(items, count, dev, L) ? L.total : 0;
+}
+
+cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, long long scratch_bytes,
+                           cudaStream_t stream, const PeerSync* peers) {
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return e;
+  TcLayout L;
+  if (!tc_layout(items, count, *dev, L)) return cudaErrorInvalidValue;
+  if (!scratch || scratch_bytes < L.total || (reinterpret_cast<uintptr_t>(scratch) & 255)) return cudaErrorInvalidValue;
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+
+  // ---- activations -> fp16 tiles (one small kernel for the whole list) ----
+  PrepArgs prep{};
+  int n_x = 0;
+  for (int i = 0; i < count; ++i) {
+    if (items[i].x_share >= 0) continue;
+    PrepX& px = prep.x[n_x++];
+    px.x = static_cast<const uint16_t*>(items[i].x);
+    px.xprep = base + L.x_offset[i];
+    px.unscale = reinterpret_cast<float*>(base + L.unscale_offset[i]);
+    px.m = (int)items[i].m;
+    px.k = (int)items[i].k;
+    if (items[i].xt != items[0].xt) return cudaErrorInvalidValue;
+  }
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(16, (unsigned)n_x);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = items[0].xt == kF16 ? cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ4_K, true>, prep)
+                            : cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ4_K, false>, prep);
+    if (e != cudaSuccess) return e;
+  }
+
+  // ---- the list ----
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  int unit_base = 0, tile_base = 0, max_nb = 1;
+  for (int i = 0; i < count; ++i) {
+    const TcLaunchItem& src = items[i];
+    TcItem& it = p.item[i];
+    it.xprep = base + L.x_offset[i];
+    it.unscale = reinterpret_cast<const float*>(base + L.unscale_offset[i]);
+    if (src.out.count < 1 || src.out.count > kMaxOutputs || src.out.ld < src.n) return cudaErrorInvalidValue;
+    for (int d = 0; d < src.out.count; ++d) it.outs[d] = src.out.ptr[d];
+    it.n_out = src.out.count;
+    it.out_ld = src.out.ld;
+    it.n = src.n;
+    it.m = (int)src.m;
+    it.nb = batch_columns(src.m);
+    max_nb = it.nb > max_nb ? it.nb : max_nb;
+    it.nsb = (int)(src.k / kUnitK);
+    it.row_tiles = (int)((src.n + kRows - 1) / kRows);
+    it.unit_base = unit_base;
+    it.tile_base = tile_base;
+    unit_base += it.row_tiles * it.nsb;
+    tile_base += it.row_tiles;
+    const long long rb = row_bytes(src.fmt, src.k);
+    if (!make_tensor_map_2d(&p.wmap[i], TmaType::kU64, src.w, (unsigned long long)rb / 8, (unsigned long long)src.n,
+                            (unsigned long long)rb, TcFormat<kQ4_K>::kBoxBytes / 8, kRows, false))
+      return cudaErrorNotSupported;
+  }
+  p.n_items = count;
+  p.total_units = L.total_units;
+  p.stage_bytes = kRows * TcFormat<kQ4_K>::kBoxBytes + kXTileBytes;
+  p.red_floats = kParts * max_nb * kRows;
+  const int spare = dev->max_smem_optin - kSmemHeader - p.red_floats * 4;
+  p.stages = spare / p.stage_bytes;
+  if (p.stages > kMaxStagesTc) p.stages = kMaxStagesTc;
+  if (p.stages < 2) return cudaErrorInvalidValue;
+  p.counters = reinterpret_cast<unsigned int*>(base + L.counters);
+  p.partials = reinterpret_cast<float*>(base + L.partials);
+  p.wait_limit_ns = g_peer_wait_limit_ns;
+  if (peers && peers->flags) {
+    if (peers->world < 1 || peers->world > kMaxOutputs || peers->rank < 0 || peers->rank >= peers->world)
+      return cudaErrorInvalidValue;
+    for (int i = 0; i < peers->world; ++i) p.pads[i] = peers->pads[i];
+    p.rank = peers->rank;
+    p.world = peers->world;
+    p.sync = peers->flags;
+  }
+#ifdef TB200_TC_TRACE
+  {
+    static long long* buffer = nullptr;  // device memory: stamps must not wait on a host-memory store
+    if (!buffer) {
+      cudaMalloc((void**)&buffer, 64 * 16 * 8);
+      cudaMemset(buffer, 0, 64 * 16 * 8);
+      atexit([] {
+        static long long host[64 * 16];
+        cudaMemcpy(host, buffer, sizeof(host), cudaMemcpyDeviceToHost);
+        printf("unit: stage free | mma start, issued | warp0 data ready, A stored | acc ready, drained | A stored by warps 5 10 15 13 | data ready warps 5 15\n");
+        const long long t0 = host[3];
+        for (int i = 0; i < 64 && host[i * 16 + 3]; ++i) {
+          const long long* h = host + i * 16;
+          printf("%3d: %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld %7lld %7lld | %7lld %7lld\n", i, h[0] ? h[0] - t0 : 0,
+                 h[1] - t0, h[2] - t0, h[3] - t0, h[4] - t0, h[5] - t0, h[6] - t0, h[8] - t0, h[9] - t0, h[10] - t0, h[11] - t0,
+                 h[12] - t0, h[13] - t0);
+        }
+      });
+    }
+    p.trace = buffer;
+    const char* dbg = getenv("TB200_TC_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
+    if (getenv("TB200_TC_NOTRACE")) p.trace = nullptr;
+  }
+#endif
+  auto kernel = gemv_tc_kernel<kQ4_K>;
+  e = allow_full_shared_memory(kernel);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)L.grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = (size_t)(kSmemHeader + p.stages * p.stage_bytes + p.red_floats * 4);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+}  // namespace tb200

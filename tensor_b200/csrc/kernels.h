@@ -14,6 +14,17 @@ struct DeviceInfo {
 // Properties of the current device (cached per ordinal).  Returns nullptr on a CUDA error.
 const DeviceInfo* device_info(cudaError_t* err);
 
+// Opts a kernel in to the device's whole dynamic shared memory, once per kernel and device.  The
+// attribute belongs to the function, not to a launch: setting it to each launch's own size would
+// let a later, smaller plan shrink it under launches that were captured into a graph earlier (a
+// replay of such a node as a plain launch is then checked against the smaller value and fails).
+// Always the same value, so concurrent callers cannot undo one another.
+cudaError_t allow_full_shared_memory(const void* kernel);
+template <typename Kernel>
+inline cudaError_t allow_full_shared_memory(Kernel* kernel) {
+  return allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
+}
+
 cudaError_t launch_dequant(int fmt, const uint8_t* w, float* out, long long n, long long k,
                            cudaStream_t stream);
 
@@ -87,12 +98,37 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream, const PeerSync* peers = nullptr, const uint8_t* w2 = nullptr,
                              long long n1 = 0);
+// the first bytes of a GEMV scratch buffer: arrival counters that must read zero when a call starts
+constexpr int kGemvCounterBytes = 4096;
 constexpr int kGemvTileRows = 16;  // rows per weight tile of the pipelined GEMV (n1 of a grouped launch is a multiple)
 inline cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                                     float* out, long long m, long long n, long long k, void* scratch,
                                     cudaStream_t stream) {
   return launch_gemv_fast(plan, fmt, xt, x, w, single_output(out, n), m, n, k, scratch, stream);
 }
+
+// Persistent tcgen05 / TMEM GEMV over a list of projections (gemv_tc.cu): one launch (plus one small
+// activation-conversion launch) serves up to kTcMaxItems independent GEMVs of one format, each with its
+// own batch (1..16), shape and destinations.  x_share >= 0 names an earlier item of the list that
+// reads the same activations (gate and up of an MLP): they are converted once.
+constexpr int kTcMaxItems = 12;
+struct TcLaunchItem {
+  int fmt, xt;
+  const void* x;
+  const uint8_t* w;
+  OutSpec out;
+  long long m, n, k;
+  int x_share;
+};
+bool gemv_tc_supported(int fmt, int xt, long long m, long long n, long long k);
+// Scratch a list needs (arrival counters, partial sums of row tiles that span CTAs, converted
+// activations); zero before the first use, 256-byte aligned.
+long long gemv_tc_scratch_bytes(const TcLaunchItem* items, int count, const DeviceInfo& dev);
+cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, long long scratch_bytes,
+                           cudaStream_t stream, const PeerSync* peers = nullptr);
+// How long a kernel waits for a peer GPU's signal before it records a status code and returns.
+void set_peer_wait_limit_ns(unsigned long long ns);
+unsigned long long peer_wait_limit_ns();
 
 // Cross-GPU barrier over peer-mapped signal pads (one pad of kSignalWords uint32 per rank, zeroed
 // once): every rank tells every peer that all work it enqueued before is complete and visible,
@@ -120,6 +156,7 @@ bool make_tensor_map_2d(void* map_out, TmaType type, const void* base, unsigned 
 bool allocation_range(const void* ptr, void** base, size_t* size);
 
 cudaError_t read_gemv_status(unsigned int* value, bool clear);
+cudaError_t read_gemv_tc_status(unsigned int* value, bool clear);
 cudaError_t read_gemm_status(unsigned int* value, bool clear);
 cudaError_t read_barrier_status(unsigned int* value, bool clear);
 

@@ -19,9 +19,10 @@
 // release order it before the flag at the peer, and the acquire load orders the peer's data after
 // the flag for whatever this rank enqueues next.
 //
-// The wait is bounded (two seconds of the global timer): on expiry the kernel records status
-// 0x90000 | peer in the library's sticky status word and returns, so a missing rank surfaces as a
-// host-visible error instead of a hung GPU.  Every rank must run on its own GPU: kernels that
+// The wait is bounded (two seconds of the global timer unless tb200_peer_set_wait_limit chose another
+// limit): on expiry the kernel records status 0x90000 | peer in the library's sticky status word and
+// returns, so a missing rank surfaces as a host-visible error instead of a hung GPU.  A rank that gave
+// up does not signal for that launch either, so its peers' next waits run out in turn.  Every rank must run on its own GPU: kernels that
 // wait on one another must never share a device.
 #include "kernels.h"
 #include "ptx.cuh"
@@ -35,6 +36,7 @@ struct BarrierArgs {
   int rank;
   int world;
   int mode;
+  unsigned long long wait_limit_ns;
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
@@ -63,7 +65,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
     unsigned int seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
     if ((int)(seen - epoch) >= 0) break;
-    if (ptx::global_timer_ns() - t0 > 2000000000ull) {
+    if (ptx::global_timer_ns() - t0 > a.wait_limit_ns) {
       report_timeout(0x90000u | (unsigned)peer);
       break;
     }
@@ -82,6 +84,7 @@ cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, 
   a.rank = rank;
   a.world = world;
   a.mode = mode;
+  a.wait_limit_ns = peer_wait_limit_ns();
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(1);
   cfg.blockDim = dim3(32);

@@ -13,7 +13,8 @@ from ._native import lib, raise_for_status
 from .formats import get_format
 
 _TORCH_DTYPE_IDS = {torch.uint8: 3, torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
-_VARIANTS = {"auto": 0, "simple": 1, "fast": 2, 0: 0, 1: 1, 2: 2}
+_VARIANTS = {"auto": 0, "simple": 1, "fast": 2, "mma": 3, "tc": 4, 0: 0, 1: 1, 2: 2, 3: 3, 4: 4}
+GEMV_LIST_MAX = 12
 
 
 def _require_cuda(name: str, t: torch.Tensor) -> None:
@@ -228,6 +229,93 @@ def peer_sync(pad_ptrs, rank: int, device: torch.device, mode: int = PEER_WAIT |
 def peer_barrier(pad_ptrs, rank: int, device: torch.device, stream=None) -> None:
     """Signal and wait (``tb200_peer_barrier``)."""
     peer_sync(pad_ptrs, rank, device, PEER_WAIT | PEER_SIGNAL, stream)
+
+
+class GemvList:
+    """Several independent decode GEMVs bound once and launched with one C call
+    (``tb200_gguf_gemv_list``): what a decoder layer issues back to back (q/k/v, gate/up), or one
+    projection at several batches.  ``variant="tc"`` runs them as ONE persistent tcgen05 launch.  Each entry is ``(x, w, encoding, n, k, out)`` with ``out`` either
+    an fp32 ``[m, n]`` tensor or ``(device addresses, row length, column offset)`` for an N-sharded
+    rank that stores its columns into every rank's output.  Entries must not depend on one another;
+    entries that pass the same ``x`` tensor share its conversion.  The descriptors are kept, so a
+    launch is one C call; ``rebind(i, w=..., x=...)`` swaps buffers of the same shape."""
+
+    def __init__(self, entries, pad_ptrs=None, rank: int = 0, sync: int = 0, variant="auto"):
+        if not 1 <= len(entries) <= GEMV_LIST_MAX:
+            raise ValueError(f"a list holds 1..{GEMV_LIST_MAX} projections, got {len(entries)}")
+        self._items = (abi.TB200GemvItem * len(entries))()
+        self._keep = []
+        self.device = entries[0][0].device
+        self.outs = []
+        for i, (x, w, encoding, n, k, out) in enumerate(entries):
+            fmt = get_format(encoding)
+            m = _infer_m(x, k)
+            _require_cuda("x", x)
+            _require_cuda("w", w)
+            if w.dtype != torch.uint8 or w.numel() != fmt.weight_bytes(n, k):
+                raise ValueError(f"entry {i}: w must hold the {fmt.weight_bytes(n, k)} raw bytes of [{n}, {k}] in {fmt.name}")
+            try:
+                x_dtype = _X_DTYPE_IDS[x.dtype]
+            except KeyError:
+                raise ValueError(f"entry {i}: unsupported activation dtype {x.dtype}") from None
+            if x.device != self.device or w.device != self.device:
+                raise ValueError("all buffers of a list must live on the same device")
+            item = self._items[i]
+            item.format, item.x_dtype = fmt.type_id, x_dtype
+            item.x, item.w = x.data_ptr(), w.data_ptr()
+            item.m, item.n, item.k = m, n, k
+            if isinstance(out, torch.Tensor):
+                _require_cuda("out", out)
+                if out.dtype != torch.float32 or out.numel() != m * n or out.device != self.device:
+                    raise ValueError(f"entry {i}: out must be float32 with {m * n} elements on {self.device}")
+                item.outs[0] = out.data_ptr()
+                item.out_count, item.out_ld = 1, n
+            else:
+                ptrs, ld, col = out
+                if not 1 <= len(ptrs) <= 8 or ld < col + n:
+                    raise ValueError(f"entry {i}: bad destinations")
+                for d, ptr in enumerate(ptrs):
+                    item.outs[d] = int(ptr) + 4 * col
+                item.out_count, item.out_ld = len(ptrs), ld
+            self._keep.append((x, w, out))
+            self.outs.append(out)
+        with torch.cuda.device(self.device):
+            need = int(lib().tb200_gguf_gemv_list_scratch_bytes(self._items, len(entries)))
+        self.scratch = torch.zeros(max(need, 256), dtype=torch.uint8, device=self.device)
+        self._pads = [int(p) for p in (pad_ptrs or [])]
+        self._pad_table = (ctypes.c_void_p * max(len(self._pads), 1))(*self._pads)
+        self.rank, self.sync = rank, sync if self._pads else 0
+        self.variant = _VARIANTS[variant]
+
+    def rebind(self, index: int, x: torch.Tensor | None = None, w: torch.Tensor | None = None) -> None:
+        """Point entry ``index`` at other activations / weights of the same shape and dtype."""
+        item = self._items[index]
+        old_x, old_w, out = self._keep[index]
+        if x is not None:
+            if x.shape != old_x.shape or x.dtype != old_x.dtype or x.device != self.device:
+                raise ValueError("rebind needs activations of the same shape, dtype and device")
+            item.x = x.data_ptr()
+        if w is not None:
+            if w.numel() != old_w.numel() or w.dtype != torch.uint8 or w.device != self.device:
+                raise ValueError("rebind needs a weight of the same byte size")
+            item.w = w.data_ptr()
+        self._keep[index] = (old_x if x is None else x, old_w if w is None else w, out)
+
+    def launch(self, stream=None) -> None:
+        error = abi.TensorErrorV1()
+        with torch.cuda.device(self.device):
+            status = lib().tb200_gguf_gemv_list(
+                self._items, len(self._items), self.scratch.data_ptr(), self.scratch.numel(), self.variant,
+                self._pad_table if self._pads else None, self.rank, max(len(self._pads), 1), self.sync,
+                _stream_handle(self.device, stream), ctypes.byref(error))
+        raise_for_status(status, error)
+
+    __call__ = launch
+
+
+def set_peer_wait_limit(nanoseconds: int) -> None:
+    """How long kernels wait for another GPU's signal before giving up (0: the default, two seconds)."""
+    lib().tb200_peer_set_wait_limit(int(nanoseconds))
 
 
 def gemv_pair(x: torch.Tensor, w1: torch.Tensor, n1: int, w2: torch.Tensor, n2: int, encoding, k: int,

@@ -1,0 +1,170 @@
+"""GPU paths that the main parity file does not reach: the specialised inner loops of the staged SIMT
+GEMV at the shapes that select them, the first configuration of the benchmark definition at its own
+size, the persistent tcgen05 / TMEM GEMV (an explicit variant), the list entry point, and a
+cross-GPU wait that runs out.  Everything goes through the C ABI and is compared with the CPU oracle
+(relative Frobenius error <= 1e-3, the gate of benchmarks/kernels/showcase/benchmark.py:466-470's
+contract as the benchmark definition states it)."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import tensor_b200 as tb
+from oracle import c_oracle
+from oracle import gguf_oracle as oracle
+from tensor_b200 import abi, ops
+from tensor_b200._native import lib
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+TORCH_X = {"bf16": torch.bfloat16, "f16": torch.float16}
+
+
+def dev():
+    return torch.device("cuda", 0)
+
+
+def to_dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(dev())
+    return t if dtype is None else t.to(dtype)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _no_device_timeouts():
+    yield
+    assert tb.device_status() == 0
+
+
+def _case(name, m, n, k, xdt, variant, seed=0):
+    raw = oracle.make_weights(name, n, k, seed=seed + 3)
+    x = oracle.make_activations(m, k, seed=seed + 4, dtype=xdt)
+    want = c_oracle.gemv(x, raw, name, n, k)
+    out = torch.full((m, n), float("nan"), device=dev())
+    kern = tb.gguf(m, n, k, name, x_dtype={"bf16": "bfloat16", "f16": "float16"}[xdt], op="gemv", variant=variant)
+    kern.launch(to_dev(x, TORCH_X[xdt]), to_dev(raw), out)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    err = oracle.rel_frobenius(got, want)
+    assert err < TOL, err
+    return err
+
+
+# rows whose byte stride is a multiple of 16 and that fit the staged kernel's shared memory: the
+# lane-owns-a-run inner loops for Q6_K, Q8_0 and Q4_0
+@pytest.mark.parametrize("m", [1, 2, 4])
+@pytest.mark.parametrize("k", [2048, 4096])
+def test_staged_simt_gemv_q6k(m, k):
+    _case("q6_k", m, 520, k, "bf16", "auto", seed=m + k)
+
+
+@pytest.mark.parametrize("name", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("m", [1, 3])
+def test_staged_simt_gemv_small_blocks(name, m):
+    _case(name, m, 384, 4096, "bf16", "auto", seed=m)
+
+
+def test_config1_q8_0_4096x4096_fp16():
+    """The benchmark definition's first configuration at its own size."""
+    _case("q8_0", 1, 4096, 4096, "f16", "auto")
+
+
+def test_q6k_down_projection_shape():
+    _case("q6_k", 1, 4096, 12288, "bf16", "auto")
+
+
+# ---- the persistent tcgen05 / TMEM kernel ---------------------------------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (2, 128, 3584), (4, 300, 1024), (8, 1000, 2048), (16, 2048, 3584),
+                                   (3, 18944, 3584), (16, 3584, 18944)])
+def test_tensor_memory_gemv(m, n, k):
+    raw = oracle.make_weights("q4_k", n, k, seed=m + n)
+    x = oracle.make_activations(m, k, seed=m + n + 1, dtype="bf16")
+    want = c_oracle.gemv(x, raw, "q4_k", n, k)
+    xd, wd = to_dev(x, torch.bfloat16), to_dev(raw)
+    lst = ops.GemvList([(xd, wd, "q4_k", n, k, torch.full((m, n), float("nan"), device=dev()))], variant="tc")
+    for _ in range(2):  # the second launch runs on the scratch the first one left behind
+        lst.outs[0].fill_(float("nan"))
+        lst.launch()
+        got = lst.outs[0].cpu().numpy()
+        assert np.isfinite(got).all()
+        err = oracle.rel_frobenius(got, want)
+        assert err < 3e-5, err  # operands are exact; only summation order differs
+
+
+def test_tensor_memory_gemv_f16_activations():
+    m, n, k = 4, 256, 1024
+    raw = oracle.make_weights("q4_k", n, k, seed=9)
+    x = oracle.make_activations(m, k, seed=10, dtype="f16")
+    out = torch.full((m, n), float("nan"), device=dev())
+    ops.GemvList([(to_dev(x, torch.float16), to_dev(raw), "q4_k", n, k, out)], variant="tc").launch()
+    assert oracle.rel_frobenius(out.cpu().numpy(), c_oracle.gemv(x, raw, "q4_k", n, k)) < 3e-5
+
+
+@pytest.mark.parametrize("variant", ["auto", "tc"])
+def test_gemv_list_mixed_batches(variant):
+    """Projections of different shapes and batches in one call; two of them share their activations."""
+    shapes = [(1, 1024, 2048), (1, 640, 2048), (4, 640, 2048), (16, 512, 1024), (1, 384, 4096)]
+    entries, wants = [], []
+    shared = None
+    for i, (m, n, k) in enumerate(shapes):
+        raw = oracle.make_weights("q4_k", n, k, seed=50 + i)
+        if i == 1:
+            x, xd = shared
+        else:
+            x = oracle.make_activations(m, k, seed=60 + i, dtype="bf16")
+            xd = to_dev(x, torch.bfloat16)
+        if i == 0:
+            shared = (x, xd)
+        entries.append((xd, to_dev(raw), "q4_k", n, k, torch.full((m, n), float("nan"), device=dev())))
+        wants.append(c_oracle.gemv(x, raw, "q4_k", n, k))
+    lst = ops.GemvList(entries, variant=variant)
+    for _ in range(2):
+        for e in entries:
+            e[5].fill_(float("nan"))
+        lst.launch()
+        for e, want in zip(entries, wants):
+            got = e[5].cpu().numpy()
+            assert np.isfinite(got).all()
+            assert oracle.rel_frobenius(got, want) < TOL
+
+
+def test_gemv_list_other_formats_fall_back():
+    m, n, k = 2, 96, 512
+    entries, wants = [], []
+    for i, name in enumerate(("q6_k", "q6_k")):
+        raw = oracle.make_weights(name, n, k, seed=70 + i)
+        x = oracle.make_activations(m, k, seed=80 + i, dtype="bf16")
+        entries.append((to_dev(x, torch.bfloat16), to_dev(raw), name, n, k, torch.full((m, n), float("nan"), device=dev())))
+        wants.append(c_oracle.gemv(x, raw, name, n, k))
+    ops.GemvList(entries).launch()
+    for e, want in zip(entries, wants):
+        assert oracle.rel_frobenius(e[5].cpu().numpy(), want) < TOL
+    with pytest.raises(ValueError):
+        ops.GemvList(entries, variant="tc").launch()
+
+
+# ---- a cross-GPU wait that runs out ----------------------------------------------------------------
+
+def test_peer_wait_runs_out_and_reports():
+    """World of two whose second rank never shows up: both pads live on this GPU, nobody signals.
+    The wait must give up after the limit, the status word must name the missing peer, and reading it
+    must clear it.  Nothing faults or hangs: the kernel returns normally."""
+    pads = torch.zeros(2 * 64, dtype=torch.int32, device=dev())
+    table = [pads.data_ptr(), pads.data_ptr() + 256]
+    tb.set_peer_wait_limit(2_000_000)  # 2 ms
+    try:
+        ops.peer_sync(table, 0, dev(), ops.PEER_SIGNAL)  # this rank announces once ...
+        ops.peer_sync(table, 0, dev(), ops.PEER_WAIT)    # ... and waits for a peer that never will
+        word = ctypes.c_uint32(0)
+        error = abi.TensorErrorV1()
+        status = lib().tb200_gguf_device_status(ctypes.byref(word), ctypes.byref(error))
+        assert status == abi.ERROR_PROVIDER
+        assert word.value == 0x90000 | 1
+        assert b"bounded device-side wait" in error.message
+        assert tb.device_status() == 0  # cleared by the read
+    finally:
+        tb.set_peer_wait_limit(0)
+    # the context is still usable
+    assert torch.ones(4, device=dev()).sum().item() == 4

@@ -32,7 +32,7 @@ def _call_static(fmt_id, x, w, out, m, n, k):
     return status, err.message.decode()
 
 
-@pytest.mark.parametrize("m", [1, 4])
+@pytest.mark.parametrize("m", [1, 4, 16])
 def test_static_scratch_matches_regular_entry_point_twice(m):
     from tensor_b200 import synth
 
