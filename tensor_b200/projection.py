@@ -7,8 +7,10 @@ buffers, so a call enqueues kernels and nothing else.
 
 Multi-GPU (one process per GPU): weights are column-sharded along N.  GGUF rows are contiguous byte
 spans, so rank ``r`` of ``g`` simply owns rows ``[r*N/g, (r+1)*N/g)`` -- no block is split and the
-result is bit-identical to the unsharded one.  ``forward`` then all-gathers the fp32 outputs over
-NCCL (NVLink / NVSwitch); activations are replicated.
+result is bit-identical to the unsharded one of the same launch plan.  Activations are replicated;
+every rank ends with the full ``[m, N]`` output, either through the kernels' own stores into every
+rank's peer-mapped output (:class:`FusedGatherGroup`, the decode path) or through an NCCL all-gather
+(:class:`QuantLinear`, :class:`GatherGroup`).
 """
 
 from __future__ import annotations
@@ -162,15 +164,18 @@ class GatherGroup:
             raise ValueError("projections of a group must share the device and the process group")
         if self.world > 1:
             sizes = [l.m * l.n_local for l in self.linears]
-            self._local = torch.empty(sum(sizes), dtype=torch.float32, device=self.device)
-            self._gathered = torch.empty((self.world, sum(sizes)), dtype=torch.float32, device=self.device)
-            offset = 0
+            # every slice starts on a 256-byte boundary (the kernels want 64-byte aligned outputs)
+            starts, total = [], 0
+            for size in sizes:
+                starts.append(total)
+                total += -(-size // 64) * 64
+            self._local = torch.empty(total, dtype=torch.float32, device=self.device)
+            self._gathered = torch.empty((self.world, total), dtype=torch.float32, device=self.device)
             self._spans = []
-            for l, size in zip(self.linears, sizes):
+            for l, size, offset in zip(self.linears, sizes, starts):
                 # the kernel writes straight into its slice of the group buffer
                 l.out_local = self._local[offset:offset + size].view(l.m, l.n_local)
                 self._spans.append((offset, size))
-                offset += size
 
     def forward(self, xs, raws=None):
         """``xs[i]`` is the activation of projection i (``raws[i]`` optionally replaces its weight);
@@ -199,9 +204,15 @@ class FusedGatherGroup:
     kernel's weight prefetch.  With ``fold_sync=False`` one barrier kernel follows the group instead.
 
     Whatever reads the outputs must run after a wait: the next group's first GEMV (folded), or
-    :meth:`wait` for any other consumer.  Outputs are reused from call to call; that is safe because
-    a rank's next write to a peer's buffer comes after it has seen that peer's following signal,
-    which the peer sends after it has consumed the buffer."""
+    :meth:`wait` for any other consumer.
+
+    Every output exists twice and calls alternate between the two copies: a peer signals when its
+    kernel ends, not when the consumer of its result has finished reading, so a rank that is one
+    call ahead must not store into the buffer its peer may still be reading.  With two copies the
+    stores of call t + 2 reuse the buffer of call t, and they start only after this rank has seen the
+    peer's signal of call t + 1, which the peer enqueues after everything it did with call t's
+    result (stream order).  ``forward`` returns the tensors of the copy it wrote; a CUDA graph
+    replays the copy it captured, so capture an even number of calls per replayed sequence."""
 
     def __init__(self, linears, arena, fold_sync: bool = True, shared_input: bool = False):
         """``shared_input``: the first two projections read the same activations (``xs[0]``; gate and
@@ -214,15 +225,19 @@ class FusedGatherGroup:
         self.world, self.rank, self.device = first.world, first.rank, first.device
         if arena.world != self.world or arena.rank != self.rank or arena.device != self.device:
             raise ValueError("the arena belongs to another rank, world or device")
-        self._targets = []
+        self._targets = [[], []]  # per copy, per projection: the output's address on every rank
+        self._outs = [[], []]
         for l in self.linears:
             if l.world != self.world or l.device != self.device:
                 raise ValueError("projections of a group must share the device and the process group")
             if l.kernel.op != "gemv":
                 raise ValueError("the fused gather covers decode GEMVs (m <= 16)")
-            offset = arena.take(l.m * l.n * 4)
-            l.out = arena.view(offset, (l.m, l.n))
-            self._targets.append(arena.ptrs(offset))
+            for copy in range(2):
+                offset = arena.take(l.m * l.n * 4)
+                self._outs[copy].append(arena.view(offset, (l.m, l.n)))
+                self._targets[copy].append(arena.ptrs(offset))
+            l.out = self._outs[0][-1]
+        self._copy = 1  # the first call writes copy 0
         self._pads = arena.pad_ptrs()
         self._pair_scratch = None
         if self.shared_input:
@@ -234,9 +249,16 @@ class FusedGatherGroup:
             if need:
                 self._pair_scratch = torch.zeros(need, dtype=torch.uint8, device=self.device)
 
+    def outputs(self, copy: int):
+        """The ``[m, N]`` tensors of one of the two copies."""
+        return list(self._outs[copy])
+
     def forward(self, xs, raws=None):
+        self._copy ^= 1
+        targets, outs = self._targets[self._copy], self._outs[self._copy]
         last = len(self.linears) - 1
         for i, l in enumerate(self.linears):
+            l.out = outs[i]
             raw = l.raw if raws is None or raws[i] is None else raws[i]
             sync = 0
             if self.fold_sync and self.world > 1:
@@ -248,17 +270,17 @@ class FusedGatherGroup:
                 raw_b = b.raw if raws is None or raws[1] is None else raws[1]
                 if self.fold_sync and self.world > 1 and last == 1:
                     sync |= ops.PEER_SIGNAL
-                ops.gemv_pair_sharded(xs[0], raw, l.n_local, raw_b, b.n_local, l.format, l.k, self._targets[0],
-                                      self._targets[1], l.n, l.rank * l.n_local, b.rank * b.n_local,
+                ops.gemv_pair_sharded(xs[0], raw, l.n_local, raw_b, b.n_local, l.format, l.k, targets[0],
+                                      targets[1], l.n, l.rank * l.n_local, b.rank * b.n_local,
                                       scratch=self._pair_scratch, variant=l.kernel.variant,
                                       pad_ptrs=self._pads if sync else None, rank=self.rank, sync=sync)
                 continue
-            ops.gemv_sharded(xs[i], raw, l.format, l.n_local, l.k, self._targets[i], l.n, l.rank * l.n_local,
+            ops.gemv_sharded(xs[i], raw, l.format, l.n_local, l.k, targets[i], l.n, l.rank * l.n_local,
                              scratch=l.kernel._scratch, variant=l.kernel.variant,
                              pad_ptrs=self._pads if sync else None, rank=self.rank, sync=sync)
         if self.world > 1 and not self.fold_sync:
             ops.peer_barrier(self._pads, self.rank, self.device)
-        return [l.out for l in self.linears]
+        return list(outs)
 
     def wait(self) -> None:
         """Enqueue the wait a consumer other than the next group needs (no-op after a barrier)."""

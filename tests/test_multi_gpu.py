@@ -1,7 +1,10 @@
 """N-sharded projections on two GPUs: every rank owns N/2 rows of each weight, computes its columns
 with the same kernel, and the gather (one NCCL collective per projection, one for a group of
-projections, or the kernels' own peer stores followed by the barrier kernel) must reproduce the
-single-GPU result bit for bit.  Skipped with fewer than two GPUs."""
+projections, or the kernels' own peer stores with the ordering folded into the launches or done by
+the barrier kernel) must reproduce the single-GPU result of the same launch plan bit for bit.  A
+second part calls the fused group many times in a row with no host synchronisation between calls
+while one rank's consumer is slowed down: the two output copies must keep a fast rank from storing
+into a buffer its peer still reads.  Skipped with fewer than two GPUs."""
 
 import os
 import socket
@@ -33,7 +36,7 @@ def _rank_main(rank, world, port, result_path):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     ok = True
-    arena = PeerArena(8 << 20, dev, rank, world)
+    arena = PeerArena(16 << 20, dev, rank, world)
     shapes = [(2048, 3584), (2048, 3584), (1024, 4096)]
     for m in (1, 4):
         fulls = [synth.make_weights("q4_k", n, k, seed=10 + i, device=dev) for i, (n, k) in enumerate(shapes)]
@@ -59,8 +62,9 @@ def _rank_main(rank, world, port, result_path):
         for fold in (False, True):
             fused = FusedGatherGroup(lins, arena, fold_sync=fold)
             for _ in range(2):
-                for lin in lins:
-                    lin.out.fill_(float("nan"))
+                for copy in range(2):
+                    for t in fused.outputs(copy):
+                        t.fill_(float("nan"))
                 torch.cuda.synchronize()
                 dist.barrier()
                 outs = fused.forward(xs)
@@ -74,8 +78,9 @@ def _rank_main(rank, world, port, result_path):
                              for r in range(world)], dim=1)
         shared = FusedGatherGroup(lins[0:2], arena, fold_sync=True, shared_input=True)
         for _ in range(2):
-            for lin in lins[0:2]:
-                lin.out.fill_(float("nan"))
+            for copy in range(2):
+                for t in shared.outputs(copy):
+                    t.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
             outs = shared.forward([xs[0], xs[0]])
@@ -86,6 +91,29 @@ def _rank_main(rank, world, port, result_path):
             for got, ref in ((outs[0], want[0]), (outs[1], want_up)):
                 ok &= not bool(torch.isnan(got).any())
                 ok &= float((got - ref).norm() / ref.norm()) < 2e-5
+        # Back-to-back calls with no host synchronisation and no barrier between them.  Call t uses
+        # the activations scaled by a power of two (exact in bf16 and in the kernel), so its result
+        # is the reference scaled by the same factor, bit for bit.  Rank 1's consumer is held up by
+        # a long kernel before it reads each result, so rank 0 runs ahead by as much as the
+        # protocol lets it; a store into a buffer that rank 1 has not read yet would show up as a
+        # wrong snapshot on rank 1.
+        calls = 12
+        chain = FusedGatherGroup(lins[2:3], arena, fold_sync=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        snaps = torch.zeros((calls,) + tuple(want[2].shape), device=dev)
+        ballast = torch.randn(4096, 4096, device=dev)
+        scaled = [(xs[2].float() * float(2 ** (t % 3))).to(torch.bfloat16) for t in range(calls)]
+        for t in range(calls):
+            out = chain.forward([scaled[t]])[0]
+            chain.wait()
+            if rank == 1:
+                for _ in range(3):
+                    ballast = ballast @ ballast * 1e-4  # the slow consumer
+            snaps[t].copy_(out)
+        torch.cuda.synchronize()
+        for t in range(calls):
+            ok &= bool(torch.equal(snaps[t], want[2] * float(2 ** (t % 3))))
         ok &= tb.device_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
