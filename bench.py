@@ -11,15 +11,22 @@ launch streams its weights from HBM.  Data is synthetic (seeded, with the stated
 ``value``  = raw quantised weight bytes of a step / device time, inputs resident in HBM (CUDA
              events around exactly K steps, barrier + synchronise on both sides, max over ranks).
 ``e2e``    = the same metric through the host-buffer API: activations start in pinned host memory
-             and outputs end there, every step (weights stay resident, as model parameters do).
+             and the results end there, every step (weights stay resident, as model parameters do).
 ``roofline`` is for the dominant kernel (the pipelined GEMV): algorithmic weight bytes of a launch
              / its average duration in the timed region, against the measured HBM copy bandwidth.
-``prefill`` reports the tcgen05 GEMM (Q4_K / Q6_K, N=12288, K=4096, M in {256, 512, 2048}).
+``cases``  per-batch and per-kernel rows: the three batches of the step, the first configuration of
+             the benchmark definition (Q8_0 4096 x 4096, fp16) and a Q6_K down projection.
+``prefill`` reports the tcgen05 GEMM (Q4_K / Q6_K, N=12288, K=4096, M in {256, 512, 2048}) beside the
+             ceiling without decoding: a dense bf16 GEMM on weights dequantised ahead of time.
+``decode_step`` is the 36-layer decoder configuration (252 projections per step, batch 1 and 16).
+``prefill_70b`` is the 70B-class prefill sweep at M = 4096 (on more than one GPU with the outputs
+             all-gathered over NCCL in chunks of rows that overlap the next chunk's GEMM).
 ``cpu_baseline`` times the multi-threaded C port of the reference arithmetic on the host cores on a
              bounded sample.  ``--impl reference`` runs only that port, as the reference arm.
 
-With N > 1 (torchrun, one process per GPU) every weight is column-sharded along N over the ranks
-and each projection's output is all-gathered over NCCL; total work is fixed (strong scaling).
+With N > 1 (torchrun, one process per GPU) every weight is column-sharded along N over the ranks;
+total work is fixed (strong scaling).  Decode GEMVs store their columns straight into every rank's
+output over NVLink (peer-mapped memory) with the cross-GPU ordering folded into the launches.
 """
 
 from __future__ import annotations
@@ -42,6 +49,13 @@ BATCHES = (1, 4, 16)
 FORMAT = "q4_k"
 PREFILL = (("q4_k", 12288, 4096), ("q6_k", 12288, 4096))
 PREFILL_M = (256, 512, 2048)
+# the 36-layer decoder of the benchmark definition: (name, rows N, depth K, format, which activations it reads)
+LAYER = (("q", 4096, 4096, "q4_k", 0), ("k", 1024, 4096, "q4_k", 0), ("v", 1024, 4096, "q4_k", 0),
+         ("o", 4096, 4096, "q4_k", 1), ("gate", 12288, 4096, "q4_k", 2), ("up", 12288, 4096, "q4_k", 2),
+         ("down", 4096, 12288, "q6_k", 3))
+LAYERS = 36
+BIG_PREFILL = (("gate_up", "q4_k", 28672, 8192), ("down", "q6_k", 8192, 28672))
+BIG_PREFILL_M = 4096
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "q4k_gemv_weight_gbps"
 UNIT = "GB/s"
@@ -58,23 +72,14 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def is_grouped(args, world: int) -> bool:
-    """Gate and up go out as one grouped launch (they share their activations)."""
-    return not args.separate_gate_up and (world == 1 or args.gather in ("fused", "fused-barrier"))
-
-
-def workload_config(world: int, gather: str = "fused", grouped: bool = False):
+def workload_config(world: int):
     return {
         "workload": "q4_k decode GEMV: gate/up 18944x3584 + down 3584x18944, batch 1/4/16 (9 GEMVs per step)",
-        "launches": ("gate and up share their activations and run as one grouped launch (6 GEMV launches per step)"
-                     if grouped else "one launch per GEMV"),
+        "launches": "gate and up share their activations and run as one grouped launch (6 GEMV launches per step)",
         "format": FORMAT, "batches": list(BATCHES), "activations": "bf16", "output": "fp32",
         "l2": "weights rotate over a ring of sets > 3x L2; every launch streams from HBM",
-        "parallelism": f"N-sharded x{world}" + ("" if world == 1 else (
-            " + peer stores in the GEMV epilogue over NVLink, signal/wait between ranks inside the same launches"
-            if gather == "fused" else
-            " + peer stores in the GEMV epilogue over NVLink and one barrier kernel after gate+up and after down"
-            if gather == "fused-barrier" else " + NCCL all-gather (gate+up together, then down)")),
+        "parallelism": f"N-sharded x{world}" + ("" if world == 1 else
+            " + peer stores in the GEMV epilogue over NVLink, signal/wait between ranks inside the same launches"),
     }
 
 
@@ -216,9 +221,9 @@ def run_gpu(args):
     import torch.distributed as dist
 
     import tensor_b200 as tb
-    from tensor_b200 import synth
+    from tensor_b200 import ops, synth
     from tensor_b200.peer import PeerArena
-    from tensor_b200.projection import FusedGatherGroup, GatherGroup, QuantLinear, QuantLinearPair
+    from tensor_b200.projection import ShardedGemvList
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -235,89 +240,9 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=device)
     peaks = measured_peaks()
     fmt = tb.get_format(FORMAT)
-
-    # ---- weights: ring of sets, each rank holding its rows; same seeds on every rank ----
-    step_bytes_total = sum(fmt.weight_bytes(n, k) for _, n, k in SHAPES) * len(BATCHES)
-    set_bytes_local = sum(fmt.weight_bytes(n // world, k) for _, n, k in SHAPES)
-    ring = max(2, -(-3 * L2_BYTES // set_bytes_local) + 1)
-    weights = []
-    for slot in range(ring):
-        row = []
-        for j, (_, n, k) in enumerate(SHAPES):
-            # distinct seed per (slot, projection, rank): every rank owns different rows
-            row.append(synth.make_weights(fmt, n // world, k, seed=1000 * slot + 10 * j + rank, device=device))
-        weights.append(row)
-    acts = {b: [synth.make_activations(b, k, seed=7 * b + j, device=device) for j, (_, _, k) in enumerate(SHAPES)]
-            for b in BATCHES}
-    lins = {b: [QuantLinear(weights[0][j], fmt, n, k, b, rank=rank, world=world, variant="auto")
-                for j, (_, n, k) in enumerate(SHAPES)] for b in BATCHES}
-    grouped = is_grouped(args, world)  # gate + up as one launch
-    launches_per_step = len(BATCHES) * (len(SHAPES) - 1 if grouped else len(SHAPES))
-    barriers_per_step = 2 * len(BATCHES) if world > 1 and args.gather == "fused-barrier" else 0
-    # batches above 1 run a small activation-conversion kernel ahead of each GEMV
-    barriers_per_step += sum(launches_per_step // len(BATCHES) for b in BATCHES if b > 1)
-    if world > 1 and args.gather == "fused":
-        barriers_per_step += len(BATCHES)  # the wait kernel that closes each batch
-    # gate and up are needed together (one collective for both); down follows
-    if args.gather in ("fused", "fused-barrier"):
-        # the GEMVs store their columns into every rank's output; one barrier kernel per group
-        out_bytes = sum(b * n * 4 + 256 for b in BATCHES for _, n, _ in SHAPES)
-        arena = PeerArena(out_bytes + (1 << 16), device, rank, world)
-        fold = args.gather == "fused"  # ordering inside the GEMV launches; else one barrier kernel per group
-        share = not args.separate_gate_up  # gate and up read the same activations: one grouped launch
-        groups = {b: [FusedGatherGroup(lins[b][0:2], arena, fold, shared_input=share),
-                      FusedGatherGroup(lins[b][2:3], arena, fold)] for b in BATCHES}
-    else:
-        groups = {b: [GatherGroup(lins[b][0:2]), GatherGroup(lins[b][2:3])] for b in BATCHES}
-
-    # one GPU: gate and up read the same activations and go out as ONE launch over both weights
-    pairs = None
-    if world == 1 and not args.separate_gate_up:
-        pairs = {b: QuantLinearPair(weights[0][0], SHAPES[0][1], weights[0][1], SHAPES[1][1], fmt, SHAPES[0][2], b)
-                 for b in BATCHES}
-
-    def step(slot, batches=BATCHES):
-        for b in batches:
-            if pairs is not None:
-                pairs[b].forward(acts[b][0], raw1=weights[slot][0], raw2=weights[slot][1])
-            else:
-                groups[b][0].forward(acts[b][0:2], raws=weights[slot][0:2])
-            groups[b][1].forward(acts[b][2:3], raws=weights[slot][2:3])
-            if world > 1 and args.gather == "fused":
-                groups[b][1].wait()  # the peers' columns of the last projection have landed
-
-    # ---- CUDA graphs: one per ring slot (launch-bound otherwise: a GEMV is a few microseconds) ----
     stream = torch.cuda.Stream(device)
-    graphs = {}
-
-    def capture(batches):
-        out = []
-        with torch.cuda.stream(stream):
-            step(0, batches)
-            stream.synchronize()
-            for slot in range(ring):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    step(slot, batches)
-                out.append(g)
-        return out
-
-    use_graphs = not args.no_graphs
-    if use_graphs:
-        try:
-            graphs["all"] = capture(BATCHES)
-        except Exception as exc:  # pragma: no cover - e.g. a collective that cannot be captured
-            use_graphs = False
-            if rank == 0:
-                print(f"[bench] CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
-
-    def run_steps(count, key="all", batches=BATCHES, offset=0):
-        with torch.cuda.stream(stream):
-            for i in range(count):
-                if use_graphs:
-                    graphs[key][(offset + i) % ring].replay()
-                else:
-                    step((offset + i) % ring, batches)
+    arena = PeerArena(64 << 20, device, rank, world) if world > 1 else None
+    pads = arena.pad_ptrs() if world > 1 else None
 
     def barrier():
         torch.cuda.synchronize(device)
@@ -325,44 +250,126 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    def timed(count, key="all", batches=BATCHES):
+    def max_over_ranks(value: float) -> float:
+        if world == 1:
+            return value
+        t = torch.tensor([value], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_replays(graphs, count, after=None):
+        """Device time of ``count`` replays cycling over ``graphs`` (max over ranks), in ms."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             e0.record(stream)
-        run_steps(count, key, batches)
-        with torch.cuda.stream(stream):
+            for i in range(count):
+                graphs[i % len(graphs)].replay()
+            if after is not None:
+                after()
             e1.record(stream)
         barrier()
-        ms = e0.elapsed_time(e1)
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- headline: weights as a ring of sets, each rank holding its rows; same seeds on every rank ----
+    step_bytes_total = sum(fmt.weight_bytes(n, k) for _, n, k in SHAPES) * len(BATCHES)
+    set_bytes_local = sum(fmt.weight_bytes(n // world, k) for _, n, k in SHAPES)
+    ring = max(2, -(-3 * L2_BYTES // set_bytes_local) + 1)
+    ring += ring % 2  # even: the two output copies of the N-sharded lists alternate from slot to slot
+    weights = [[synth.make_weights(fmt, n // world, k, seed=1000 * slot + 10 * j + rank, device=device)
+                for j, (_, n, k) in enumerate(SHAPES)] for slot in range(ring)]
+    acts = {b: [synth.make_activations(b, k, seed=7 * b + j, device=device) for j, (_, _, k) in enumerate(SHAPES)]
+            for b in BATCHES}
+    # gate and up read the same activations: neighbours in the list, one grouped launch
+    lists = {b: ShardedGemvList([(acts[b][0], weights[0][0], fmt, SHAPES[0][1], SHAPES[0][2]),
+                                 (acts[b][0], weights[0][1], fmt, SHAPES[1][1], SHAPES[1][2]),
+                                 (acts[b][2], weights[0][2], fmt, SHAPES[2][1], SHAPES[2][2])],
+                                arena, rank, world) for b in BATCHES}
+    launches_per_step = 2 * len(BATCHES)
+    prepare_per_step = 2 * sum(1 for b in BATCHES if b > 1)  # activation conversion ahead of batched GEMVs
+
+    def step(slot, batches=BATCHES):
+        outs = {}
+        for b in batches:
+            for j in range(3):
+                lists[b].rebind(j, w=weights[slot][j])
+            outs[b] = lists[b].forward()
+        return outs
+
+    def final_wait():
         if world > 1:
-            t = torch.tensor([ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+            ops.peer_sync(pads, rank, device, ops.PEER_WAIT)  # the peers' stores of the last launches have landed
+
+    def capture(batches):
+        graphs, outs = [], []
+        with torch.cuda.stream(stream):
+            step(0, batches)
+            step(1, batches)
+            stream.synchronize()
+            for slot in range(ring):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    outs.append(step(slot, batches))
+                graphs.append(g)
+        return graphs, outs
+
+    graphs, graph_outs = capture(BATCHES)
 
     # warm-up (also brings the clocks up), then the timed region with clock sampling
-    run_steps(max(args.warmup, 3))
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            graphs[i % ring].replay()
+        final_wait()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    ms = timed(args.steps)
+    ms = timed_replays(graphs, args.steps, after=final_wait)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = step_bytes_total / (ms_per_step * 1e-3) / 1e9
 
-    # ---- per-batch breakdown (outside the headline region) ----
+    # ---- N-sharded outputs: identical on every rank, and this rank's columns equal a local launch ----
+    sharded_ok = None
+    if world > 1:
+        ok = True
+        with torch.cuda.stream(stream):
+            graphs[0].replay()
+            final_wait()
+        barrier()
+        for b in BATCHES:
+            local = ShardedGemvList([(acts[b][0], weights[0][0], fmt, SHAPES[0][1] // world, SHAPES[0][2]),
+                                     (acts[b][0], weights[0][1], fmt, SHAPES[1][1] // world, SHAPES[1][2]),
+                                     (acts[b][2], weights[0][2], fmt, SHAPES[2][1] // world, SHAPES[2][2])])
+            mine = local.forward()
+            torch.cuda.synchronize(device)
+            for j, (_, n, _) in enumerate(SHAPES):
+                got = graph_outs[0][b][j]
+                n_local = n // world
+                ok &= bool(torch.equal(got[:, rank * n_local:(rank + 1) * n_local], mine[j]))
+                ref = got.clone()
+                dist.broadcast(ref, src=0)
+                ok &= bool(torch.equal(ref, got))
+        flag = torch.tensor([1 if ok else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        sharded_ok = bool(flag.item())
+
+    # ---- per-batch rows (medians over several timed runs, outside the headline region) ----
     cases = []
+    batch_graphs = {}
     for b in BATCHES:
-        if use_graphs:
-            graphs[b] = capture((b,))
-        reps = max(20, args.steps)
-        run_steps(5, b, (b,))
-        t = timed(reps, b, (b,)) / reps
+        batch_graphs[b], _ = capture((b,))
+        reps = max(40, args.steps)
+        with torch.cuda.stream(stream):
+            for i in range(6):
+                batch_graphs[b][i % ring].replay()
+        samples = [timed_replays(batch_graphs[b], reps, after=final_wait) / reps for _ in range(5)]
+        t = statistics.median(samples)
         bytes_b = step_bytes_total // len(BATCHES)
-        cases.append({"batch": b, "us_per_3_gemv": t * 1e3, "gbps": bytes_b / (t * 1e-3) / 1e9})
+        cases.append({"case": f"gate+up+down q4_k, batch {b}", "batch": b, "us": t * 1e3,
+                      "gbps": bytes_b / (t * 1e-3) / 1e9,
+                      "frac_of_hbm_peak": bytes_b / world / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], "samples": len(samples)})
 
     # ---- roofline of the dominant kernel: the pipelined GEMV ----
     launch_bytes_local = set_bytes_local * len(BATCHES) / launches_per_step  # weight bytes of an average launch
@@ -372,35 +379,56 @@ def run_gpu(args):
     roofline = {
         "bound": "hbm", "kernel": "gemv_mma_kernel (bulk-copy ring + mma.sync)",
         "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-        "peak_source": peaks["source"], "traffic": None,
+        "peak_source": peaks["source"],
+        # dram__bytes_read.sum + dram__bytes_write.sum of one captured 38,191,104-byte launch
+        # (profiles/gemv_q4k_batch1_18944x3584.md: 38,245,120 B, i.e. no re-reads), scaled to the weight
+        # bytes of an average launch of this run (traffic is proportional to the rows streamed)
+        "traffic": round(launch_bytes_local * 38245120 / 38191104),
         "algorithmic_bytes_per_launch": launch_bytes_local,
-        "note": f"average over the {launches_per_step} GEMV launches of a step (batch 1/4/16"
-                + (", gate and up grouped into one launch" if grouped else "")
-                + "), gaps between launches included; "
-                f"best batch ({best['batch']}) reaches {best['gbps'] / world:.0f} GB/s per GPU",
+        "note": f"average over the {launches_per_step} GEMV launches of a step (batch 1/4/16, gate and up grouped "
+                f"into one launch), gaps between launches included; best batch ({best['batch']}) reaches "
+                f"{best['gbps'] / world:.0f} GB/s per GPU",
     }
+
+    # ---- single-kernel rows: the first configuration of the definition and a Q6_K down projection ----
+    def single_case(label, name, n, k, m, x_dtype, copies):
+        f = tb.get_format(name)
+        ws = [synth.make_weights(f, n, k, seed=300 + c, device=device) for c in range(copies)]
+        x = synth.make_activations(m, k, seed=301, device=device, dtype=x_dtype)
+        lst = ShardedGemvList([(x, ws[0], f, n, k)])
+        with torch.cuda.stream(stream):
+            lst.forward()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()  # one graph over all the weight copies: launches back to back, as in a step
+            with torch.cuda.graph(g, stream=stream):
+                for c in range(copies):
+                    lst.rebind(0, w=ws[c])
+                    lst.forward()
+        reps = 10
+        samples = [timed_replays([g], reps) / (reps * copies) for _ in range(5)]
+        t = statistics.median(samples)
+        nbytes = f.weight_bytes(n, k)
+        return {"case": label, "batch": m, "us": t * 1e3, "gbps": nbytes / (t * 1e-3) / 1e9,
+                "frac_of_hbm_peak": nbytes / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], "samples": len(samples)}
+
     if world == 1:
-        # dram__bytes_read.sum + dram__bytes_write.sum from the committed ncu capture of one 38,191,104-byte
-        # launch (profiles/gemv_q4k_batch1_18944x3584.md: 38,245,120 B, i.e. no re-reads), scaled to the
-        # weight bytes of an average launch of this run (traffic is proportional to the rows streamed)
-        roofline["traffic"] = round(launch_bytes_local * 38245120 / 38191104)
+        cases.append(single_case("q8_0 4096x4096 fp16 (first configuration)", "q8_0", 4096, 4096, 1, torch.float16, 24))
+        cases.append(single_case("q6_k down 4096x12288 bf16", "q6_k", 4096, 12288, 1, torch.bfloat16, 12))
+        for b in BATCHES:
+            cases.append(single_case(f"q4_k gate 18944x3584 alone, batch {b}", "q4_k", 18944, 3584, b, torch.bfloat16, 11))
 
     # ---- end to end: host buffers in, host buffers out, every step ----
-    # device tensors that travel: with the grouped launch gate and up share one activation buffer
-    # and one [m, 2N] output
-    live_acts = {b: ([acts[b][0], acts[b][2]] if pairs is not None else list(acts[b])) for b in BATCHES}
-    live_outs = {b: ([pairs[b].out, lins[b][2].out] if pairs is not None else [l.out for l in lins[b]])
-                 for b in BATCHES}
-    x_host = {b: [a.cpu().pin_memory() for a in live_acts[b]] for b in BATCHES}
-    y_host = {b: [torch.empty(tuple(o.shape), dtype=torch.float32).pin_memory() for o in live_outs[b]] for b in BATCHES}
+    x_live = {b: [acts[b][0], acts[b][2]] for b in BATCHES}
+    x_host = {b: [a.cpu().pin_memory() for a in x_live[b]] for b in BATCHES}
+    y_host = {b: [torch.empty(tuple(o.shape), dtype=torch.float32).pin_memory() for o in graph_outs[0][b]] for b in BATCHES}
     h2d = sum(t.numel() * t.element_size() for b in BATCHES for t in x_host[b])
     d2h = sum(t.numel() * 4 for b in BATCHES for t in y_host[b])
 
-    # Every step copies every activation in from pinned host memory and every output back out.  The
-    # copies ride on two side streams and are ordered by events per batch: the largest batch runs
-    # first, so its outputs travel while the smaller batches compute, and the inputs of the next
-    # step's batch b go in as soon as this step's batch b has been computed.  Buffers are single:
-    # the compute of batch b waits until its previous outputs have left and its inputs have arrived.
+    # Every step copies every activation in from pinned host memory (on every rank: activations are
+    # replicated) and every result back out (on rank 0: one copy of the result is what a caller
+    # receives).  The copies ride on two side streams ordered by events per batch: the largest batch
+    # runs first, so its outputs travel while the smaller batches compute, and the inputs of the next
+    # step's batch b go in as soon as this step's batch b has been computed.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     order = sorted(BATCHES, reverse=True)
     ev_in = {b: torch.cuda.Event() for b in BATCHES}
@@ -409,25 +437,28 @@ def run_gpu(args):
 
     def copy_in(b):
         with torch.cuda.stream(s_in):
-            for dst, src in zip(live_acts[b], x_host[b]):
+            for dst, src in zip(x_live[b], x_host[b]):
                 dst.copy_(src, non_blocking=True)
             ev_in[b].record(s_in)
+
+    def outs_of(b, i):
+        # the output copy that replay i of a batch graph writes: the copies alternate from slot to slot
+        return lists[b].outputs((i % ring) % 2 if world > 1 else 0)
 
     def e2e_step(i):
         for b in order:
             stream.wait_event(ev_in[b])
             stream.wait_event(ev_out[b])
             with torch.cuda.stream(stream):
-                if use_graphs:
-                    graphs[b][i % ring].replay()
-                else:
-                    step(i % ring, (b,))
+                batch_graphs[b][i % ring].replay()
+                final_wait()
                 ev_done[b].record(stream)
-            s_out.wait_event(ev_done[b])
-            with torch.cuda.stream(s_out):
-                for dst, src in zip(y_host[b], live_outs[b]):
-                    dst.copy_(src, non_blocking=True)
-                ev_out[b].record(s_out)
+            if rank == 0:
+                s_out.wait_event(ev_done[b])
+                with torch.cuda.stream(s_out):
+                    for dst, src in zip(y_host[b], outs_of(b, i)):
+                        dst.copy_(src, non_blocking=True)
+                    ev_out[b].record(s_out)
             s_in.wait_event(ev_done[b])
             copy_in(b)  # the next step's inputs of this batch
 
@@ -439,7 +470,7 @@ def run_gpu(args):
     for b in BATCHES:
         ev_out[b].record(s_out)
         copy_in(b)
-    for i in range(3):
+    for i in range(4):
         e2e_step(i)
     e2e_drain()
     barrier()
@@ -447,52 +478,210 @@ def run_gpu(args):
     for i in range(args.steps):
         e2e_step(i)
     e2e_drain()
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e = {"value": step_bytes_total * args.steps / e2e_s / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "note": "activations from pinned host memory and outputs back to it every step, on copy streams "
-                   "ordered by events per batch (largest batch first); weights resident"}
+           "note": "activations from pinned host memory on every rank and the results back to it on rank 0, every "
+                   "step, on copy streams ordered by events per batch (largest batch first); weights resident"}
 
-    # ---- prefill GEMM (single GPU numbers; N-sharded when world > 1) ----
+    # free the weight ring before the next parts
+    del weights, graphs, batch_graphs, graph_outs
+    torch.cuda.empty_cache()
+
+    # ---- prefill GEMM beside its ceiling without decoding (dense bf16 GEMM on pre-dequantised weights) ----
     prefill = []
-    if rank == 0 or world > 1:
-        for name, n, k in PREFILL:
-            n_local = n // world
-            copies = max(2, -(-2 * L2_BYTES // tb.weight_bytes(name, n_local, k)))
-            ws = [synth.make_weights(name, n_local, k, seed=50 + c + rank, device=device) for c in range(copies)]
-            for m in PREFILL_M:
-                x = synth.make_activations(m, k, seed=60 + m, device=device)
-                out = torch.empty((m, n_local), dtype=torch.float32, device=device)
-                kern = tb.gguf(m, n_local, k, name, op="gemm")
-                for c in range(3):
-                    kern.launch(x, ws[c % copies], out)
-                torch.cuda.synchronize(device)
-                reps = 20
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
+    for name, n, k in PREFILL:
+        n_local = n // world
+        copies = max(2, -(-2 * L2_BYTES // tb.weight_bytes(name, n_local, k)))
+        ws = [synth.make_weights(name, n_local, k, seed=50 + c + rank, device=device) for c in range(copies)]
+        dense = [tb.dequantize(w, name, n_local, k).to(torch.bfloat16) for w in ws]
+        for m in PREFILL_M:
+            x = synth.make_activations(m, k, seed=60 + m, device=device)
+            out = torch.empty((m, n_local), dtype=torch.float32, device=device)
+            kern = tb.gguf(m, n_local, k, name, op="gemm")
+            reps = 20
+
+            def run_ours():
                 for c in range(reps):
                     kern.launch(x, ws[c % copies], out)
-                e1.record()
+
+            def run_dense():
+                for c in range(reps):
+                    torch.matmul(x, dense[c % copies].t())
+
+            row = {"format": name, "m": m, "n": n_local, "k": k}
+            for key, fn in (("us", run_ours), ("ceiling_us", run_dense)):
+                fn()
                 torch.cuda.synchronize(device)
-                us = e0.elapsed_time(e1) / reps * 1e3
-                tf = 2.0 * m * n_local * k / (us * 1e-6) / 1e12
-                prefill.append({"format": name, "m": m, "n": n_local, "k": k, "us": us, "tflops": tf,
-                                "frac_of_bf16_peak": tf / peaks["bf16_tflops"]})
-            del ws
+                samples = []
+                for _ in range(3):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn()
+                    e1.record()
+                    torch.cuda.synchronize(device)
+                    samples.append(e0.elapsed_time(e1) / reps * 1e3)
+                row[key] = statistics.median(samples)
+            row["tflops"] = 2.0 * m * n_local * k / (row["us"] * 1e-6) / 1e12
+            row["frac_of_bf16_peak"] = row["tflops"] / peaks["bf16_tflops"]
+            row["ceiling_tflops"] = 2.0 * m * n_local * k / (row["ceiling_us"] * 1e-6) / 1e12
+            row["ceiling"] = "torch.matmul, bf16 operands and output, weights dequantised ahead of time (library GEMM, no decode)"
+            prefill.append(row)
+        del ws, dense
+    torch.cuda.empty_cache()
+
+    # ---- the 36-layer decode step: 252 projections per step, two calls per layer ----
+    decode_step = []
+    if not args.skip_decode_step:
+        layer_bytes = sum(tb.weight_bytes(f, n, k) for _, n, k, f, _ in LAYER)
+        layer_w = [[synth.make_weights(f, n // world, k, seed=5000 + 10 * layer + j + 100 * rank, device=device)
+                    for j, (_, n, k, f, _) in enumerate(LAYER)] for layer in range(LAYERS)]
+        step_arena = PeerArena(48 << 20, device, rank, world) if world > 1 else None
+        step_pads = step_arena.pad_ptrs() if world > 1 else None
+        for b in (1, 16):
+            xs = {g: synth.make_activations(b, k, seed=40 + g, device=device)
+                  for g, k in ((0, 4096), (1, 4096), (2, 4096), (3, 12288))}
+            # the q4_k projections of a layer in one list (q+k and gate+up pair up), the q6_k down projection in its own
+            q4 = ShardedGemvList([(xs[g], layer_w[0][j], f, n, k) for j, (_, n, k, f, g) in enumerate(LAYER) if f == "q4_k"],
+                                 step_arena, rank, world)
+            q6 = ShardedGemvList([(xs[3], layer_w[0][6], "q6_k", LAYER[6][1], LAYER[6][2])], step_arena, rank, world)
+
+            def whole_step():
+                for layer in range(LAYERS):
+                    for j in range(6):
+                        q4.rebind(j, w=layer_w[layer][j])
+                    q4.forward()
+                    q6.rebind(0, w=layer_w[layer][6])
+                    q6.forward()
+
+            def step_wait():
+                if world > 1:
+                    ops.peer_sync(step_pads, rank, device, ops.PEER_WAIT)
+
+            with torch.cuda.stream(stream):
+                whole_step()
+                stream.synchronize()
+                gs = []
+                for _ in range(2):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        whole_step()
+                    gs.append(g)
+                for i in range(2):
+                    gs[i].replay()
+                step_wait()
+            reps = 6
+            samples = [timed_replays(gs, reps, after=step_wait) / reps for _ in range(3)]
+            t_ms = statistics.median(samples)
+            # end to end: the step's input activations from pinned host memory on every rank, the last
+            # projection's result back to the host on rank 0
+            x_in = xs[0].cpu().pin_memory()
+            y_out = torch.empty((b, LAYER[6][1]), dtype=torch.float32).pin_memory()
+            last_out = q6.outputs(q6._copy)[0]  # an even number of calls per step: every step ends on the same copy
+            barrier()
+            t0 = time.perf_counter()
+            with torch.cuda.stream(stream):
+                for i in range(reps):
+                    xs[0].copy_(x_in, non_blocking=True)
+                    gs[i % 2].replay()
+                    step_wait()
+                    if rank == 0:
+                        y_out.copy_(last_out, non_blocking=True)
+                stream.synchronize()
+            e2e_ms = max_over_ranks(time.perf_counter() - t0) / reps * 1e3
+            total = layer_bytes * LAYERS
+            decode_step.append({
+                "batch": b, "layers": LAYERS, "projections": 7 * LAYERS, "weight_bytes": total,
+                "ms": t_ms, "gbps": total / (t_ms * 1e-3) / 1e9,
+                "frac_of_hbm_peak": total / world / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                "e2e_ms": e2e_ms, "e2e_gbps": total / (e2e_ms * 1e-3) / 1e9,
+                "note": "q/k/v, o, gate/up in Q4_K (q+k and gate+up as grouped launches), down in Q6_K; projections "
+                        "only (no attention or glue); 121.5 MB of distinct weights per layer, so every launch streams from HBM"})
+            del q4, q6, gs
+        del layer_w
+        torch.cuda.empty_cache()
+
+    # ---- the 70B-class prefill sweep at M = 4096 ----
+    big_prefill = []
+    if not args.skip_big_prefill:
+        m = BIG_PREFILL_M
+        side = torch.cuda.Stream(device)
+        for label, name, n, k in BIG_PREFILL:
+            n_local = n // world
+            w = synth.make_weights(name, n_local, k, seed=900 + rank, device=device)
+            x = synth.make_activations(m, k, seed=901, device=device)
+            out_local = torch.empty((m, n_local), dtype=torch.float32, device=device)
+            kern = tb.gguf(m, n_local, k, name, op="gemm")
+            flops = 2.0 * m * n * k
+            chunks = 4 if world > 1 else 1
+            mc = m // chunks
+            kerns = tb.gguf(mc, n_local, k, name, op="gemm")
+            gathered = out_full = None
+            if world > 1:
+                gathered = torch.empty((chunks, world, mc, n_local), dtype=torch.float32, device=device)
+                out_full = torch.empty((m, n), dtype=torch.float32, device=device)
+            events = [torch.cuda.Event() for _ in range(chunks)]
+
+            def kernel_only():
+                kern.launch(x, w, out_local)
+
+            def with_gather():
+                # chunk i's all-gather (and its rearrangement into row-major [M, N]) runs on a side
+                # stream while chunk i + 1's GEMM runs on the main one
+                cur = torch.cuda.current_stream(device)
+                side.wait_stream(cur)
+                for c in range(chunks):
+                    kerns.launch(x[c * mc:(c + 1) * mc], w, out_local[c * mc:(c + 1) * mc])
+                    events[c].record(cur)
+                    side.wait_event(events[c])
+                    with torch.cuda.stream(side):
+                        dist.all_gather_into_tensor(gathered[c].view(world * mc, n_local), out_local[c * mc:(c + 1) * mc])
+                        out_full[c * mc:(c + 1) * mc].view(mc, world, n_local).copy_(gathered[c].permute(1, 0, 2))
+                cur.wait_stream(side)
+
+            row = {"projection": label, "format": name, "m": m, "n": n, "k": k, "n_local": n_local}
+            for key, fn in (("kernel_us", kernel_only), ("gathered_us", with_gather)):
+                if key == "gathered_us" and world == 1:
+                    continue
+                for _ in range(2):
+                    fn()
+                barrier()
+                samples = []
+                for _ in range(3):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(3):
+                        fn()
+                    e1.record()
+                    barrier()
+                    samples.append(max_over_ranks(e0.elapsed_time(e1)) / 3 * 1e3)
+                row[key] = statistics.median(samples)
+            row["kernel_tflops"] = flops / (row["kernel_us"] * 1e-6) / 1e12
+            row["kernel_frac_of_bf16_peak"] = row["kernel_tflops"] / world / peaks["bf16_tflops_sustained"]
+            row["peak"] = "sustained bf16 (a kernel of a millisecond runs under the power cap)"
+            if world > 1:
+                row["gathered_tflops"] = flops / (row["gathered_us"] * 1e-6) / 1e12
+                recv = (world - 1) * m * n_local * 4
+                row["gather_bytes_received_per_gpu"] = recv
+                row["gather_floor_us_at_770GBs"] = recv / 770e9 * 1e6
+                row["note"] = ("N-sharded; fp32 outputs all-gathered with NCCL in 4 chunks of rows on a side stream and "
+                               "rearranged to row-major [M, N]; the floor is the bytes a GPU must receive over NVLink")
+            big_prefill.append(row)
+            del w, x, out_local, gathered, out_full
+        torch.cuda.empty_cache()
 
     status = tb.device_status()
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16 mma / f32 accumulate", "data": "synthetic",
-        "config": workload_config(world, args.gather, grouped), "clocks": clocks, "e2e": e2e,
-        "gpu_launches": (launches_per_step + barriers_per_step) * args.steps, "roofline": roofline, "cases": cases,
-        "prefill": prefill, "cuda_graphs": use_graphs, "device_status": status,
+        "config": workload_config(world), "clocks": clocks, "e2e": e2e,
+        "gpu_launches": (launches_per_step + prepare_per_step) * args.steps + (1 if world > 1 else 0),
+        "roofline": roofline, "cases": cases, "prefill": prefill, "decode_step": decode_step,
+        "prefill_70b": big_prefill, "cuda_graphs": True, "device_status": status,
     }
+    if sharded_ok is not None:
+        line["sharded_outputs_ok"] = sharded_ok
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         rate, cores, n_steps, med, _ = cpu_port_gemv_rate(10.0)
         line["cpu_baseline"] = {
@@ -500,15 +689,17 @@ def run_gpu(args):
             "sample": f"the same nine GEMVs as a GPU step, {n_steps} passes, median {med * 1e3:.1f} ms per pass"}
     if rank == 0:
         print(json.dumps(line), flush=True)
+    failed = sharded_ok is False or status != 0
     if world > 1:
         # Every collective of this run has completed on every rank (the last one returned a value to
         # the host).  Tearing the NCCL communicator down while CUDA graphs that captured its kernels
-        # are alive was seen to block, so drop the graphs first and leave without the teardown.
-        graphs.clear()
+        # are alive was seen to block, so leave without the teardown.
         torch.cuda.synchronize(device)
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(1 if failed else 0)
+    if failed:
+        raise SystemExit(1)
 
 
 def main():
@@ -518,14 +709,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--separate-gate-up", action="store_true",
-                    help="one GPU: launch gate and up as two GEMVs instead of one grouped launch")
-    ap.add_argument("--no-graphs", action="store_true",
-                    help="launch every kernel eagerly (for per-kernel profiling; the numbers then include "
-                         "the host's launch overhead)")
-    ap.add_argument("--gather", default="fused", choices=("fused", "fused-barrier", "nccl"),
-                    help="multi-GPU: peer stores and signal/wait inside the GEMV launches; the same stores with a "
-                         "barrier kernel per group; or NCCL all-gather")
+    ap.add_argument("--skip-decode-step", action="store_true", help="leave the 36-layer decode step out")
+    ap.add_argument("--skip-big-prefill", action="store_true", help="leave the 70B-class prefill sweep out")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -290,6 +290,68 @@ class FusedGatherGroup:
     __call__ = forward
 
 
+class ShardedGemvList:
+    """Independent projections of one rank of an N-sharded run, issued with one call: a decoder
+    layer's q/k/v, o, gate/up, down, or one MLP at several batches.  ``specs`` is a list of
+    ``(x, raw_local, encoding, n, k)``: ``raw_local`` holds this rank's ``n / world`` rows of the
+    ``[n, k]`` weight, ``x`` the replicated ``[m, k]`` activations.  Every rank ends with every full
+    ``[m, n]`` output: the kernels store their columns into all ranks' outputs (peer-mapped memory of
+    ``arena``), the first launch of a call waits for the peers' previous signal, the last one signals.
+    Outputs exist twice and calls alternate between the copies (see :class:`FusedGatherGroup`).
+    With ``world == 1`` no arena is needed and the outputs are ordinary tensors."""
+
+    def __init__(self, specs, arena=None, rank: int = 0, world: int = 1, variant="auto"):
+        self.rank, self.world = rank, world
+        self.device = specs[0][0].device
+        if world > 1 and arena is None:
+            raise ValueError("an N-sharded list needs a PeerArena")
+        self._outs = [[], []]
+        entries = [[], []]
+        self.weight_bytes_local = 0
+        for x, raw, encoding, n, k in specs:
+            fmt = get_format(encoding)
+            start, stop = shard_rows(n, rank, world)
+            n_local = stop - start
+            if raw.numel() != fmt.weight_bytes(n_local, k):
+                raise ValueError(f"raw holds {raw.numel()} bytes; {n_local} rows of K={k} need {fmt.weight_bytes(n_local, k)}")
+            m = x.numel() // k
+            self.weight_bytes_local += raw.numel()
+            for copy in range(2 if world > 1 else 1):
+                if world > 1:
+                    offset = arena.take(m * n * 4)
+                    out = arena.view(offset, (m, n))
+                    dest = (arena.ptrs(offset), n, start)
+                else:
+                    out = torch.empty((m, n), dtype=torch.float32, device=self.device)
+                    dest = out
+                self._outs[copy].append(out)
+                entries[copy].append((x, raw, fmt, n_local, k, dest))
+        pads = arena.pad_ptrs() if world > 1 else None
+        sync = (ops.PEER_WAIT | ops.PEER_SIGNAL) if world > 1 else 0
+        self._lists = [ops.GemvList(e, pad_ptrs=pads, rank=rank, sync=sync, variant=variant) for e in entries if e]
+        self._copy = len(self._lists) - 1
+
+    def outputs(self, copy: int = 0):
+        return list(self._outs[copy])
+
+    def rebind(self, index: int, x=None, w=None) -> None:
+        for lst in self._lists:
+            lst.rebind(index, x=x, w=w)
+
+    def forward(self, stream=None):
+        """Enqueue the projections; returns the ``[m, n]`` outputs of the copy this call writes."""
+        self._copy = (self._copy + 1) % len(self._lists)
+        self._lists[self._copy].launch(stream)
+        return list(self._outs[self._copy])
+
+    def wait(self, pads, stream=None) -> None:
+        """For a consumer that is not the next call of a list: wait until the peers' stores have landed."""
+        if self.world > 1:
+            ops.peer_sync(pads, self.rank, self.device, ops.PEER_WAIT, stream)
+
+    __call__ = forward
+
+
 class HostProjection:
     """Host-buffer front end: activations arrive in (pinned) host memory and results are returned
     in host memory; weights stay resident on the GPU.  One call = H2D copy of ``x``, the kernel(s),
@@ -317,5 +379,5 @@ class HostProjection:
         return self.y_host
 
 
-__all__ = ["FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "QuantLinearPair", "all_gather_columns", "shard_rows",
-           "shard_weight_bytes"]
+__all__ = ["FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "QuantLinearPair",
+           "ShardedGemvList", "all_gather_columns", "shard_rows", "shard_weight_bytes"]
