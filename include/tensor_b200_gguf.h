@@ -98,8 +98,8 @@ typedef struct TensorErrorV1 {
 #define TB200_VARIANT_SIMPLE 1 /* SIMT fp32 kernels, any shape */
 #define TB200_VARIANT_FAST 2   /* a pipelined tensor-core kernel or an error: GEMV bulk-copy ring + mma.sync, GEMM tcgen05 */
 #define TB200_VARIANT_MMA 3    /* GEMV only: the same as FAST */
-#define TB200_VARIANT_TC 4     /* GEMV only: the persistent tcgen05 / TMEM kernel (needs scratch), or an error;
-                                * never chosen by AUTO: measured slower than the mma.sync pipeline on B200 */
+#define TB200_VARIANT_TC 4     /* GEMV only: the persistent tcgen05 / TMEM kernel (Q4_K, Q6_K; needs scratch), or an
+                                * error.  AUTO picks it for Q6_K; for Q4_K the mma.sync pipeline measures faster */
 
 /* Library / ABI version: (major << 16) | minor. */
 int32_t tb200_gguf_version(void);
@@ -236,7 +236,7 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
  * the column window already added to the pointers).  Items must not depend on one another.
  * Neighbouring items with the same x pointer, m, k and format run as one grouped launch.
  * variant: TB200_VARIANT_AUTO ... as for tb200_gguf_gemv; TB200_VARIANT_TC runs the whole list as ONE
- * persistent tcgen05 / TMEM launch (Q4_K, 2-byte activations, m <= 16).
+ * persistent tcgen05 / TMEM launch (Q4_K or Q6_K, 2-byte activations, m <= 16).
  * scratch: tb200_gguf_gemv_list_scratch_bytes, 256-byte aligned, zeroed before first use, not shared
  * with a call that may overlap.  pads / rank / world / sync as in tb200_gguf_gemv_sharded_sync (sync 0
  * on one GPU): the first launch waits, the last one signals. */

@@ -169,7 +169,18 @@ int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int6
   if (!dev) return 0;
   // The plan does not depend on the 2-byte activation type.
   GemvPlan plan = plan_gemv_fast(format, kBF16, m, n, k, (long long)1 << 40, *dev);
-  return plan.supported ? plan.scratch_bytes : 0;
+  if (plan.supported) return plan.scratch_bytes;
+  if (format == kQ6_K && gemv_tc_supported(format, kBF16, m, n, k)) {  // served by the tensor-memory kernel
+    TcLaunchItem item{};
+    item.fmt = format;
+    item.xt = kBF16;
+    item.m = m;
+    item.n = n;
+    item.k = k;
+    item.x_share = -1;
+    return gemv_tc_scratch_bytes(&item, 1, *dev);
+  }
+  return 0;
 }
 
 int32_t tb200_gguf_gemv_plan(int32_t format, int64_t m, int64_t n, int64_t k, int64_t scratch_bytes,
@@ -272,9 +283,12 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (int32_t s = require_device(error, &dev)) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint8_t* wp = static_cast<const uint8_t*>(w);
-  // The tensor-memory kernel runs only on request: measured on B200 it is slower than the mma.sync
-  // pipeline at every batch (tcgen05 takes in one 128-row k-slice per 4 cycles whatever the batch).
-  if (variant == TB200_VARIANT_TC) {
+  // The tensor-memory kernel: on request, and by default for Q6_K, which has no other pipelined GEMV
+  // (measured 1.0x .. 10x faster than the SIMT kernels there).  For Q4_K it is measured slower than the
+  // mma.sync pipeline at every batch on B200, so the default never picks it.
+  const bool tc_default = format == kQ6_K && (variant == TB200_VARIANT_AUTO || variant == TB200_VARIANT_FAST) &&
+                          gemv_tc_supported(format, x_dtype, m, n, k);
+  if (variant == TB200_VARIANT_TC || tc_default) {
     TcLaunchItem item{};
     item.fmt = format;
     item.xt = x_dtype;
@@ -291,8 +305,9 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
       if (e != cudaSuccess) return cuda_fail(error, "tensor-memory GEMV launch", e);
       return ok(error);
     }
+    if (variant == TB200_VARIANT_TC)
     return fail(error, TENSOR_ERROR_ARGUMENT,
-                "the tensor-memory GEMV needs format 12, 2-byte activations, m <= 16 and %lld bytes of scratch "
+                "the tensor-memory GEMV needs format 12 or 14 (K a multiple of 2048), 2-byte activations, m <= 16 and %lld bytes of scratch "
                 "(format %d, dtype %d, m=%lld, n=%lld, k=%lld, scratch %lld)",
                 need, format, x_dtype, (long long)m, (long long)n, (long long)k,
                 (long long)(scratch ? scratch_bytes : 0));
@@ -732,7 +747,7 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
     cudaError_t e;
     if (!try_list(list, count, scratch, scratch_bytes, *dev, st, peers.flags ? &peers : nullptr, &e))
       return fail(error, TENSOR_ERROR_ARGUMENT,
-                  "the persistent tensor-memory kernel takes Q4_K lists with 2-byte activations, m <= 16 and %lld "
+                  "the persistent tensor-memory kernel takes Q4_K or Q6_K lists with 2-byte activations, m <= 16 and %lld "
                   "bytes of scratch", (long long)gemv_tc_scratch_bytes(list, count, *dev));
     if (e != cudaSuccess) return cuda_fail(error, "tensor-memory GEMV launch (list)", e);
     return ok(error);

@@ -52,8 +52,7 @@ constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kProducerWarp = kDecodeWarps, kMmaWarp = kDecodeWarps + 1;
 constexpr int kThreads = (kDecodeWarps + 2) * 32;
 constexpr int kUnitK = 256;                   // weights per row and unit
-constexpr int kXMainBytes = 16 * kUnitK * 2;  // activation tile: 16 rows x 256 k, fp16
-constexpr int kXTileBytes = kXMainBytes + 512;  // + fp32 sums of the 8 scale groups of each of the 16 rows
+constexpr int kXMainBytes = 16 * kUnitK * 2;  // activation tile: 16 rows x 256 k, fp16; the sums of its scale groups follow
 constexpr int kMaxStagesTc = 8;
 constexpr int kSlotFloats = 16 * kRows;       // one partial-sum slot
 constexpr int kSmemHeader = 1024;
@@ -94,7 +93,9 @@ struct alignas(64) TcParams {
 #endif
 #ifdef TB200_TC_TRACE
 #define TC_DEBUG(bit) (p.debug & (bit))
+#define TC_WALL(cond, slot) do { if (p.trace && blockIdx.x == 0 && (cond)) p.trace[63 * 16 + (slot)] = (long long)ptx::global_timer_ns(); } while (0)
 #else
+#define TC_WALL(cond, slot) do { } while (0)
 #define TC_DEBUG(bit) 0
 #endif
 
@@ -260,8 +261,20 @@ struct UnitScales {
 template <int FMT> struct TcFormat;
 template <> struct TcFormat<kQ4_K> {
   static constexpr int kBoxBytes = 144;    // bytes of a row inside a unit's ring stage
-  static constexpr int kBoxStep = 144;     // bytes between consecutive units of a row
-  __device__ static __forceinline__ void decode(uint32_t wrow, int part, uint32_t tmem_a, UnitScales& out) {
+  static constexpr int kSub = 1;           // sub-units a staged block is decoded in
+  static constexpr int kSumGroups = 8;     // scale groups per block whose activation sums travel with the tile
+  static constexpr int kXTileBytes = kXMainBytes + kSumGroups * 64;
+  __host__ __device__ static __forceinline__ int box_x(int sb) { return sb * 18; }  // 8-byte units
+  __host__ __device__ static __forceinline__ int box_offset(int) { return 0; }
+  // two k-steps of 16 per 32-weight group; a k-step's activations are 512 bytes (32 descriptor units)
+  __device__ static __forceinline__ void issue(uint32_t d, uint32_t a, uint64_t xdesc, int, uint32_t idesc) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      umma_ts<false>(d + 16 * g, a + 16 * g, xdesc + 64 * g, idesc);
+      umma_ts<true>(d + 16 * g, a + 16 * g + 8, xdesc + 64 * g + 32, idesc);
+    }
+  }
+  __device__ static __forceinline__ void decode(uint32_t wrow, int part, int, int, uint32_t tmem_a, UnitScales& out) {
     const uint4 hdr = ptx::lds128(wrow);
     const uint4 q0 = ptx::lds128(wrow + 16 + 32 * part), q1 = ptx::lds128(wrow + 32 + 32 * part);
     const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
@@ -303,6 +316,78 @@ template <> struct TcFormat<kQ4_K> {
   }
 };
 
+// ---- Q6_K: 210-byte blocks (ql[128] low nibbles, qh[64] high bit pairs, 16 int8 scales, fp16 d), 16
+// scale groups of 16 weights, w = d * sc * (q - 32).  A staged block is decoded as two sub-units of 128
+// weights (the two halves of the block layout): quarter p of half h = bytes ql[64h + 32(p%2) ..+32]
+// (low nibbles for p < 2, high ones else) joined with bit pair p of qh[32h ..+32]; its 32 weights are
+// the scale groups 2p and 2p + 1 of the half.  Every k-step of 16 is one scale group with its own
+// accumulator block, so no MMA accumulates.  Blocks are only 2-byte aligned: the ring holds, per row, the
+// 240 bytes from the 16-byte boundary below the block, and `O` says where the block starts in there.
+template <> struct TcFormat<kQ6_K> {
+  static constexpr int kBoxBytes = 240;
+  static constexpr int kSub = 2;
+  static constexpr int kSumGroups = 16;
+  static constexpr int kXTileBytes = kXMainBytes + kSumGroups * 64;
+  __host__ __device__ static __forceinline__ int box_x(int sb) { return (210 * sb / 16) * 2; }  // 8-byte units
+  __host__ __device__ static __forceinline__ int box_offset(int sb) { return (210 * sb) & 15; }
+
+  // 32 bytes that start O bytes into the three aligned 16-byte words at `addr`
+  template <int O>
+  __device__ static __forceinline__ void load32(uint32_t addr, uint32_t (&out)[8]) {
+    const uint4 a = ptx::lds128(addr), b = ptx::lds128(addr + 16), c = ptx::lds128(addr + 32);
+    const uint32_t w[12] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w};
+    constexpr int kWord = O >> 2, kHalf = (O >> 1) & 1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      out[i] = kHalf ? __funnelshift_r(w[i + kWord], w[i + kWord + 1], 16) : w[i + kWord];
+  }
+
+  template <int O>
+  __device__ static __forceinline__ void decode_at(uint32_t wrow, int part, int sub, uint32_t tmem_a, UnitScales& out) {
+    uint32_t ql[8], qh[8];
+    load32<O>(wrow + sub * 64 + (part & 1) * 32, ql);
+    load32<O>(wrow + 128 + sub * 32, qh);
+    const int lsh = (part >> 1) * 4, hsh = 2 * part;
+    uint32_t cells[16];
+    uint32_t magic;
+    asm volatile("mov.b32 %0, 0x64646464;" : "=r"(magic));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t q = ((ql[i] >> lsh) & 0x0F0F0F0Fu) | (((qh[i] >> hsh) & 0x03030303u) << 4);  // four 6-bit values
+      cells[2 * i] = __byte_perm(q, magic, 0x4140);      // fp16 pair 1024 + q of bytes 0, 1
+      cells[2 * i + 1] = __byte_perm(q, magic, 0x4342);  // bytes 2, 3
+    }
+    tmem_st16(tmem_a + 16 * part, cells);
+    // int8 scales of groups 2p, 2p+1 of this half; fp16 d
+    unsigned short sc2, dbits;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc2) : "r"(wrow + O + 192 + 8 * sub + 2 * part));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dbits) : "r"(wrow + O + 208));
+    const float d = __half2float(__ushort_as_half(dbits));
+    out.s_lo = d * (float)(int)(signed char)(sc2 & 0xFF);
+    out.s_hi = d * (float)(int)(signed char)(sc2 >> 8);
+    out.e_lo = 1056.f * out.s_lo;  // (1024 + q) - 1056 = q - 32
+    out.e_hi = 1056.f * out.s_hi;
+  }
+  __device__ static __forceinline__ void decode(uint32_t wrow, int part, int sub, int offset, uint32_t tmem_a,
+                                                UnitScales& out) {
+    switch (offset >> 1) {  // the same for every thread of the CTA
+      case 0: decode_at<0>(wrow, part, sub, tmem_a, out); break;
+      case 1: decode_at<2>(wrow, part, sub, tmem_a, out); break;
+      case 2: decode_at<4>(wrow, part, sub, tmem_a, out); break;
+      case 3: decode_at<6>(wrow, part, sub, tmem_a, out); break;
+      case 4: decode_at<8>(wrow, part, sub, tmem_a, out); break;
+      case 5: decode_at<10>(wrow, part, sub, tmem_a, out); break;
+      case 6: decode_at<12>(wrow, part, sub, tmem_a, out); break;
+      default: decode_at<14>(wrow, part, sub, tmem_a, out); break;
+    }
+  }
+  // one accumulator block per 16-weight group: 8 MMAs per sub-unit, none accumulating
+  __device__ static __forceinline__ void issue(uint32_t d, uint32_t a, uint64_t xdesc, int sub, uint32_t idesc) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) umma_ts<false>(d + 16 * g, a + 8 * g, xdesc + 32 * (8 * sub + g), idesc);
+  }
+};
+
 // accumulators of one unit -> this thread's running sums (its two groups, NB activation rows)
 template <int NB>
 __device__ __forceinline__ void drain(uint32_t tmem_d, int part, const UnitScales& sc, float (&acc)[16]) {
@@ -318,10 +403,10 @@ __device__ __forceinline__ void drain(uint32_t tmem_d, int part, const UnitScale
 }
 // the e_g Sx_g terms of a unit, from the group sums that travel with its activation tile
 template <int NB>
-__device__ __forceinline__ void correct(uint32_t sums, int part, const UnitScales& sc, float (&acc)[16]) {
+__device__ __forceinline__ void correct(uint32_t sums, int group, const UnitScales& sc, float (&acc)[16]) {
   float sx_lo[NB], sx_hi[NB];
-  lds_floats<NB>(sums + (2 * part) * 64, sx_lo);
-  lds_floats<NB>(sums + (2 * part + 1) * 64, sx_hi);
+  lds_floats<NB>(sums + group * 64, sx_lo);
+  lds_floats<NB>(sums + (group + 1) * 64, sx_hi);
 #pragma unroll
   for (int b = 0; b < NB; ++b) {
     acc[b] = fmaf(-sc.e_lo, sx_lo[b], acc[b]);
@@ -424,11 +509,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
   float* red = reinterpret_cast<float*>(smem + kSmemHeader + p.stages * p.stage_bytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  TC_WALL(threadIdx.x == 0, 0);
   const int S = p.stages;
   const int u0 = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
   const int u1 = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
   const int count = u1 - u0;
   constexpr int kWTileBytes = kRows * F::kBoxBytes;
+  constexpr int kXTileBytes = F::kXTileBytes;
+  constexpr int kSub = F::kSub;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -466,12 +554,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
       const int pre = count < S ? count : S;
       Cursor c = first;
       for (int i = 0; i < pre; ++i) {
-        ptx::mbar_arrive_expect_tx(&full[i], (uint32_t)(kWTileBytes + kXTileBytes));
-        ptx::tma_load_2d(smem + kSmemHeader + i * p.stage_bytes, &p.wmap[c.item], c.sb * (F::kBoxStep / 8),
-                         c.tile * kRows, &full[i]);
+        ptx::mbar_arrive_expect_tx(&full[i], (uint32_t)((TC_DEBUG(8) ? 0 : kWTileBytes) + (TC_DEBUG(4) ? 0 : kXTileBytes)));
+        if (!TC_DEBUG(8))
+        ptx::tma_load_2d(smem + kSmemHeader + i * p.stage_bytes, &p.wmap[c.item], F::box_x(c.sb), c.tile * kRows,
+                         &full[i]);
         advance(p, c);
       }
       ptx::grid_dependency_wait();
+      TC_WALL(true, 1);
       if (p.sync & kPeerWait) {
         // until every peer has signalled as often as this rank has (their stores into buffers this
         // list reads have landed); bounded
@@ -495,6 +585,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
       }
       Cursor c2 = first;
       for (int i = 0; i < pre; ++i) {
+        if (!TC_DEBUG(4))
         ptx::bulk_g2s(smem + kSmemHeader + i * p.stage_bytes + kWTileBytes,
                       p.item[c2.item].xprep + (size_t)c2.sb * kXTileBytes, kXTileBytes, &full[i]);
         advance(p, c2);
@@ -504,9 +595,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
         if (!wait_bar(&empty[s], ((idx / S) - 1) & 1, abort, 0x10000u | (unsigned)s)) break;
         TC_STAMP(true, idx, 0);
         uint8_t* dst = smem + kSmemHeader + s * p.stage_bytes;
-        ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)(kWTileBytes + kXTileBytes));
-        ptx::tma_load_2d(dst, &p.wmap[c.item], c.sb * (F::kBoxStep / 8), c.tile * kRows, &full[s]);
-        ptx::bulk_g2s(dst + kWTileBytes, p.item[c.item].xprep + (size_t)c.sb * kXTileBytes, kXTileBytes, &full[s]);
+        ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)((TC_DEBUG(8) ? 0 : kWTileBytes) + (TC_DEBUG(4) ? 0 : kXTileBytes)));
+        if (!TC_DEBUG(8)) ptx::tma_load_2d(dst, &p.wmap[c.item], F::box_x(c.sb), c.tile * kRows, &full[s]);
+        if (!TC_DEBUG(4)) ptx::bulk_g2s(dst + kWTileBytes, p.item[c.item].xprep + (size_t)c.sb * kXTileBytes, kXTileBytes, &full[s]);
         advance(p, c);
       }
     }
@@ -515,27 +606,37 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
     if (lane == 0) {
       uint32_t idesc;
       asm volatile("mov.b32 %0, %1;" : "=r"(idesc) : "n"(kIdesc));
-      for (int idx = 0; idx < count; ++idx) {
-        const int s = idx % S, buf = idx & 1, use = idx >> 1;
-        if (!wait_bar(&full[s], (idx / S) & 1, abort, 0x20000u | (unsigned)s)) break;
-        if (!wait_bar(&a_ready[buf], use & 1, abort, 0x30000u)) break;
-        if (use > 0 && !wait_bar(&d_free[buf], (use - 1) & 1, abort, 0x40000u)) break;
-        TC_STAMP(true, idx, 1);
-        ptx::tc_fence_after();
-        const uint32_t a = tmem + kColA + buf * kBufCols;
-        const uint32_t d = tmem + kColD + buf * kBufCols;
+      int s = 0, full_phase = 0, step = 0;  // step counts sub-units: buffers alternate between them
+      bool ok = true;
+      for (int idx = 0; idx < count && ok; ++idx) {
+        TC_STAMP(true, idx, 8);
+        if (!wait_bar(&full[s], full_phase, abort, 0x20000u | (unsigned)s)) break;
+        TC_STAMP(true, idx, 9);
         const uint64_t xdesc = desc_kmajor(stage0 + s * p.stage_bytes + kWTileBytes);
-        if (!TC_DEBUG(1)) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          // two k-steps of 16 per 32-weight group; a k-step's activations are 512 bytes (32 descriptor units)
-          umma_ts<false>(d + 16 * g, a + 16 * g, xdesc + 64 * g, idesc);
-          umma_ts<true>(d + 16 * g, a + 16 * g + 8, xdesc + 64 * g + 32, idesc);
+        for (int sub = 0; sub < kSub; ++sub, ++step) {
+          const int buf = step & 1, use = step >> 1;
+          if (!wait_bar(&a_ready[buf], use & 1, abort, 0x30000u)) {
+            ok = false;
+            break;
+          }
+          TC_STAMP(true, idx, 10);
+          if (use > 0 && !wait_bar(&d_free[buf], (use - 1) & 1, abort, 0x40000u)) {
+            ok = false;
+            break;
+          }
+          TC_STAMP(true, idx, 1);
+          ptx::tc_fence_after();
+          if (!TC_DEBUG(1)) F::issue(tmem + kColD + buf * kBufCols, tmem + kColA + buf * kBufCols, xdesc, sub, idesc);
+          TC_STAMP(true, idx, 11);
+          if (sub == kSub - 1) ptx::umma_commit(&empty[s]);
+          ptx::umma_commit(&d_ready[buf]);
+          TC_STAMP(true, idx, 2);
         }
+        if (++s == S) {
+          s = 0;
+          full_phase ^= 1;
         }
-        ptx::umma_commit(&empty[s]);
-        ptx::umma_commit(&d_ready[buf]);
-        TC_STAMP(true, idx, 2);
       }
     }
   } else {
@@ -551,12 +652,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
     for (int b = 0; b < 16; ++b) acc[b] = 0.f;
 
     // the accumulators of unit `idx` (its MMAs ran while the unit after it was decoded)
-    auto drain_unit = [&](int nb, int idx, const UnitScales& sc) -> bool {
-      const int buf = idx & 1;
-      if (!wait_bar(&d_ready[buf], (idx >> 1) & 1, abort, 0x60000u)) return false;
-      TC_STAMP(tid == 0, idx, 5);
+    auto drain_unit = [&](int nb, int at_step, const UnitScales& sc) -> bool {
+      const int buf = at_step & 1;
+      if (!wait_bar(&d_ready[buf], (at_step >> 1) & 1, abort, 0x60000u)) return false;
+      TC_STAMP(tid == 0, at_step, 5);
       ptx::tc_fence_after();
       const uint32_t d = tmem + lane_base + kColD + buf * kBufCols;
+#ifdef TB200_TC_ONLY16
+      drain<16>(d, part, sc, acc);
+#else
       switch (nb) {
         case 1: drain<1>(d, part, sc, acc); break;
         case 2: drain<2>(d, part, sc, acc); break;
@@ -564,10 +668,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
         case 8: drain<8>(d, part, sc, acc); break;
         default: drain<16>(d, part, sc, acc); break;
       }
+#endif
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&d_free[buf]);
-      TC_STAMP(tid == 0, idx, 6);
+      TC_STAMP(tid == 0, at_step, 6);
       return true;
     };
     // this thread's sums of the segment that ended -> staging buffer, then the CTA-wide part
@@ -582,57 +687,71 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
     };
 
     Cursor cur = count > 0 ? locate(p, u0) : Cursor{0, 0, 0};
-    Cursor prev = cur;
+    Cursor prev = cur;  // the block whose sub-unit is still in the tensor core
     int seg_sb0 = cur.sb;
     UnitScales sc_prev{};
     bool ok = true;
+    int s = 0, full_phase = 0, step = 0;  // step counts sub-units
     for (int idx = 0; idx < count && ok; ++idx) {
-      const int s = idx % S;
-      if (!wait_bar(&full[s], (idx / S) & 1, abort, 0x70000u | (unsigned)s)) {
+      if (!wait_bar(&full[s], full_phase, abort, 0x70000u | (unsigned)s)) {
         ok = false;
         break;
       }
       TC_STAMP(tid == 0, idx, 3);
-      TC_STAMP(lane == 0 && warp == 5, idx, 12);
-      TC_STAMP(lane == 0 && warp == 15, idx, 13);
+      TC_WALL(tid == 0 && idx == 0, 2);
       const uint32_t stage = stage0 + s * p.stage_bytes;
-      UnitScales sc_cur{};
-      if (!TC_DEBUG(2)) F::decode(stage + row * F::kBoxBytes, part, tmem + lane_base + kColA + (idx & 1) * kBufCols, sc_cur);
-      tmem_st_wait();
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&a_ready[idx & 1]);
-      TC_STAMP(tid == 0, idx, 4);
-      TC_STAMP(lane == 0 && warp == 5, idx, 8);
-      TC_STAMP(lane == 0 && warp == 10, idx, 9);
-      TC_STAMP(lane == 0 && warp == 15, idx, 10);
-      TC_STAMP(lane == 0 && warp == 13, idx, 11);
-      if (idx > 0) {
-        ok = drain_unit(p.item[prev.item].nb, idx - 1, sc_prev);
-        if (ok && (cur.item != prev.item || cur.tile != prev.tile)) {
-          ok = end_segment(prev, seg_sb0);
-          seg_sb0 = cur.sb;
+      const int offset = F::box_offset(cur.sb);
+      const int nb_cur = p.item[cur.item].nb;
+#pragma unroll
+      for (int sub = 0; sub < kSub && ok; ++sub, ++step) {
+        UnitScales sc_cur{};
+        if (!TC_DEBUG(2))
+          F::decode(stage + row * F::kBoxBytes, part, sub, offset, tmem + lane_base + kColA + (step & 1) * kBufCols, sc_cur);
+        tmem_st_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&a_ready[step & 1]);
+        TC_STAMP(tid == 0, idx, 4);
+        if (step > 0) {
+          // the sub-unit before: its MMAs ran while this one was decoded
+          ok = drain_unit(p.item[prev.item].nb, step - 1, sc_prev);
+          if (ok && sub == 0 && (cur.item != prev.item || cur.tile != prev.tile)) {
+            ok = end_segment(prev, seg_sb0);
+            seg_sb0 = cur.sb;
+          }
         }
-      }
-      // the Sx terms of this unit need nothing from the tensor core
-      const uint32_t sums = stage + kWTileBytes + kXMainBytes;
-      switch (p.item[cur.item].nb) {
-        case 1: correct<1>(sums, part, sc_cur, acc); break;
-        case 2: correct<2>(sums, part, sc_cur, acc); break;
-        case 4: correct<4>(sums, part, sc_cur, acc); break;
-        case 8: correct<8>(sums, part, sc_cur, acc); break;
-        default: correct<16>(sums, part, sc_cur, acc); break;
+        if (!ok) break;
+        // the Sx terms of this sub-unit need nothing from the tensor core
+        const uint32_t sums = stage + kWTileBytes + kXMainBytes;
+        const int group = (F::kSumGroups / kSub) * sub + 2 * part;
+#ifdef TB200_TC_ONLY16
+        correct<16>(sums, group, sc_cur, acc);
+#else
+        switch (nb_cur) {
+          case 1: correct<1>(sums, group, sc_cur, acc); break;
+          case 2: correct<2>(sums, group, sc_cur, acc); break;
+          case 4: correct<4>(sums, group, sc_cur, acc); break;
+          case 8: correct<8>(sums, group, sc_cur, acc); break;
+          default: correct<16>(sums, group, sc_cur, acc); break;
+        }
+#endif
+        sc_prev = sc_cur;
+        prev = cur;
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);  // this warp is done with the stage
-      sc_prev = sc_cur;
-      prev = cur;
       advance(p, cur);
+      if (++s == S) {
+        s = 0;
+        full_phase ^= 1;
+      }
     }
+    TC_WALL(tid == 0, 3);
     if (ok && count > 0) {
-      ok = drain_unit(p.item[prev.item].nb, count - 1, sc_prev);
+      ok = drain_unit(p.item[prev.item].nb, step - 1, sc_prev);
       if (ok) ok = end_segment(prev, seg_sb0);
     }
+    TC_WALL(tid == 0, 5);
   }
 
   ptx::tc_fence_before();
@@ -648,6 +767,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
+  TC_WALL(threadIdx.x == 0, 4);
   if (threadIdx.x == 0 && (p.sync & kPeerSignal)) {
     // every warp of this CTA has stored what it will store; the last CTA of the grid tells the peers
     unsigned int* mine = p.pads[p.rank];
@@ -677,22 +797,34 @@ struct PrepX {
 };
 struct PrepArgs {
   PrepX x[kTcMaxItems];
+#ifdef TB200_TC_TRACE
+  long long* trace;
+#endif
 };
+#ifdef TB200_TC_TRACE
+#define PREP_WALL(slot) do { if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.trace[63 * 16 + (slot)] = (long long)ptx::global_timer_ns(); } while (0)
+#else
+#define PREP_WALL(slot) do { } while (0)
+#endif
 
 template <int FMT, bool F16>
 __global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) {
+  constexpr int kXTileBytes = TcFormat<FMT>::kXTileBytes;
+  constexpr int kSumGroups = TcFormat<FMT>::kSumGroups;
   __shared__ uint32_t s_max[8];
   const PrepX px = a.x[blockIdx.y];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  PREP_WALL(8);
   if (tid == 0) ptx::grid_launch_dependents();  // the GEMV behind fills its weight ring meanwhile
   ptx::grid_dependency_wait();                   // the GEMV before may still read these tiles
+  PREP_WALL(9);
   const int chunks = px.k >> 3;                  // 8 values = 16 bytes; a multiple of 32
   if (b >= px.m) {
     const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int c = tid; c < chunks; c += 256) {
       const int j = c >> 5, k8 = c & 31;
       *reinterpret_cast<uint4*>(px.xprep + (size_t)j * kXTileBytes + k8 * 256 + b * 16) = zero;
-      if (k8 < 8) *reinterpret_cast<float*>(px.xprep + (size_t)j * kXTileBytes + kXMainBytes + k8 * 64 + b * 4) = 0.f;
+      if (k8 < kSumGroups) *reinterpret_cast<float*>(px.xprep + (size_t)j * kXTileBytes + kXMainBytes + k8 * 64 + b * 4) = 0.f;
     }
     if (tid == 0) px.unscale[b] = 1.f;
     return;
@@ -742,21 +874,27 @@ __global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) 
       h[i] = __float2half_rn(f[i]);
       sum += __half2float(h[i]);
     }
-    // the four chunks of a 32-value scale group sit in four neighbouring lanes
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    // where the chunk goes: unit j, scale group g, core column k8; order inside each 4-value word
-    // [x0, x2, x1, x3] (see TcFormat<kQ4_K>)
-    const int j = c >> 5, cc = c & 31;         // chunk inside the unit: 8 cc .. 8 cc + 7
-    const int quarter = cc >> 3, nib = (cc >> 2) & 1, i8 = cc & 3;
-    const int g = 2 * quarter + nib;
-    const int k8 = 4 * g + i8;
-    auto pack = [&](int lo, int hi) { return (uint32_t)__half_as_ushort(h[lo]) | ((uint32_t)__half_as_ushort(h[hi]) << 16); };
-    const uint4 o = make_uint4(pack(0, 2), pack(1, 3), pack(4, 6), pack(5, 7));
+    const int j = c >> 5, cc = c & 31;  // unit, chunk inside the unit: values 8 cc .. 8 cc + 7
     uint8_t* tile = px.xprep + (size_t)j * kXTileBytes;
-    *reinterpret_cast<uint4*>(tile + k8 * 256 + b * 16) = o;
-    if (i8 == 0) *reinterpret_cast<float*>(tile + kXMainBytes + g * 64 + b * 4) = sum;
+    auto pack = [&](int lo, int hi) { return (uint32_t)__half_as_ushort(h[lo]) | ((uint32_t)__half_as_ushort(h[hi]) << 16); };
+    if constexpr (FMT == kQ4_K) {
+      // the four chunks of a 32-value scale group sit in four neighbouring lanes
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      // scale group g (low / high nibbles of a 32-byte quarter), core column k8; order inside each
+      // 4-value word [x0, x2, x1, x3] (see TcFormat<kQ4_K>)
+      const int quarter = cc >> 3, nib = (cc >> 2) & 1, i8 = cc & 3;
+      const int g = 2 * quarter + nib;
+      *reinterpret_cast<uint4*>(tile + (4 * g + i8) * 256 + b * 16) = make_uint4(pack(0, 2), pack(1, 3), pack(4, 6), pack(5, 7));
+      if (i8 == 0) *reinterpret_cast<float*>(tile + kXMainBytes + g * 64 + b * 4) = sum;
+    } else {
+      // Q6_K: natural order; a 16-value scale group is two neighbouring chunks
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      *reinterpret_cast<uint4*>(tile + cc * 256 + b * 16) = make_uint4(pack(0, 1), pack(2, 3), pack(4, 5), pack(6, 7));
+      if ((cc & 1) == 0) *reinterpret_cast<float*>(tile + kXMainBytes + (cc >> 1) * 64 + b * 4) = sum;
+    }
   }
+  PREP_WALL(10);
 }
 
 inline long long round_up_ll(long long v, long long to) { return (v + to - 1) / to * to; }
@@ -771,8 +909,36 @@ TB200_DEFINE_STATUS_READER(read_gemv_tc_status)
 void set_peer_wait_limit_ns(unsigned long long ns) { g_peer_wait_limit_ns = ns ? ns : 2000000000ull; }
 unsigned long long peer_wait_limit_ns() { return g_peer_wait_limit_ns; }
 
+static int x_tile_bytes(int fmt) { return fmt == kQ6_K ? TcFormat<kQ6_K>::kXTileBytes : TcFormat<kQ4_K>::kXTileBytes; }
+static int box_bytes(int fmt) { return fmt == kQ6_K ? TcFormat<kQ6_K>::kBoxBytes : TcFormat<kQ4_K>::kBoxBytes; }
+
+#ifdef TB200_TC_TRACE
+static long long* trace_buffer() {
+    static long long* buffer = nullptr;  // device memory: stamps must not wait on a host-memory store
+    if (!buffer) {
+      cudaMalloc((void**)&buffer, 64 * 16 * 8);
+      cudaMemset(buffer, 0, 64 * 16 * 8);
+      atexit([] {
+        static long long host[64 * 16];
+        cudaMemcpy(host, buffer, sizeof(host), cudaMemcpyDeviceToHost);
+        printf("unit: stage free | mma start, issued | warp0 data ready, A stored | acc ready, drained | mma thread: loop top, data seen, A seen, mmas issued\n");
+        const long long t0 = host[3];
+        const long long* w = host + 63 * 16;
+        printf("wall clock (ns after prepare entry): prepare past wait %lld, prepare end %lld | gemv entry %lld, past wait %lld, first data %lld, loop end %lld, segment done %lld, exit %lld\n",
+               w[9] - w[8], w[10] - w[8], w[0] - w[8], w[1] - w[8], w[2] - w[8], w[3] - w[8], w[5] - w[8], w[4] - w[8]);
+        for (int i = 0; i < 63 && host[i * 16 + 3]; ++i) {
+          const long long* h = host + i * 16;
+          printf("%3d: %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld %7lld %7lld\n", i, h[0] ? h[0] - t0 : 0,
+                 h[1] - t0, h[2] - t0, h[3] - t0, h[4] - t0, h[5] - t0, h[6] - t0, h[8] - t0, h[9] - t0, h[10] - t0, h[11] - t0);
+        }
+      });
+    }
+    return buffer;
+}
+#endif
+
 bool gemv_tc_supported(int fmt, int xt, long long m, long long n, long long k) {
-  if (fmt != kQ4_K) return false;
+  if (fmt != kQ4_K && fmt != kQ6_K) return false;
   if (xt != kBF16 && xt != kF16) return false;
   if (m < 1 || m > 16 || n < 1 || k < kUnitK || k % kUnitK) return false;
   if (row_bytes(fmt, k) % 16) return false;
@@ -814,7 +980,7 @@ static bool tc_layout(const TcLaunchItem* items, int count, const DeviceInfo& de
       continue;
     }
     L.x_offset[i] = off;
-    off += round_up_ll(items[i].k / kUnitK * (long long)kXTileBytes, 256);
+    off += round_up_ll(items[i].k / kUnitK * (long long)x_tile_bytes(items[i].fmt), 256);
     L.unscale_offset[i] = off;
     off += 256;
   }
@@ -839,6 +1005,9 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
 
   // ---- activations -> fp16 tiles (one small kernel for the whole list) ----
   PrepArgs prep{};
+#ifdef TB200_TC_TRACE
+  prep.trace = getenv("TB200_TC_NOTRACE") ? nullptr : trace_buffer();
+#endif
   int n_x = 0;
   for (int i = 0; i < count; ++i) {
     if (items[i].x_share >= 0) continue;
@@ -860,8 +1029,13 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = items[0].xt == kF16 ? cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ4_K, true>, prep)
-                            : cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ4_K, false>, prep);
+    const bool f16 = items[0].xt == kF16;
+    if (items[0].fmt == kQ6_K)
+      e = f16 ? cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ6_K, true>, prep)
+              : cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ6_K, false>, prep);
+    else
+      e = f16 ? cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ4_K, true>, prep)
+              : cudaLaunchKernelEx(&cfg, gemv_tc_prepare_kernel<kQ4_K, false>, prep);
     if (e != cudaSuccess) return e;
   }
 
@@ -890,12 +1064,12 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
     tile_base += it.row_tiles;
     const long long rb = row_bytes(src.fmt, src.k);
     if (!make_tensor_map_2d(&p.wmap[i], TmaType::kU64, src.w, (unsigned long long)rb / 8, (unsigned long long)src.n,
-                            (unsigned long long)rb, TcFormat<kQ4_K>::kBoxBytes / 8, kRows, false))
+                            (unsigned long long)rb, box_bytes(src.fmt) / 8, kRows, false))
       return cudaErrorNotSupported;
   }
   p.n_items = count;
   p.total_units = L.total_units;
-  p.stage_bytes = kRows * TcFormat<kQ4_K>::kBoxBytes + kXTileBytes;
+  p.stage_bytes = kRows * box_bytes(items[0].fmt) + x_tile_bytes(items[0].fmt);
   p.red_floats = kParts * max_nb * kRows;
   const int spare = dev->max_smem_optin - kSmemHeader - p.red_floats * 4;
   p.stages = spare / p.stage_bytes;
@@ -913,31 +1087,14 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
     p.sync = peers->flags;
   }
 #ifdef TB200_TC_TRACE
+  p.trace = trace_buffer();
   {
-    static long long* buffer = nullptr;  // device memory: stamps must not wait on a host-memory store
-    if (!buffer) {
-      cudaMalloc((void**)&buffer, 64 * 16 * 8);
-      cudaMemset(buffer, 0, 64 * 16 * 8);
-      atexit([] {
-        static long long host[64 * 16];
-        cudaMemcpy(host, buffer, sizeof(host), cudaMemcpyDeviceToHost);
-        printf("unit: stage free | mma start, issued | warp0 data ready, A stored | acc ready, drained | A stored by warps 5 10 15 13 | data ready warps 5 15\n");
-        const long long t0 = host[3];
-        for (int i = 0; i < 64 && host[i * 16 + 3]; ++i) {
-          const long long* h = host + i * 16;
-          printf("%3d: %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld %7lld %7lld | %7lld %7lld\n", i, h[0] ? h[0] - t0 : 0,
-                 h[1] - t0, h[2] - t0, h[3] - t0, h[4] - t0, h[5] - t0, h[6] - t0, h[8] - t0, h[9] - t0, h[10] - t0, h[11] - t0,
-                 h[12] - t0, h[13] - t0);
-        }
-      });
-    }
-    p.trace = buffer;
     const char* dbg = getenv("TB200_TC_DEBUG");
     p.debug = dbg ? atoi(dbg) : 0;
     if (getenv("TB200_TC_NOTRACE")) p.trace = nullptr;
   }
 #endif
-  auto kernel = gemv_tc_kernel<kQ4_K>;
+  auto kernel = items[0].fmt == kQ6_K ? gemv_tc_kernel<kQ6_K> : gemv_tc_kernel<kQ4_K>;
   e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg{};

@@ -93,6 +93,22 @@ def test_tensor_memory_gemv(m, n, k):
         assert err < 3e-5, err  # operands are exact; only summation order differs
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 2048), (2, 300, 4096), (16, 520, 2048), (5, 4096, 12288)])
+def test_tensor_memory_gemv_q6k(m, n, k):
+    """Q6_K blocks are 2-byte aligned: every block offset inside the staged 16-byte window occurs."""
+    raw = oracle.make_weights("q6_k", n, k, seed=m + n)
+    x = oracle.make_activations(m, k, seed=m + n + 1, dtype="bf16")
+    want = c_oracle.gemv(x, raw, "q6_k", n, k)
+    out = torch.full((m, n), float("nan"), device=dev())
+    lst = ops.GemvList([(to_dev(x, torch.bfloat16), to_dev(raw), "q6_k", n, k, out)], variant="tc")
+    for _ in range(2):
+        out.fill_(float("nan"))
+        lst.launch()
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert oracle.rel_frobenius(got, want) < 3e-5
+
+
 def test_tensor_memory_gemv_f16_activations():
     m, n, k = 4, 256, 1024
     raw = oracle.make_weights("q4_k", n, k, seed=9)
