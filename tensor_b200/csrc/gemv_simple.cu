@@ -12,10 +12,8 @@
 namespace tb200 {
 
 template <int FMT, typename XT, int NB>
-__global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__ x,
-                                                          const uint8_t* __restrict__ w,
-                                                          const OutSpec out, int m,
-                                                          long long n, int k, int weights_bf16) {
+__device__ __forceinline__ void gemv_simple_body(const XT* __restrict__ x, const uint8_t* __restrict__ w,
+                                                 const OutSpec& out, int m, long long n, int k, int weights_bf16) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   const int b0 = blockIdx.y * NB;
@@ -46,6 +44,27 @@ __global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__
     if (lane == 0 && b0 + b < m)
       for (int d = 0; d < out.count; ++d) out.ptr[d][(long long)(b0 + b) * out.ld + row] = v;
   }
+}
+
+// Static-shape entry used by generated .tbin wrappers: the reference's own kernels for this path take
+// fp32 activations and present `kernel(const float* x, const uint8_t* w, float* out)` over flat buffers.
+template <int FMT, typename XT, int NB>
+__device__ __forceinline__ void gemv_simple_static_entry(const XT* x, const uint8_t* w, float* out, int m, long long n,
+                                                         int k) {
+  OutSpec spec{};
+  spec.ptr[0] = out;
+  spec.count = 1;
+  spec.ld = n;
+  gemv_simple_body<FMT, XT, NB>(x, w, spec, m, n, k, 0);
+}
+
+#ifndef TB200_TBIN_WRAPPER
+template <int FMT, typename XT, int NB>
+__global__ void __launch_bounds__(256) gemv_simple_kernel(const XT* __restrict__ x,
+                                                          const uint8_t* __restrict__ w,
+                                                          const OutSpec out, int m,
+                                                          long long n, int k, int weights_bf16) {
+  gemv_simple_body<FMT, XT, NB>(x, w, out, m, n, k, weights_bf16);
 }
 
 // The same arithmetic with everything staged in shared memory first: the CTA converts the
@@ -310,5 +329,7 @@ cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint8_t* w,
   }
   return cudaErrorInvalidValue;
 }
+
+#endif  // TB200_TBIN_WRAPPER
 
 }  // namespace tb200

@@ -183,6 +183,36 @@ kernel_kernel(const void* x, {wparam}, float* out{', unsigned char* scratch' if 
     return manifest
 
 
+def build_gemv_f32_tbin(path: str, encoding, m: int, n: int, k: int) -> dict:
+    """The GEMV with the reference kernels' exact signature and manifest shape for this path:
+    ``kernel_kernel(const float* x, const uint8_t* w, float* out)`` over flat 64-byte aligned buffers
+    ``x: float32 [m*k]``, ``w: uint8 [bytes]``, ``out: float32 [m*n]`` and NO declared outputs (the caller
+    passes all three, as benchmarks/kernels/showcase/benchmark.py:293-295 does).  Any of the four
+    formats, any batch; fp32 weights x fp32 activations, one warp per weight row."""
+    fmt = get_format(encoding)
+    if m < 1 or n < 1:
+        raise ValueError("m and n must be positive")
+    fmt.row_bytes(k)
+    nb = 1 if m == 1 else (4 if m <= 4 else 8)
+    warps = 8
+    grid = ((n + warps - 1) // warps, (m + nb - 1) // nb, 1)
+    source = f"""// generated by tensor_b200.tbin: {fmt.name} GEMV with fp32 activations, m={m}, n={n}, k={k}
+#define TB200_TBIN_WRAPPER
+#include "gemv_simple.cu"
+extern "C" __global__ void __launch_bounds__({warps * 32})
+kernel_kernel(const float* x, const uint8_t* w, float* out) {{
+  tb200::gemv_simple_static_entry<{fmt.type_id}, float, {nb}>(x, w, out, {m}, {n}LL, {k});
+}}
+"""
+    cubin = compile_cubin(source)
+    arguments = [_buffer("x", "float32", (m * k,)), _buffer("w", "uint8", (fmt.weight_bytes(n, k),)),
+                 _buffer("out", "float32", (m * n,))]
+    manifest = make_manifest(grid=grid, block=(warps * 32, 1, 1), shared_memory_bytes=0, arguments=arguments,
+                             outputs=[], source=source.encode())
+    write_tbin(path, manifest, cubin)
+    return manifest
+
+
 def build_gemm_tbin(path: str, encoding, m: int, n: int, k: int) -> dict:
     """Prefill GEMM (tcgen05, bf16 operands) as a static-shape artifact: arguments ``x, w, out``;
     ``x`` is consumed through a TMA descriptor the runtime encodes from ``cuda_tensor_maps``."""

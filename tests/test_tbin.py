@@ -139,3 +139,32 @@ def test_gemm_artifact_runs_like_the_provider_would(tmp_path, name):
     got = bufs["out"].cpu().numpy()
     assert np.isfinite(got).all()
     assert oracle.rel_frobenius(got, c_oracle.gemm(x, raw, name, n, k, operand="bf16")) < 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,m,n,k", [("q4_k", 1, 512, 1024), ("q6_k", 1, 300, 512), ("q8_0", 3, 256, 512), ("q4_0", 9, 64, 256)])
+def test_f32_signature_artifact_runs_like_the_provider_would(tmp_path, name, m, n, k):
+    """``kernel_kernel(const float* x, const uint8_t* w, float* out)`` over flat buffers, the signature the
+    reference's own kernels for this path present (no declared outputs: the caller passes all three)."""
+    import torch
+
+    from oracle import c_oracle
+    from oracle import gguf_oracle as oracle
+    from tbin_runner import TbinKernel
+
+    dev = torch.device("cuda", 0)
+    torch.zeros(1, device=dev)
+    path = str(tmp_path / "f32.tbin")
+    manifest = tbin.build_gemv_f32_tbin(path, name, m, n, k)
+    assert manifest["outputs"] == []
+    kern = TbinKernel(path)
+    raw = oracle.make_weights(name, n, k, seed=5)
+    x = oracle.make_activations(m, k, seed=6, dtype="f32")
+    bufs = {"x": torch.from_numpy(x).to(dev).reshape(-1), "w": torch.from_numpy(raw).to(dev),
+            "out": torch.full((m * n,), float("nan"), device=dev)}
+    keep = kern.launch(torch.cuda.current_stream().cuda_stream, **bufs)
+    torch.cuda.synchronize()
+    del keep
+    got = bufs["out"].cpu().numpy().reshape(m, n)
+    assert np.isfinite(got).all()
+    assert oracle.rel_frobenius(got, c_oracle.gemv(x, raw, name, n, k)) < 1e-3
