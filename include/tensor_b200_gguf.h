@@ -117,11 +117,39 @@ int64_t tb200_gguf_gemv_scratch_bytes(int32_t format, int64_t m, int64_t n, int6
 /* The launch plan the pipelined GEMV would use with `scratch_bytes` of scratch available:
  * plan_out[0..7] = {covered by the pipelined kernel (0/1), CTAs along K, CTAs along N,
  * 256-weight super-blocks per K range, ring stages, dynamic shared memory bytes, scratch bytes
- * needed, CTAs per SM}.  Without a CUDA device the plan is made for a B200 (148 SMs).  Plays the
- * role of the reference's schedule dictionaries (src/tensor/compiler/cuda/schedules.py:3-52),
- * except that the schedule is derived from the shape instead of searched. */
+ * needed, CTAs per SM}.  Without a CUDA device the plan is made for a B200 (148 SMs).  This is the
+ * schedule the library derives (or the one recorded for the shape); TB200Schedule below pins one. */
 int32_t tb200_gguf_gemv_plan(int32_t format, int64_t m, int64_t n, int64_t k, int64_t scratch_bytes,
                              int32_t *plan_out);
+
+/* A schedule: the launch choices of the pipelined kernels that a caller may pin; a zero field means
+ * "let the library derive it".  This is the counterpart of the reference's schedule dictionaries and
+ * their legality predicate (src/tensor/compiler/cuda/schedules.py:3-52) for kernels that are written by
+ * hand instead of generated: tb200_gguf_schedule_legal answers whether a schedule can run at a shape,
+ * tb200_gguf_*_scheduled runs it, tb200_gguf_schedule_record makes it the default for that exact shape
+ * in this process (what a search stores in its profile; src/tensor/compiler/search.py:29-159). */
+#define TB200_OP_GEMV 1
+#define TB200_OP_GEMM 2
+typedef struct TB200Schedule {
+  int32_t k_splits;      /* GEMV: CTAs along K per 16-row tile (1 .. 64) */
+  int32_t ctas_per_sm;   /* GEMV: 1 (up to 16 decode warps) or 2 (8 decode warps each) */
+  int32_t convert_ahead; /* GEMV, m > 1: 1 = activations converted by a kernel ahead of the GEMV (needs scratch), 2 = by every CTA */
+  int32_t overlap;       /* 1 = the launch may start while its predecessor drains (default), 2 = fully serialized */
+  int32_t gemm_shape;    /* GEMM: 11, 12 or 22 = <256-token tiles per CTA, decode warp groups> */
+  int32_t reserved[3];
+} TB200Schedule;
+int32_t tb200_gguf_schedule_legal(int32_t op, int32_t format, int64_t m, int64_t n, int64_t k,
+                                  int64_t scratch_bytes, const TB200Schedule *schedule);
+int32_t tb200_gguf_schedule_record(int32_t op, int32_t format, int64_t m, int64_t n, int64_t k,
+                                   const TB200Schedule *schedule);
+void tb200_gguf_schedule_clear(void);
+/* The pipelined GEMV / the tcgen05 GEMM with a pinned schedule; status 2 if it is not legal at the shape. */
+int32_t tb200_gguf_gemv_scheduled(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
+                                  int64_t m, int64_t n, int64_t k, void *scratch, int64_t scratch_bytes,
+                                  const TB200Schedule *schedule, void *stream, TensorErrorV1 *error);
+int32_t tb200_gguf_gemm_scheduled(int32_t format, int32_t x_dtype, const void *x, const void *w, float *out,
+                                  int64_t m, int64_t n, int64_t k, const TB200Schedule *schedule, void *stream,
+                                  TensorErrorV1 *error);
 
 /* Launch constants for packaging a static-shape kernel as a `.tbin` artifact of the reference
  * (src/tensor/artifacts/format.py), planned for a B200: the reference's provider launches with the

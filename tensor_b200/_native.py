@@ -20,6 +20,8 @@ EXPORTS = (
     "tb200_peer_sync", "tb200_gguf_gemv_pair", "tb200_gguf_gemv_pair_sharded_sync",
     "tb200_peer_export", "tb200_peer_open", "tb200_peer_close",
     "tb200_gguf_gemv_list", "tb200_gguf_gemv_list_scratch_bytes", "tb200_peer_set_wait_limit",
+    "tb200_gguf_schedule_legal", "tb200_gguf_schedule_record", "tb200_gguf_schedule_clear",
+    "tb200_gguf_gemv_scheduled", "tb200_gguf_gemm_scheduled",
 )
 
 
@@ -100,6 +102,16 @@ def lib():
     handle.tb200_gguf_gemv_list.restype = i32
     handle.tb200_gguf_gemv_list.argtypes = [ctypes.POINTER(abi.TB200GemvItem), i32, vp, i64, i32, ctypes.POINTER(vp),
                                             i32, i32, i32, vp, err]
+    sched = ctypes.POINTER(abi.TB200Schedule)
+    handle.tb200_gguf_schedule_legal.restype = i32
+    handle.tb200_gguf_schedule_legal.argtypes = [i32, i32, i64, i64, i64, i64, sched]
+    handle.tb200_gguf_schedule_record.restype = i32
+    handle.tb200_gguf_schedule_record.argtypes = [i32, i32, i64, i64, i64, sched]
+    handle.tb200_gguf_schedule_clear.restype = None
+    handle.tb200_gguf_gemv_scheduled.restype = i32
+    handle.tb200_gguf_gemv_scheduled.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, vp, i64, sched, vp, err]
+    handle.tb200_gguf_gemm_scheduled.restype = i32
+    handle.tb200_gguf_gemm_scheduled.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, sched, vp, err]
     handle.tb200_peer_set_wait_limit.restype = i32
     handle.tb200_peer_set_wait_limit.argtypes = [ctypes.c_uint64]
     handle.tb200_gguf_gemm.restype = i32

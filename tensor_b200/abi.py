@@ -54,6 +54,12 @@ class TB200GemvItem(ctypes.Structure):
                 ("n", ctypes.c_int64), ("k", ctypes.c_int64)]
 
 
+class TB200Schedule(ctypes.Structure):
+    """Pinned launch choices (include/tensor_b200_gguf.h); zero fields are derived by the library."""
+    _fields_ = [("k_splits", ctypes.c_int32), ("ctas_per_sm", ctypes.c_int32), ("convert_ahead", ctypes.c_int32),
+                ("overlap", ctypes.c_int32), ("gemm_shape", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+
+
 assert ctypes.sizeof(TensorBufferV1) == 48
 assert ctypes.sizeof(TensorArgumentV1) == 64
 assert ctypes.sizeof(TensorStreamV1) == 16

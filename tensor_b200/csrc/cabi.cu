@@ -58,6 +58,37 @@ const DeviceInfo* device_info(cudaError_t* err) {
   return &d;
 }
 
+namespace {
+struct ScheduleEntry {
+  int op, fmt;
+  long long m, n, k;
+  Schedule schedule;
+};
+std::mutex g_schedule_lock;
+std::vector<ScheduleEntry> g_schedules;  // entries are never moved once handed out: see record_schedule
+}  // namespace
+
+const Schedule* lookup_schedule(int op, int fmt, long long m, long long n, long long k) {
+  std::lock_guard<std::mutex> guard(g_schedule_lock);
+  for (const ScheduleEntry& e : g_schedules)
+    if (e.op == op && e.fmt == fmt && e.m == m && e.n == n && e.k == k) return &e.schedule;
+  return nullptr;
+}
+void record_schedule(int op, int fmt, long long m, long long n, long long k, const Schedule& s) {
+  std::lock_guard<std::mutex> guard(g_schedule_lock);
+  for (ScheduleEntry& e : g_schedules)
+    if (e.op == op && e.fmt == fmt && e.m == m && e.n == n && e.k == k) {
+      e.schedule = s;
+      return;
+    }
+  if (g_schedules.capacity() == 0) g_schedules.reserve(4096);  // pointers handed out by lookup stay valid
+  if (g_schedules.size() < g_schedules.capacity()) g_schedules.push_back(ScheduleEntry{op, fmt, m, n, k, s});
+}
+void clear_schedules() {
+  std::lock_guard<std::mutex> guard(g_schedule_lock);
+  for (ScheduleEntry& e : g_schedules) e.schedule = Schedule{};  // entries stay in place; "derive everything"
+}
+
 cudaError_t allow_full_shared_memory(const void* kernel) {
   static std::mutex lock;
   static std::vector<std::pair<const void*, int>> done;  // (kernel, device) pairs already opted in
@@ -272,7 +303,7 @@ namespace {
 // Shared by the plain and the sharded entry points: `out` says where the [m, n] result goes.
 int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* w, const OutSpec& out, int64_t m,
                     int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
-                    TensorErrorV1* error, const PeerSync* peers = nullptr) {
+                    TensorErrorV1* error, const PeerSync* peers = nullptr, const Schedule* sched = nullptr) {
   if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
   if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
   for (int i = 0; i < out.count; ++i)
@@ -313,12 +344,17 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
                 (long long)(scratch ? scratch_bytes : 0));
   }
   if (variant != TB200_VARIANT_SIMPLE) {
-    GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev);
+    GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev, true, sched);
     if (plan.supported) {
       cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch", e);
       return ok(error);
     }
+    if (sched)
+      return fail(error, TENSOR_ERROR_ARGUMENT,
+                  "the schedule {k_splits %d, ctas_per_sm %d, convert_ahead %d} is not legal for format %d, m=%lld, "
+                  "n=%lld, k=%lld with %lld bytes of scratch", sched->k_splits, sched->ctas_per_sm, sched->convert_ahead,
+                  format, (long long)m, (long long)n, (long long)k, (long long)(scratch ? scratch_bytes : 0));
     if (variant == TB200_VARIANT_FAST || variant == TB200_VARIANT_MMA)
       return fail(error, TENSOR_ERROR_ARGUMENT,
                   "the pipelined GEMV does not cover format %d, dtype %d, m=%lld, n=%lld, k=%lld", format, x_dtype,
@@ -625,8 +661,85 @@ int32_t tb200_peer_close(void* base, TensorErrorV1* error) {
   return ok(error);
 }
 
+}  // extern "C"
+
+namespace {
+Schedule to_schedule(const TB200Schedule* in) {
+  Schedule s;
+  if (in) {
+    s.k_splits = in->k_splits;
+    s.ctas_per_sm = in->ctas_per_sm;
+    s.convert_ahead = in->convert_ahead;
+    s.overlap = in->overlap;
+    s.gemm_shape = in->gemm_shape;
+  }
+  return s;
+}
+int32_t gemm_common(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m, int64_t n,
+                    int64_t k, int32_t variant, void* stream, TensorErrorV1* error, const Schedule* sched);
+}  // namespace
+
+extern "C" {
+
 int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
                         int64_t n, int64_t k, int32_t variant, void* stream, TensorErrorV1* error) {
+  return gemm_common(format, x_dtype, x, w, out, m, n, k, variant, stream, error, nullptr);
+}
+
+int32_t tb200_gguf_gemm_scheduled(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
+                                  int64_t n, int64_t k, const TB200Schedule* schedule, void* stream,
+                                  TensorErrorV1* error) {
+  if (!schedule) return fail(error, TENSOR_ERROR_ARGUMENT, "schedule is null");
+  const Schedule s = to_schedule(schedule);
+  return gemm_common(format, x_dtype, x, w, out, m, n, k, TB200_VARIANT_FAST, stream, error, &s);
+}
+
+int32_t tb200_gguf_gemv_scheduled(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m,
+                                  int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
+                                  const TB200Schedule* schedule, void* stream, TensorErrorV1* error) {
+  if (!schedule) return fail(error, TENSOR_ERROR_ARGUMENT, "schedule is null");
+  if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n, k, TB200_VARIANT_FAST)) return s;
+  if (m == 0 || n == 0) return ok(error);
+  const Schedule s = to_schedule(schedule);
+  return gemv_common(format, x_dtype, x, w, single_output(out, n), m, n, k, scratch, scratch_bytes, TB200_VARIANT_MMA,
+                     stream, error, nullptr, &s);
+}
+
+int32_t tb200_gguf_schedule_legal(int32_t op, int32_t format, int64_t m, int64_t n, int64_t k, int64_t scratch_bytes,
+                                  const TB200Schedule* schedule) {
+  if (!schedule || !valid_format(format) || m < 1 || n < 1 || k < 1 || k % block_weights(format)) return 0;
+  DeviceInfo b200;  // without a device, judge legality for a B200
+  b200.ordinal = 0;
+  b200.sm_count = 148;
+  b200.max_smem_optin = 232448;
+  b200.cc_major = 10;
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) {
+    cudaGetLastError();
+    dev = &b200;
+  }
+  const Schedule s = to_schedule(schedule);
+  if (s.overlap < 0 || s.overlap > 2 || s.convert_ahead < 0 || s.convert_ahead > 2) return 0;
+  if (op == TB200_OP_GEMV) return plan_gemv_fast(format, kBF16, m, n, k, scratch_bytes, *dev, true, &s).supported ? 1 : 0;
+  if (op == TB200_OP_GEMM) return gemm_fast_supported(format, m, n, k, *dev) && gemm_shape_legal(s.gemm_shape, m, *dev) ? 1 : 0;
+  return 0;
+}
+
+int32_t tb200_gguf_schedule_record(int32_t op, int32_t format, int64_t m, int64_t n, int64_t k,
+                                   const TB200Schedule* schedule) {
+  if ((op != TB200_OP_GEMV && op != TB200_OP_GEMM) || !valid_format(format)) return TENSOR_ERROR_ARGUMENT;
+  record_schedule(op, format, m, n, k, to_schedule(schedule));
+  return TENSOR_OK;
+}
+
+void tb200_gguf_schedule_clear(void) { clear_schedules(); }
+
+}  // extern "C"
+
+namespace {
+int32_t gemm_common(int32_t format, int32_t x_dtype, const void* x, const void* w, float* out, int64_t m, int64_t n,
+                    int64_t k, int32_t variant, void* stream, TensorErrorV1* error, const Schedule* sched) {
   if (int32_t s = check_shape(error, format, m, n, k)) return s;
   if (x_dtype != TENSOR_BFLOAT16)
     return fail(error, TENSOR_ERROR_ARGUMENT, "the GEMM takes bfloat16 activations (dtype 13), got %d", x_dtype);
@@ -642,7 +755,9 @@ int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void* x, const vo
   if (variant != TB200_VARIANT_SIMPLE) {
     if (gemm_fast_supported(format, m, n, k, *dev)) {
       const char* detail = "";
-      cudaError_t e = launch_gemm_fast(format, x, wp, out, m, n, k, st, &detail);
+      if (sched && !gemm_shape_legal(sched->gemm_shape, m, *dev))
+        return fail(error, TENSOR_ERROR_ARGUMENT, "GEMM shape %d is not legal on this device", sched->gemm_shape);
+      cudaError_t e = launch_gemm_fast(format, x, wp, out, m, n, k, st, &detail, sched);
       if (e != cudaSuccess) return cuda_fail(error, detail && *detail ? detail : "tcgen05 GEMM launch", e);
       return ok(error);
     }
@@ -654,6 +769,9 @@ int32_t tb200_gguf_gemm(int32_t format, int32_t x_dtype, const void* x, const vo
   if (e != cudaSuccess) return cuda_fail(error, "GEMM launch", e);
   return ok(error);
 }
+}  // namespace
+
+extern "C" {
 
 namespace {
 int32_t check_list(TensorErrorV1* error, const TB200GemvItem* items, int32_t count) {

@@ -18,8 +18,6 @@
 // decode / epilogue overlaps the other's MMAs.
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -449,17 +447,13 @@ cudaError_t launch_shape(const CUtensorMap& tmap, const uint8_t* w, float* out, 
   return cudaGetLastError();
 }
 
-// TB200_GEMM_SHAPE=11|12|22 pins <token tiles, decode groups> (tuning experiments); otherwise 512
-// tokens per tile above M = 256 and one 256-token CTA with two decode groups up to there.
+// <token tiles, decode groups>: 512 tokens per tile above M = 256 and one 256-token CTA with two
+// decode groups up to there, unless a schedule pins the shape (11, 12 or 22).
 template <int FMT>
 cudaError_t launch_fmt(const CUtensorMap& tmap, const uint8_t* w, float* out, long long m, long long n,
-                       long long k, cudaStream_t stream, bool big_ok) {
-  static const int forced = [] {
-    const char* v = getenv("TB200_GEMM_SHAPE");
-    return v ? atoi(v) : 0;
-  }();
+                       long long k, cudaStream_t stream, bool big_ok, int pinned) {
   int shape = !big_ok ? 11 : (m > 256 ? 22 : 12);
-  if (forced == 11 || (big_ok && (forced == 12 || forced == 22))) shape = forced;
+  if (pinned == 11 || (big_ok && (pinned == 12 || pinned == 22))) shape = pinned;
   if (shape == 22) return launch_shape<FMT, 2, 2>(tmap, w, out, m, n, k, stream);
   if (shape == 12) return launch_shape<FMT, 1, 2>(tmap, w, out, m, n, k, stream);
   return launch_shape<FMT, 1, 1>(tmap, w, out, m, n, k, stream);
@@ -496,8 +490,15 @@ bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const D
   return dev.max_smem_optin >= kSmemBytes;
 }
 
+bool gemm_shape_legal(int shape, long long, const DeviceInfo& dev) {
+  if (shape == 0 || shape == 11) return true;
+  return (shape == 12 || shape == 22) && dev.max_smem_optin >= Cfg<2, 2>::kSmemBytes;
+}
+
 cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m, long long n,
-                             long long k, cudaStream_t stream, const char** detail) {
+                             long long k, cudaStream_t stream, const char** detail, const Schedule* sched) {
+  if (!sched) sched = lookup_schedule(kOpGemm, fmt, m, n, k);
+  const int pinned = sched ? sched->gemm_shape : 0;
   // x as a 2-D tensor [m rows, k columns] of bf16; box = 64 columns (128 bytes) x 256 rows,
   // 128-byte swizzle, rows past m read as zero.
   alignas(64) CUtensorMap tmap;
@@ -511,8 +512,8 @@ cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* ou
   cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   const bool wide_ok = optin >= Cfg<2, 2>::kSmemBytes;
   switch (fmt) {
-    case kQ4_K: return launch_fmt<kQ4_K>(tmap, w, out, m, n, k, stream, wide_ok);
-    case kQ6_K: return launch_fmt<kQ6_K>(tmap, w, out, m, n, k, stream, wide_ok);
+    case kQ4_K: return launch_fmt<kQ4_K>(tmap, w, out, m, n, k, stream, wide_ok, pinned);
+    case kQ6_K: return launch_fmt<kQ6_K>(tmap, w, out, m, n, k, stream, wide_ok, pinned);
   }
   return cudaErrorInvalidValue;
 }

@@ -1194,8 +1194,12 @@ __device__ __forceinline__ void gemv_static_entry(const GemvStatic& s, const voi
 TB200_DEFINE_STATUS_READER(read_gemv_status)
 
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
-                        long long scratch_bytes_available, const DeviceInfo& dev, bool allow_prep) {
+                        long long scratch_bytes_available, const DeviceInfo& dev, bool allow_prep,
+                        const Schedule* sched) {
   GemvPlan best;
+  if (!sched) sched = lookup_schedule(kOpGemv, fmt, m, n, k);
+  const Schedule none{};
+  if (!sched) sched = &none;
   if (fmt != kQ4_K) return best;
   if (xt != kBF16 && xt != kF16) return best;
   if (m < 1 || m > 16 || n < 1 || k < 256 || k % 256 || k > (1 << 24)) return best;
@@ -1209,16 +1213,11 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
   const long long prep_x_bytes = (m * k * 2 + 255) / 256 * 256;
   // (measured at batch 4 and 8 as well: the extra launch, which starts while the previous kernel
   // drains, costs less than every CTA converting its K range: 48.6 -> 46.9 us for gate+up and down)
-  static const int prep_min = [] {  // TB200_GEMV_PREP_MIN: smallest batch that uses it (tuning experiments)
-    const char* v = getenv("TB200_GEMV_PREP_MIN");
-    return v ? atoi(v) : 2;
-  }();
-  const long long prep_bytes = (allow_prep && m >= prep_min && m > 1) ? prep_x_bytes + ((k / 32) * ntb * 8 + 255) / 256 * 256 : 0;
+  const bool ahead = allow_prep && m > 1 && sched->convert_ahead != 2;
+  const long long prep_bytes = ahead ? prep_x_bytes + ((k / 32) * ntb * 8 + 255) / 256 * 256 : 0;
   double best_cost = 1e300;
-  // TB200_GEMV_FORCE="<k splits>:<CTAs per SM>" pins the plan search (tuning experiments only).
-  static const char* forced = getenv("TB200_GEMV_FORCE");
-  int force_splits = 0, force_per_sm = 0;
-  if (forced) sscanf(forced, "%d:%d", &force_splits, &force_per_sm);
+  const int force_splits = sched->k_splits, force_per_sm = sched->ctas_per_sm;
+  if (force_splits < 0 || force_per_sm < 0 || force_per_sm > 2) return best;
   // Two CTAs per SM hide each other's barriers and reductions when the shared memory allows it.
   for (int per_sm = 2; per_sm >= 1; --per_sm) {
     if (force_per_sm && per_sm != force_per_sm) continue;
@@ -1282,23 +1281,41 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
         best.ctas_per_sm = per_sm;
         best.consumer_warps = warps;
         best.red_bufs = red_bufs;
+        best.overlap = sched->overlap == 2 ? 0 : 1;
       }
     }
   }
+  // a caller that asked for conversion ahead of the launch must have got it
+  if (best.supported && sched->convert_ahead == 1 && m > 1 && !best.prep_x_offset) best.supported = false;
   return best;
 }
 
-// TB200_GEMV_NO_OVERLAP=1 in the environment launches every GEMV fully serialized (for A/B timing).
-static bool overlap_launches() {
-  static const bool on = [] {
-    const char* v = getenv("TB200_GEMV_NO_OVERLAP");
-    return !(v && *v && *v != '0');
-  }();
-  return on;
+#ifdef TB200_GEMV_TRACE
+// Trace builds: a pinned host buffer the traced CTAs stamp, printed when the process exits.
+static unsigned long long* gemv_trace_buffer() {
+    static unsigned long long* host = nullptr;
+    if (!host) {
+      cudaHostAlloc((void**)&host, 80 * 8 * 8, cudaHostAllocMapped);
+      memset(host, 0, 80 * 8 * 8);
+      atexit([] {
+        for (int c = 0; c < 3; ++c) {
+          const unsigned long long* d = host + c * 80;
+          if (!d[0]) continue;
+          printf("trace cta %d (start %llu): dependency resolved +%llu ns, activations landed +%llu ns, staged +%llu ns; conversion rounds at +%llu +%llu +%llu +%llu; last warp out +%llu\n",
+                 c * 100, d[0] % 1000000ull, d[7] ? d[7] - d[0] : 0ull, d[2] ? d[2] - d[0] : 0ull, d[1] - d[0], d[3] - d[0], d[4] - d[0], d[5] - d[0], d[6] - d[0],
+                 d[72] ? d[72] - d[0] : 0ull);
+          for (int i = 0; i < 16 && d[8 + i]; ++i)
+            printf("  tile %2d: copy issued +%6llu  data ready +%6llu  decoded +%6llu  reduced +%6llu\n", i,
+                   d[56 + i] - d[0], d[8 + i] - d[0], d[24 + i] - d[0], d[40 + i] - d[0]);
+        }
+      });
+    }
+    return host;
 }
+#endif
 
 template <int FMT, bool F16, int NT, bool GROUPS, bool WIDE>
-static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t stream) {
+static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t stream, bool overlap) {
   auto kernel = gemv_mma_kernel<FMT, F16, NT, GROUPS, WIDE>;
   cudaError_t e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
@@ -1323,7 +1340,7 @@ static cudaError_t launch_variant(GemvArgs& a, int grid, int smem, cudaStream_t 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  cfg.numAttrs = overlap ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, a, wmap);
 }
 
@@ -1379,26 +1396,7 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     }
   }
 #ifdef TB200_GEMV_TRACE
-  {
-    static unsigned long long* host = nullptr;
-    if (!host) {
-      cudaHostAlloc((void**)&host, 80 * 8 * 8, cudaHostAllocMapped);
-      memset(host, 0, 80 * 8 * 8);
-      atexit([] {
-        for (int c = 0; c < 3; ++c) {
-          const unsigned long long* d = host + c * 80;
-          if (!d[0]) continue;
-          printf("trace cta %d (start %llu): dependency resolved +%llu ns, activations landed +%llu ns, staged +%llu ns; conversion rounds at +%llu +%llu +%llu +%llu; last warp out +%llu\n",
-                 c * 100, d[0] % 1000000ull, d[7] ? d[7] - d[0] : 0ull, d[2] ? d[2] - d[0] : 0ull, d[1] - d[0], d[3] - d[0], d[4] - d[0], d[5] - d[0], d[6] - d[0],
-                 d[72] ? d[72] - d[0] : 0ull);
-          for (int i = 0; i < 16 && d[8 + i]; ++i)
-            printf("  tile %2d: copy issued +%6llu  data ready +%6llu  decoded +%6llu  reduced +%6llu\n", i,
-                   d[56 + i] - d[0], d[8 + i] - d[0], d[24 + i] - d[0], d[40 + i] - d[0]);
-        }
-      });
-    }
-    a.trace = host;
-  }
+  a.trace = gemv_trace_buffer();
 #endif
   if (plan.k_splits > 1) {
     if (!scratch) return cudaErrorInvalidValue;
@@ -1420,7 +1418,7 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = overlap_launches() ? 1 : 0;
+    cfg.numAttrs = plan.overlap ? 1 : 0;
     const uint16_t* xin = static_cast<const uint16_t*>(x);
     cudaError_t e = xt == kF16
                         ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m, (int)k, ntb)
@@ -1434,10 +1432,10 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
   const bool f16 = xt == kF16;
   const bool wide = plan.ctas_per_sm == 1;
 #define TB200_GEMV_DISPATCH(NT, GROUPS)                                                                    \
-  (f16 ? (wide ? launch_variant<kQ4_K, true, NT, GROUPS, true>(a, grid, smem_total, stream)                \
-               : launch_variant<kQ4_K, true, NT, GROUPS, false>(a, grid, smem_total, stream))              \
-       : (wide ? launch_variant<kQ4_K, false, NT, GROUPS, true>(a, grid, smem_total, stream)               \
-               : launch_variant<kQ4_K, false, NT, GROUPS, false>(a, grid, smem_total, stream)))
+  (f16 ? (wide ? launch_variant<kQ4_K, true, NT, GROUPS, true>(a, grid, smem_total, stream, plan.overlap != 0)   \
+               : launch_variant<kQ4_K, true, NT, GROUPS, false>(a, grid, smem_total, stream, plan.overlap != 0)) \
+       : (wide ? launch_variant<kQ4_K, false, NT, GROUPS, true>(a, grid, smem_total, stream, plan.overlap != 0)  \
+               : launch_variant<kQ4_K, false, NT, GROUPS, false>(a, grid, smem_total, stream, plan.overlap != 0)))
   if (m == 1) return TB200_GEMV_DISPATCH(1, true);
   if (m <= 8) return TB200_GEMV_DISPATCH(1, false);
   return TB200_GEMV_DISPATCH(2, false);

@@ -60,6 +60,22 @@ inline cudaError_t launch_gemv_simple(int fmt, int xt, const void* x, const uint
   return launch_gemv_simple(fmt, xt, x, w, single_output(out, n), m, n, k, weights_bf16, stream);
 }
 
+// A schedule: the launch choices a caller may pin instead of letting the library derive them.  Zero in
+// a field means "derive".  Plays the role of the reference's schedule dictionaries
+// (src/tensor/compiler/cuda/schedules.py:3-52).
+struct Schedule {
+  int k_splits = 0;       // GEMV: CTAs along K per row tile
+  int ctas_per_sm = 0;    // GEMV: 1 or 2
+  int convert_ahead = 0;  // GEMV, m > 1: 1 = activations converted by a kernel ahead of the GEMV, 2 = by every CTA
+  int overlap = 0;        // 1 = launch with programmatic stream serialization (default), 2 = fully serialized
+  int gemm_shape = 0;     // GEMM: 11, 12 or 22 = <256-token tiles per CTA, decode warp groups>
+};
+// Schedules recorded for a shape (by a search) that the default entry points consult; nullptr if none.
+enum ScheduleOp : int { kOpGemv = 1, kOpGemm = 2 };
+const Schedule* lookup_schedule(int op, int fmt, long long m, long long n, long long k);
+void record_schedule(int op, int fmt, long long m, long long n, long long k, const Schedule& s);
+void clear_schedules();
+
 // Bulk-copy pipeline + mma.sync GEMV for m <= 16.
 struct GemvPlan {
   bool supported = false;
@@ -79,9 +95,13 @@ struct GemvPlan {
   // CTAs convert on their own.
   long long prep_x_offset = 0;
   long long prep_table_offset = 0;
+  int overlap = 1;  // 1: the launch may start while its predecessor drains (programmatic dependent launch)
 };
+// sched: pinned choices (nullptr: the schedule recorded for the shape, else derived).  A pinned choice
+// that is not legal at the shape (shared memory, scratch, empty K ranges) yields supported == false.
 GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
-                        long long scratch_bytes_available, const DeviceInfo& dev, bool allow_prep = true);
+                        long long scratch_bytes_available, const DeviceInfo& dev, bool allow_prep = true,
+                        const Schedule* sched = nullptr);
 // All launch constants of a plan (grid, threads, shared memory, ring layout ...): see tbin.py.
 bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n, long long k, int* out32);
 // Cross-GPU ordering folded into a GEMV launch (N-sharded runs): pads[i] is rank i's signal pad as
@@ -142,7 +162,9 @@ cudaError_t launch_peer_barrier(unsigned int* const* pads, int rank, int world, 
 void gemm_launch_config(long long m, long long n, int* out8);
 bool gemm_fast_supported(int fmt, long long m, long long n, long long k, const DeviceInfo& dev);
 cudaError_t launch_gemm_fast(int fmt, const void* x, const uint8_t* w, float* out, long long m,
-                             long long n, long long k, cudaStream_t stream, const char** detail);
+                             long long n, long long k, cudaStream_t stream, const char** detail,
+                             const Schedule* sched = nullptr);
+bool gemm_shape_legal(int shape, long long m, const DeviceInfo& dev);
 
 // 2-D tiled TMA tensor map (128 bytes, 64-byte aligned) over a row-major matrix; elements are bf16
 // or opaque 8-byte words.  Returns false if the driver entry point is unavailable or rejects it.
