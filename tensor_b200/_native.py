@@ -121,7 +121,24 @@ def lib():
         fn.restype = i32
         fn.argtypes = [call, err]
     _lib = handle
+    _apply_shipped_schedules()
     return _lib
+
+
+def _apply_shipped_schedules() -> None:
+    """Schedules found by a measured search on a B200 (``tensor_b200.schedule.search``) for shapes where
+    the derived plan is not the fastest; recorded so that the ordinary entry points use them."""
+    import json
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "schedules_b200.json")
+    if not os.path.exists(path):
+        return
+    from . import schedule
+
+    with open(path) as f:
+        entries = json.load(f).get("entries", [])
+    for e in entries:
+        schedule.record(e["op"], e["format"], e["m"], e["n"], e["k"], e["best"])
 
 
 def raise_for_status(status: int, error: abi.TensorErrorV1) -> None:

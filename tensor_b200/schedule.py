@@ -79,6 +79,7 @@ def record(op: str, encoding, m: int, n: int, k: int, config: dict) -> None:
 
 
 def clear() -> None:
+    """Forget every recorded schedule (the shipped ones included): everything is derived again."""
     lib().tb200_gguf_schedule_clear()
 
 
