@@ -285,6 +285,20 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem *items, int32_t count, void *sc
                              int64_t scratch_bytes, int32_t variant, uint32_t *const *pads, int32_t rank,
                              int32_t world, int32_t sync, void *stream, TensorErrorV1 *error);
 
+/* The steps either side of a decode projection, launched so that they chain with the GEMVs without a gap
+ * (programmatic dependent launch): RMS normalisation of the fp32 residual stream into the bf16
+ * activations of the next projection, SwiGLU of the fp32 [m, 2 * width] output of a grouped gate + up launch
+ * into the bf16 activations of the down projection, and the residual add behind a projection.  The
+ * reference states these as generated kernels (packages/tensor-nn/src/tensor_nn/kernels/normalization.py)
+ * or matmul epilogues (tensor_nn/kernels/linear.py:6-100).  Pointers 16-byte aligned, k / width / count
+ * multiples of 4. */
+int32_t tb200_rmsnorm_bf16(const float *x, const float *weight, void *out_bf16, int64_t m, int64_t k, float eps,
+                           void *stream, TensorErrorV1 *error);
+int32_t tb200_swiglu_bf16(const float *gate_up, void *out_bf16, int64_t m, int64_t width, void *stream,
+                          TensorErrorV1 *error);
+int32_t tb200_residual_add(float *stream_buffer, const float *delta, int64_t count, void *stream,
+                           TensorErrorV1 *error);
+
 /* How long a kernel of this library waits for another GPU's signal before it gives up, records
  * 0x80000 | peer (GEMV) or 0x90000 | peer (barrier) in the status word and returns; 0 restores the
  * default of two seconds.  Process-wide; applies to launches made after the call.  A rank whose wait

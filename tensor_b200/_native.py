@@ -22,6 +22,7 @@ EXPORTS = (
     "tb200_gguf_gemv_list", "tb200_gguf_gemv_list_scratch_bytes", "tb200_peer_set_wait_limit",
     "tb200_gguf_schedule_legal", "tb200_gguf_schedule_record", "tb200_gguf_schedule_clear",
     "tb200_gguf_gemv_scheduled", "tb200_gguf_gemm_scheduled",
+    "tb200_rmsnorm_bf16", "tb200_swiglu_bf16", "tb200_residual_add",
 )
 
 
@@ -112,6 +113,12 @@ def lib():
     handle.tb200_gguf_gemv_scheduled.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, vp, i64, sched, vp, err]
     handle.tb200_gguf_gemm_scheduled.restype = i32
     handle.tb200_gguf_gemm_scheduled.argtypes = [i32, i32, vp, vp, vp, i64, i64, i64, sched, vp, err]
+    handle.tb200_rmsnorm_bf16.restype = i32
+    handle.tb200_rmsnorm_bf16.argtypes = [vp, vp, vp, i64, i64, ctypes.c_float, vp, err]
+    handle.tb200_swiglu_bf16.restype = i32
+    handle.tb200_swiglu_bf16.argtypes = [vp, vp, i64, i64, vp, err]
+    handle.tb200_residual_add.restype = i32
+    handle.tb200_residual_add.argtypes = [vp, vp, i64, vp, err]
     handle.tb200_peer_set_wait_limit.restype = i32
     handle.tb200_peer_set_wait_limit.argtypes = [ctypes.c_uint64]
     handle.tb200_gguf_gemm.restype = i32

@@ -898,6 +898,41 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   return ok(error);
 }
 
+int32_t tb200_rmsnorm_bf16(const float* x, const float* weight, void* out, int64_t m, int64_t k, float eps, void* stream,
+                           TensorErrorV1* error) {
+  if (m < 1 || k < 4 || k % 4) return fail(error, TENSOR_ERROR_ARGUMENT, "rmsnorm needs m >= 1 and k a multiple of 4");
+  if (int32_t s = check_pointer(error, "x", x, 16, true)) return s;
+  if (int32_t s = check_pointer(error, "weight", weight, 16, true)) return s;
+  if (int32_t s = check_pointer(error, "out", out, 8, true)) return s;
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaError_t e = launch_rmsnorm(x, weight, out, m, k, eps, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(error, "rmsnorm launch", e);
+  return ok(error);
+}
+
+int32_t tb200_swiglu_bf16(const float* gate_up, void* out, int64_t m, int64_t width, void* stream, TensorErrorV1* error) {
+  if (m < 1 || width < 4 || width % 4) return fail(error, TENSOR_ERROR_ARGUMENT, "swiglu needs m >= 1 and a width that is a multiple of 4");
+  if (int32_t s = check_pointer(error, "gate_up", gate_up, 16, true)) return s;
+  if (int32_t s = check_pointer(error, "out", out, 8, true)) return s;
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaError_t e = launch_swiglu(gate_up, out, m, width, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(error, "swiglu launch", e);
+  return ok(error);
+}
+
+int32_t tb200_residual_add(float* stream_buffer, const float* delta, int64_t count, void* stream, TensorErrorV1* error) {
+  if (count < 4 || count % 4) return fail(error, TENSOR_ERROR_ARGUMENT, "residual add needs a count that is a multiple of 4");
+  if (int32_t s = check_pointer(error, "stream_buffer", stream_buffer, 16, true)) return s;
+  if (int32_t s = check_pointer(error, "delta", delta, 16, true)) return s;
+  const DeviceInfo* dev;
+  if (int32_t s = require_device(error, &dev)) return s;
+  cudaError_t e = launch_residual_add(stream_buffer, delta, count, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(error, "residual add launch", e);
+  return ok(error);
+}
+
 int32_t tb200_peer_set_wait_limit(uint64_t nanoseconds) {
   set_peer_wait_limit_ns(nanoseconds);
   return TENSOR_OK;

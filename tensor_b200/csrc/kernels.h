@@ -150,6 +150,13 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
 void set_peer_wait_limit_ns(unsigned long long ns);
 unsigned long long peer_wait_limit_ns();
 
+// The steps either side of a decode projection (glue.cu); every pointer 16-byte aligned, k and width
+// multiples of 4.  All three are launched so that the kernel behind them may start early.
+cudaError_t launch_rmsnorm(const float* x, const float* weight, void* out_bf16, long long m, long long k, float eps,
+                           cudaStream_t stream);
+cudaError_t launch_swiglu(const float* gate_up, void* out_bf16, long long m, long long width, cudaStream_t stream);
+cudaError_t launch_residual_add(float* stream_buffer, const float* delta, long long count, cudaStream_t stream);
+
 // Cross-GPU barrier over peer-mapped signal pads (one pad of kSignalWords uint32 per rank, zeroed
 // once): every rank tells every peer that all work it enqueued before is complete and visible,
 // then waits (bounded) until every peer has said the same.  pads[i] is rank i's pad as mapped here.

@@ -313,6 +313,64 @@ class GemvList:
     __call__ = launch
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out: torch.Tensor | None = None, stream=None):
+    """``out[r] = bf16(x[r] * rsqrt(mean(x[r]^2) + eps) * weight)`` for fp32 ``x [m, k]`` (``tb200_rmsnorm_bf16``):
+    the residual stream turned into the activations of the next projection."""
+    _require_cuda("x", x)
+    _require_cuda("weight", weight)
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or x.dim() != 2 or weight.numel() != x.shape[1]:
+        raise ValueError("rmsnorm takes float32 x [m, k] and float32 weight [k]")
+    m, k = x.shape
+    if out is None:
+        out = torch.empty((m, k), dtype=torch.bfloat16, device=x.device)
+    _require_cuda("out", out)
+    if out.dtype != torch.bfloat16 or out.numel() != m * k:
+        raise ValueError("out must be bfloat16 [m, k]")
+    device = _same_device(x, weight, out)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_rmsnorm_bf16(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, k, float(eps),
+                                          _stream_handle(device, stream), ctypes.byref(error))
+    raise_for_status(status, error)
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, stream=None):
+    """``out = bf16(silu(gate) * up)`` for the fp32 ``[m, 2 * width]`` output of a grouped gate + up launch
+    (gate in the first ``width`` columns); ``tb200_swiglu_bf16``."""
+    _require_cuda("gate_up", gate_up)
+    if gate_up.dtype != torch.float32 or gate_up.dim() != 2 or gate_up.shape[1] % 2:
+        raise ValueError("swiglu takes float32 [m, 2 * width]")
+    m, width = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((m, width), dtype=torch.bfloat16, device=gate_up.device)
+    _require_cuda("out", out)
+    if out.dtype != torch.bfloat16 or out.numel() != m * width:
+        raise ValueError("out must be bfloat16 [m, width]")
+    device = _same_device(gate_up, out)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_swiglu_bf16(gate_up.data_ptr(), out.data_ptr(), m, width, _stream_handle(device, stream),
+                                         ctypes.byref(error))
+    raise_for_status(status, error)
+    return out
+
+
+def residual_add(stream_buffer: torch.Tensor, delta: torch.Tensor, stream=None):
+    """``stream_buffer += delta`` (fp32, in place); ``tb200_residual_add``."""
+    _require_cuda("stream_buffer", stream_buffer)
+    _require_cuda("delta", delta)
+    if stream_buffer.dtype != torch.float32 or delta.dtype != torch.float32 or stream_buffer.numel() != delta.numel():
+        raise ValueError("residual_add takes two float32 tensors of the same size")
+    device = _same_device(stream_buffer, delta)
+    error = abi.TensorErrorV1()
+    with torch.cuda.device(device):
+        status = lib().tb200_residual_add(stream_buffer.data_ptr(), delta.data_ptr(), stream_buffer.numel(),
+                                          _stream_handle(device, stream), ctypes.byref(error))
+    raise_for_status(status, error)
+    return stream_buffer
+
+
 def set_peer_wait_limit(nanoseconds: int) -> None:
     """How long kernels wait for another GPU's signal before giving up (0: the default, two seconds)."""
     lib().tb200_peer_set_wait_limit(int(nanoseconds))

@@ -352,6 +352,35 @@ class ShardedGemvList:
     __call__ = forward
 
 
+class DecoderMlp:
+    """One decoder MLP at decode batch ``m`` on one GPU, every step a kernel of this library chained
+    without launch gaps: ``h += down(silu(gate(n)) * up(n))`` with ``n = rmsnorm(h)``.  ``h`` is the fp32
+    residual stream ``[m, hidden]`` (updated in place); gate and up share their activations and run as one
+    grouped GEMV; the normalised activations and the SwiGLU product are the bf16 inputs of the
+    projections.  The steps between the projections are what a real step pays for besides the GEMVs
+    (the reference states them as matmul epilogues and a normalisation kernel:
+    packages/tensor-nn/src/tensor_nn/kernels/linear.py:6-100, normalization.py)."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, norm_weight: torch.Tensor,
+                 hidden: int, intermediate: int, m: int, gate_up_format="q4_k", down_format="q4_k", eps: float = 1e-6):
+        self.hidden, self.intermediate, self.m, self.eps = int(hidden), int(intermediate), int(m), float(eps)
+        self.device = gate.device
+        self.norm_weight = norm_weight
+        self.normed = torch.empty((m, hidden), dtype=torch.bfloat16, device=self.device)
+        self.pair = QuantLinearPair(gate, intermediate, up, intermediate, gate_up_format, hidden, m)
+        self.act = torch.empty((m, intermediate), dtype=torch.bfloat16, device=self.device)
+        self.down = QuantLinear(down, down_format, hidden, intermediate, m)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        ops.rmsnorm(h, self.norm_weight, self.eps, out=self.normed)
+        gate_up = self.pair.forward(self.normed)
+        ops.swiglu(gate_up, out=self.act)
+        ops.residual_add(h, self.down.forward(self.act))
+        return h
+
+    __call__ = forward
+
+
 class HostProjection:
     """Host-buffer front end: activations arrive in (pinned) host memory and results are returned
     in host memory; weights stay resident on the GPU.  One call = H2D copy of ``x``, the kernel(s),
@@ -379,5 +408,5 @@ class HostProjection:
         return self.y_host
 
 
-__all__ = ["FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "QuantLinearPair",
+__all__ = ["DecoderMlp", "FusedGatherGroup", "GEMV_MAX_ROWS", "GatherGroup", "HostProjection", "QuantLinear", "QuantLinearPair",
            "ShardedGemvList", "all_gather_columns", "shard_rows", "shard_weight_bytes"]

@@ -170,3 +170,40 @@ def test_tensor_torch_loads_our_artifact_under_fake_tensors(reference_on_path, t
     tbin.build_gemv_f32_tbin(f32, "q4_k", 1, 256, 512)
     with pytest.raises(ValueError):
         tensor_torch.load(f32)
+
+
+def test_reference_module_system_installs_and_resolves_our_module(reference_on_path, tmp_path):
+    """``tensor.json`` + prebuilt artifacts: installed, resolved for target sm_100 and loaded by tensor-torch
+    through the reference's own package code, with no compiler on the consumer side."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import tensor_torch
+    from tensor.modules.archive import pack
+    from tensor.modules.errors import ModuleError
+    from tensor.modules.project import resolve_reference
+    from tensor.modules.resolver import install
+
+    from tensor_b200 import module
+
+    root, cache = str(tmp_path / "gguf-b200"), str(tmp_path / "cache")
+    shapes = [{"op": "gemv", "encoding": "q4_k", "m": 1, "n": 1024, "k": 2048},
+              {"op": "gemv", "encoding": "q6_k", "m": 1, "n": 256, "k": 512, "x_dtype": "float32"},
+              {"op": "gemm", "encoding": "q4_k", "m": 256, "n": 256, "k": 1024}]
+    manifest = module.write_module(root, shapes)
+    assert set(manifest["exports"]) == {"q4_k_gemv_m1_n1024_k2048", "q6_k_gemv_m1_n256_k512_f32", "q4_k_gemm_m256_n256_k1024"}
+    assert install(root, cache_dir=cache)["status"] == "installed"
+    for export in manifest["exports"]:
+        found = resolve_reference(f"gguf-b200::{export}", project=root, module_cache=cache, target="sm_100")
+        assert found["selection"] == "packaged" and found["target"] == "sm_100" and found["path"].endswith(export + ".tbin")
+    with pytest.raises(ModuleError):
+        resolve_reference("gguf-b200::q4_k_gemm_m256_n256_k1024", project=root, module_cache=cache, target="sm_90")
+    kernel = tensor_torch.load("gguf-b200::q4_k_gemm_m256_n256_k1024", project=root, module_cache=cache, target="sm_100")
+    with FakeTensorMode():
+        x = torch.empty((256, 1024), dtype=torch.bfloat16, device="cuda")
+        w = torch.empty((256 * 1024 // 256 * 144,), dtype=torch.uint8, device="cuda")
+        (out,) = kernel._op([x, w], [])
+        assert tuple(out.shape) == (256, 256) and out.dtype == torch.float32
+    archive = str(tmp_path / "gguf-b200.tpack")
+    pack(root, archive, cache_dir=cache)
+    assert os.path.getsize(archive) > 0
