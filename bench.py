@@ -1,6 +1,7 @@
 """Benchmark of the GGUF quantised-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --single gemv:q4_k:1:18944:3584        # one kernel, one shape, plain launches
 
 Workload (``config.workload``): the decode configuration the headline metric is quoted on --
 Q4_K GEMVs of one decoder MLP, gate and up ``[18944 x 3584]`` and down ``[3584 x 18944]``, at batch
@@ -19,8 +20,8 @@ launch streams its weights from HBM.  Data is synthetic (seeded, with the stated
 ``prefill`` reports the tcgen05 GEMM (Q4_K / Q6_K, N=12288, K=4096, M in {256, 512, 2048}) beside the
              ceiling without decoding: a dense bf16 GEMM on weights dequantised ahead of time.
 ``decode_step`` is the 36-layer decoder configuration (252 projections per step, batch 1 and 16).
-``prefill_70b`` is the 70B-class prefill sweep at M = 4096 (on more than one GPU with the outputs
-             all-gathered over NCCL in chunks of rows that overlap the next chunk's GEMM).
+``prefill_70b`` is the 70B-class prefill sweep at M = 4096 (on more than one GPU the fp32 outputs of
+             a rank's columns are all-gathered with NCCL in chunks of rows that overlap the next chunk's GEMM).
 ``cpu_baseline`` times the multi-threaded C port of the reference arithmetic on the host cores on a
              bounded sample.  ``--impl reference`` runs only that port, as the reference arm.
 
@@ -235,9 +236,18 @@ def run_gpu(args):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner would share stdout with the JSON line
-        dist.init_process_group("nccl", device_id=device)
+        # NCCL prints its version banner on stdout while the communicator is set up; stdout carries
+        # the JSON line alone, so the banner goes to stderr
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device)
+            dist.barrier()
+            torch.cuda.synchronize(device)
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     peaks = measured_peaks()
     fmt = tb.get_format(FORMAT)
     stream = torch.cuda.Stream(device)
@@ -702,6 +712,49 @@ def run_gpu(args):
         raise SystemExit(1)
 
 
+def run_single(args):
+    """One kernel at one shape, launched plainly over enough distinct weight copies to exceed the L2: the
+    launch sequence to time a shape outside the step, and small enough to hand to a profiler."""
+    import torch
+
+    import tensor_b200 as tb
+    from tensor_b200 import synth
+
+    parts = args.single.split(":")
+    if len(parts) not in (5, 6) or parts[0] not in ("gemv", "gemm"):
+        raise SystemExit("--single takes gemv|gemm:FORMAT:M:N:K[:VARIANT]")
+    op, name, (m, n, k) = parts[0], parts[1], (int(v) for v in parts[2:5])
+    variant = parts[5] if len(parts) == 6 else "auto"
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    fmt = tb.get_format(name)
+    nbytes = fmt.weight_bytes(n, k)
+    copies = max(2, min(16, -(-(L2_BYTES * 3 // 2) // nbytes)))
+    weights = [synth.make_weights(fmt, n, k, seed=500 + c, device=device) for c in range(copies)]
+    x_dtype = torch.float16 if args.single_dtype == "float16" else torch.bfloat16
+    x = synth.make_activations(m, k, seed=501, device=device, dtype=x_dtype)
+    out = torch.empty(m, n, device=device)
+    kernel = tb.gguf(m, n, k, fmt, op=op, variant=variant, x_dtype=args.single_dtype)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for w in weights[:2]:
+        kernel.launch(x, w, out)
+    torch.cuda.synchronize(device)
+    start.record()
+    for _ in range(args.single_rounds):
+        for w in weights:
+            kernel.launch(x, w, out)
+    stop.record()
+    torch.cuda.synchronize(device)
+    us = start.elapsed_time(stop) * 1e3 / (args.single_rounds * copies)
+    line = {"single": args.single, "x_dtype": args.single_dtype, "us_per_launch": us, "weight_copies": copies,
+            "launches": 2 + args.single_rounds * copies, "device_status": tb.device_status()}
+    if op == "gemv":
+        line["weight_gbps"] = nbytes / us / 1e3
+    else:
+        line["tflops"] = 2.0 * m * n * k / us / 1e6
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -711,8 +764,14 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-decode-step", action="store_true", help="leave the 36-layer decode step out")
     ap.add_argument("--skip-big-prefill", action="store_true", help="leave the 70B-class prefill sweep out")
+    ap.add_argument("--single", default=None, metavar="OP:FORMAT:M:N:K[:VARIANT]",
+                    help="time one kernel at one shape with plain launches (e.g. gemv:q4_k:1:18944:3584) and exit")
+    ap.add_argument("--single-dtype", default="bfloat16", choices=("bfloat16", "float16"))
+    ap.add_argument("--single-rounds", type=int, default=1, help="passes over the weight copies of --single")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.single:
+        run_single(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
