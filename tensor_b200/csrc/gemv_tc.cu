@@ -22,10 +22,10 @@
 //  * One thread issues tcgen05.mma (M = 128 rows, N = 16 activation rows, K = 16) with A from tensor
 //    memory and the fp16 activations from the ring.  Each 32-weight scale group accumulates into
 //    its own block of accumulator columns; the block scales are applied to those 32-weight sums in
-//    fp32 by the decode threads when they drain the accumulators (tcgen05.ld):
+//    fp32 by 8 drain warps of their own (tcgen05.ld), so that the decode warps never wait for the
+//    tensor core:
 //        sum_k (d*sc*q - dmin*mn) x = d*sc*(S - 1024*Sx) - dmin*mn*Sx,   S = sum (1024 + q) x.
-//    The two Sx terms are themselves contractions over the 8 groups, done by two more MMAs against
-//    a tile of group sums (each split into an fp16 high and low part).
+//    The Sx terms use the fp32 sums of each scale group that travel with the activation tile.
 //  * Activations are converted once per list by a small kernel ahead of this one: fp16 after one
 //    power-of-two scale per activation row (largest magnitude -> [2^9, 2^10), so bf16 -> fp16 is exact
 //    for every value within 2^-26 of the row's largest), laid out as the K-major core matrices the
@@ -46,11 +46,15 @@ namespace tb200 {
 namespace {
 
 constexpr int kRows = 128;                    // weight rows per tile = TMEM lanes
-constexpr int kParts = 4;                     // threads per row; each owns a quarter of a unit
+constexpr int kParts = 4;                     // decode threads per row; each owns a quarter of a unit
 constexpr int kDecodeWarps = 4 * kParts;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kProducerWarp = kDecodeWarps, kMmaWarp = kDecodeWarps + 1;
-constexpr int kThreads = (kDecodeWarps + 2) * 32;
+constexpr int kHalves = 2;                    // drain threads per row; each owns the scale groups of two quarters
+constexpr int kDrainWarps = 4 * kHalves;
+constexpr int kDrainThreads = kDrainWarps * 32;
+constexpr int kProducerWarp = kDecodeWarps + kDrainWarps, kMmaWarp = kProducerWarp + 1;
+constexpr int kMmaWarps = 2;                  // two issuers take alternate sub-units
+constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;
 constexpr int kUnitK = 256;                   // weights per row and unit
 constexpr int kXMainBytes = 16 * kUnitK * 2;  // activation tile: 16 rows x 256 k, fp16; the sums of its scale groups follow
 constexpr int kMaxStagesTc = 8;
@@ -82,8 +86,7 @@ struct alignas(64) TcParams {
   int rank, world, sync;
   unsigned long long wait_limit_ns;
 #ifdef TB200_TC_TRACE
-  long long* trace;  // diagnostic timeline of CTA 0 (trace builds only): 8 stamps per unit
-  int debug;         // experiment switches (trace builds only)
+  long long* trace;  // diagnostic timeline of CTA 0 (trace builds only)
 #endif
 };
 #ifdef TB200_TC_TRACE
@@ -92,11 +95,9 @@ struct alignas(64) TcParams {
 #define TC_STAMP(cond, idx, slot) do { } while (0)
 #endif
 #ifdef TB200_TC_TRACE
-#define TC_DEBUG(bit) (p.debug & (bit))
 #define TC_WALL(cond, slot) do { if (p.trace && blockIdx.x == 0 && (cond)) p.trace[63 * 16 + (slot)] = (long long)ptx::global_timer_ns(); } while (0)
 #else
 #define TC_WALL(cond, slot) do { } while (0)
-#define TC_DEBUG(bit) 0
 #endif
 
 struct Cursor {
@@ -167,20 +168,33 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
   return d;
 }
 
-// D[tmem] (+)= A[tmem] * B[smem descriptor]
+// D[tmem] (+)= A[tmem] * B[smem descriptor], issued by the lanes whose `leader` is set.  The whole warp
+// runs the issue loop with uniform control flow, so the addresses and descriptors stay in uniform
+// registers: with a divergent `if (lane == 0)` around the loop every operand of every MMA is moved
+// there one by one, and the issue rate of these small MMAs (about 60 cycles each) suffers.
 template <bool ACCUMULATE>
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t leader) {
   if constexpr (ACCUMULATE) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        "{\n\t.reg .pred p, q;\n\tsetp.eq.u32 p, 1, 1;\n\tsetp.ne.u32 q, %4, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc),
+        "r"(leader)
         : "memory");
   } else {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        "{\n\t.reg .pred p, q;\n\tsetp.eq.u32 p, 1, 0;\n\tsetp.ne.u32 q, %4, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc),
+        "r"(leader)
         : "memory");
   }
+}
+// tcgen05.commit by the lanes whose `leader` is set
+__device__ __forceinline__ void umma_commit_if(uint64_t* bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(ptx::smem_addr(bar)),
+      "r"(leader)
+      : "memory");
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
@@ -267,15 +281,14 @@ template <> struct TcFormat<kQ4_K> {
   __host__ __device__ static __forceinline__ int box_x(int sb) { return sb * 18; }  // 8-byte units
   __host__ __device__ static __forceinline__ int box_offset(int) { return 0; }
   // two k-steps of 16 per 32-weight group; a k-step's activations are 512 bytes (32 descriptor units)
-  __device__ static __forceinline__ void issue(uint32_t d, uint32_t a, uint64_t xdesc, int, uint32_t idesc) {
+  __device__ static __forceinline__ void issue(uint32_t d, uint32_t a, uint64_t xdesc, int, uint32_t idesc, uint32_t leader) {
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
-      umma_ts<false>(d + 16 * g, a + 16 * g, xdesc + 64 * g, idesc);
-      umma_ts<true>(d + 16 * g, a + 16 * g + 8, xdesc + 64 * g + 32, idesc);
+      umma_ts<false>(d + 16 * g, a + 16 * g, xdesc + 64 * g, idesc, leader);
+      umma_ts<true>(d + 16 * g, a + 16 * g + 8, xdesc + 64 * g + 32, idesc, leader);
     }
   }
-  __device__ static __forceinline__ void decode(uint32_t wrow, int part, int, int, uint32_t tmem_a, UnitScales& out) {
-    const uint4 hdr = ptx::lds128(wrow);
+  __device__ static __forceinline__ void decode(uint32_t wrow, int part, int, int, uint32_t tmem_a) {
     const uint4 q0 = ptx::lds128(wrow + 16 + 32 * part), q1 = ptx::lds128(wrow + 32 + 32 * part);
     const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     uint32_t mlo, mhi, bits;
@@ -293,26 +306,30 @@ template <> struct TcFormat<kQ4_K> {
     }
     tmem_st16(tmem_a + 32 * part, lo);
     tmem_st16(tmem_a + 32 * part + 16, hi);
-    // 6-bit scales / mins of groups 2p, 2p+1 (bytes 4..15 of the block: hdr.y, hdr.z, hdr.w)
-    uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
-    if (part < 2) {
-      const int sh = 16 * part;
-      sc_lo = (hdr.y >> sh) & 63u;
-      sc_hi = (hdr.y >> (sh + 8)) & 63u;
-      mn_lo = (hdr.z >> sh) & 63u;
-      mn_hi = (hdr.z >> (sh + 8)) & 63u;
-    } else {
-      const int sh = 16 * (part - 2);
-      sc_lo = ((hdr.w >> sh) & 15u) | (((hdr.y >> (sh + 6)) & 3u) << 4);
-      sc_hi = ((hdr.w >> (sh + 8)) & 15u) | (((hdr.y >> (sh + 14)) & 3u) << 4);
-      mn_lo = ((hdr.w >> (sh + 4)) & 15u) | (((hdr.z >> (sh + 6)) & 3u) << 4);
-      mn_hi = ((hdr.w >> (sh + 12)) & 15u) | (((hdr.z >> (sh + 14)) & 3u) << 4);
+  }
+  // scales of the four groups 4 half .. 4 half + 3 of a row's block (quarters 2 half and 2 half + 1):
+  // 6-bit scales / mins in bytes 4..15 of the block (hdr.y, hdr.z, hdr.w), fp16 d and dmin in hdr.x
+  __device__ static __forceinline__ void scales2(uint32_t wrow, int half, int, int, UnitScales (&out)[2]) {
+    const uint4 hdr = ptx::lds128(wrow);
+    uint32_t sc[4], mn[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (half == 0) {
+        sc[j] = (hdr.y >> (8 * j)) & 63u;
+        mn[j] = (hdr.z >> (8 * j)) & 63u;
+      } else {
+        sc[j] = ((hdr.w >> (8 * j)) & 15u) | (((hdr.y >> (8 * j + 6)) & 3u) << 4);
+        mn[j] = ((hdr.w >> (8 * j + 4)) & 15u) | (((hdr.z >> (8 * j + 6)) & 3u) << 4);
+      }
     }
     const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // d, dmin
-    out.s_lo = dd.x * (float)sc_lo;
-    out.s_hi = dd.x * (float)sc_hi * 0.0625f;  // the odd group's MMAs sum 1024 + 16 q
-    out.e_lo = fmaf(1024.f, out.s_lo, dd.y * (float)mn_lo);
-    out.e_hi = fmaf(1024.f, out.s_hi, dd.y * (float)mn_hi);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      out[q].s_lo = dd.x * (float)sc[2 * q];
+      out[q].s_hi = dd.x * (float)sc[2 * q + 1] * 0.0625f;  // the odd group's MMAs sum 1024 + 16 q
+      out[q].e_lo = fmaf(1024.f, out[q].s_lo, dd.y * (float)mn[2 * q]);
+      out[q].e_hi = fmaf(1024.f, out[q].s_hi, dd.y * (float)mn[2 * q + 1]);
+    }
   }
 };
 
@@ -343,7 +360,7 @@ template <> struct TcFormat<kQ6_K> {
   }
 
   template <int O>
-  __device__ static __forceinline__ void decode_at(uint32_t wrow, int part, int sub, uint32_t tmem_a, UnitScales& out) {
+  __device__ static __forceinline__ void decode_at(uint32_t wrow, int part, int sub, uint32_t tmem_a) {
     uint32_t ql[8], qh[8];
     load32<O>(wrow + sub * 64 + (part & 1) * 32, ql);
     load32<O>(wrow + 128 + sub * 32, qh);
@@ -358,33 +375,38 @@ template <> struct TcFormat<kQ6_K> {
       cells[2 * i + 1] = __byte_perm(q, magic, 0x4342);  // bytes 2, 3
     }
     tmem_st16(tmem_a + 16 * part, cells);
-    // int8 scales of groups 2p, 2p+1 of this half; fp16 d
-    unsigned short sc2, dbits;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc2) : "r"(wrow + O + 192 + 8 * sub + 2 * part));
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dbits) : "r"(wrow + O + 208));
-    const float d = __half2float(__ushort_as_half(dbits));
-    out.s_lo = d * (float)(int)(signed char)(sc2 & 0xFF);
-    out.s_hi = d * (float)(int)(signed char)(sc2 >> 8);
-    out.e_lo = 1056.f * out.s_lo;  // (1024 + q) - 1056 = q - 32
-    out.e_hi = 1056.f * out.s_hi;
   }
-  __device__ static __forceinline__ void decode(uint32_t wrow, int part, int sub, int offset, uint32_t tmem_a,
-                                                UnitScales& out) {
+  __device__ static __forceinline__ void decode(uint32_t wrow, int part, int sub, int offset, uint32_t tmem_a) {
     switch (offset >> 1) {  // the same for every thread of the CTA
-      case 0: decode_at<0>(wrow, part, sub, tmem_a, out); break;
-      case 1: decode_at<2>(wrow, part, sub, tmem_a, out); break;
-      case 2: decode_at<4>(wrow, part, sub, tmem_a, out); break;
-      case 3: decode_at<6>(wrow, part, sub, tmem_a, out); break;
-      case 4: decode_at<8>(wrow, part, sub, tmem_a, out); break;
-      case 5: decode_at<10>(wrow, part, sub, tmem_a, out); break;
-      case 6: decode_at<12>(wrow, part, sub, tmem_a, out); break;
-      default: decode_at<14>(wrow, part, sub, tmem_a, out); break;
+      case 0: decode_at<0>(wrow, part, sub, tmem_a); break;
+      case 1: decode_at<2>(wrow, part, sub, tmem_a); break;
+      case 2: decode_at<4>(wrow, part, sub, tmem_a); break;
+      case 3: decode_at<6>(wrow, part, sub, tmem_a); break;
+      case 4: decode_at<8>(wrow, part, sub, tmem_a); break;
+      case 5: decode_at<10>(wrow, part, sub, tmem_a); break;
+      case 6: decode_at<12>(wrow, part, sub, tmem_a); break;
+      default: decode_at<14>(wrow, part, sub, tmem_a); break;
+    }
+  }
+  // int8 scales of the four groups 4 half .. 4 half + 3 of this half of the block; fp16 d
+  __device__ static __forceinline__ void scales2(uint32_t wrow, int half, int sub, int offset, UnitScales (&out)[2]) {
+    unsigned short dbits;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dbits) : "r"(wrow + offset + 208));
+    const float d = __half2float(__ushort_as_half(dbits));
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      unsigned short sc2;
+      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc2) : "r"(wrow + offset + 192 + 8 * sub + 4 * half + 2 * q));
+      out[q].s_lo = d * (float)(int)(signed char)(sc2 & 0xFF);
+      out[q].s_hi = d * (float)(int)(signed char)(sc2 >> 8);
+      out[q].e_lo = 1056.f * out[q].s_lo;  // (1024 + q) - 1056 = q - 32
+      out[q].e_hi = 1056.f * out[q].s_hi;
     }
   }
   // one accumulator block per 16-weight group: 8 MMAs per sub-unit, none accumulating
-  __device__ static __forceinline__ void issue(uint32_t d, uint32_t a, uint64_t xdesc, int sub, uint32_t idesc) {
+  __device__ static __forceinline__ void issue(uint32_t d, uint32_t a, uint64_t xdesc, int sub, uint32_t idesc, uint32_t leader) {
 #pragma unroll
-    for (int g = 0; g < 8; ++g) umma_ts<false>(d + 16 * g, a + 8 * g, xdesc + 32 * (8 * sub + g), idesc);
+    for (int g = 0; g < 8; ++g) umma_ts<false>(d + 16 * g, a + 8 * g, xdesc + 32 * (8 * sub + g), idesc, leader);
   }
 };
 
@@ -414,7 +436,7 @@ __device__ __forceinline__ void correct(uint32_t sums, int group, const UnitScal
   }
 }
 
-// State the decode warps share when they meet among themselves.
+// State the drain warps share when they meet among themselves.
 struct DecodeSync {
   uint64_t* cbar;
   volatile int* abort;
@@ -429,24 +451,24 @@ struct DecodeSync {
   }
 };
 
-// A segment = the units of one row tile that this CTA owns (columns sb0 .. at.sb).  The decode
-// threads have put their sums into `red` ([quarter][activation row][weight row]).  All of K: add the
-// four quarters and store.  Part of K: the sum goes to this CTA's scratch slot and the last CTA of the
+// A segment = the units of one row tile that this CTA owns (columns sb0 .. at.sb).  The drain
+// threads have put their sums into `red` ([half][activation row][weight row]).  All of K: add the
+// two halves and store.  Part of K: the sum goes to this CTA's scratch slot and the last CTA of the
 // tile to arrive adds the slots in K order (deterministic).
 __device__ __noinline__ bool finish_segment(const TcParams& p, const Cursor at, int sb0, int u0, const float* red,
                                             DecodeSync& ds) {
   const TcItem& it = p.item[at.item];
-  const int nb = it.nb, tid = threadIdx.x;
+  const int nb = it.nb, tid = threadIdx.x - kDecodeThreads;
   if (!ds.sync()) return false;
   const bool whole = sb0 == 0 && at.sb == it.nsb - 1;
   const long long tile_unit0 = (long long)it.unit_base + (long long)at.tile * it.nsb;
   const bool from_range_start = tile_unit0 + sb0 == u0;
   float* slot = p.partials + ((size_t)2 * blockIdx.x + (from_range_start ? 0 : 1)) * kSlotFloats;
-  for (int i = tid; i < nb * kRows; i += kDecodeThreads) {
+  for (int i = tid; i < nb * kRows; i += kDrainThreads) {
     const int b = i >> 7, r = i & (kRows - 1);
     float v = red[b * kRows + r];
 #pragma unroll
-    for (int q = 1; q < kParts; ++q) v += red[(q * nb + b) * kRows + r];
+    for (int q = 1; q < kHalves; ++q) v += red[(q * nb + b) * kRows + r];
     if (whole) {
       const long long grow = (long long)at.tile * kRows + r;
       if (b < it.m && grow < it.n) {
@@ -474,38 +496,69 @@ __device__ __noinline__ bool finish_segment(const TcParams& p, const Cursor at, 
     if (!ds.sync()) return false;
     if (*ds.s_last) {
       __threadfence();
-      for (int i = tid; i < nb * kRows; i += kDecodeThreads) {
+      // Every element this thread owns (up to 8: one per 256 of the nb x 128 sums) is the sum over the
+      // CTAs of the tile in K order.  All loads of a batch of four CTAs are issued before any of them
+      // is used: as a chain of dependent round trips to L2 this sum took tens of microseconds.
+      constexpr int kOwn = 16 * kRows / kDrainThreads;
+      const int own = (nb * kRows + kDrainThreads - 1) / kDrainThreads;
+      float v[kOwn];
+#pragma unroll
+      for (int j = 0; j < kOwn; ++j) v[j] = 0.f;
+      for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+        float part[4][kOwn];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u;
+          const long long range0 = (long long)c * U / G;
+          const float* theirs = p.partials + ((size_t)2 * c + (range0 < tile_unit0 ? 1 : 0)) * kSlotFloats;
+#pragma unroll
+          for (int j = 0; j < kOwn; ++j) {
+            const int i = tid + j * kDrainThreads;
+            part[u][j] = (c <= c_last && j < own && i < nb * kRows) ? __ldcg(theirs + i) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int j = 0; j < kOwn; ++j) v[j] += part[u][j];
+      }
+#pragma unroll
+      for (int j = 0; j < kOwn; ++j) {
+        const int i = tid + j * kDrainThreads;
+        if (j >= own || i >= nb * kRows) continue;
         const int b = i >> 7, r = i & (kRows - 1);
         const long long grow = (long long)at.tile * kRows + r;
         if (b >= it.m || grow >= it.n) continue;
-        float v = 0.f;
-        for (int c = c_first; c <= c_last; ++c) {
-          const long long range0 = (long long)c * U / G;
-          const float* theirs = p.partials + ((size_t)2 * c + (range0 < tile_unit0 ? 1 : 0)) * kSlotFloats;
-          v += __ldcg(theirs + i);
-        }
-        v *= __ldg(it.unscale + b);
-        for (int d = 0; d < it.n_out; ++d) it.outs[d][(long long)b * it.out_ld + grow] = v;
+        const float out = v[j] * __ldg(it.unscale + b);
+        for (int d = 0; d < it.n_out; ++d) it.outs[d][(long long)b * it.out_ld + grow] = out;
       }
     }
   }
   return ds.sync();  // the staging buffer may be overwritten by the next segment
 }
 
+// What the producer tells the other warps about the unit in a ring stage.
+struct StageMeta {
+  int item, tile, sb;
+  int seg_end;  // the unit is the last one of its row tile that this CTA owns
+};
+
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_constant__ TcParams p) {
   using F = TcFormat<FMT>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + kMaxStagesTc;     // the MMAs of a unit have completed and the decode warps are done with its stage
+  uint64_t* empty = full + kMaxStagesTc;     // the MMAs of a unit have completed and every reader is done with its stage
   uint64_t* a_ready = empty + kMaxStagesTc;  // [2] decode warps -> MMA: an A buffer is complete
-  uint64_t* d_ready = a_ready + 2;           // [2] MMA -> decode warps: a unit's accumulators are final
-  uint64_t* d_free = d_ready + 2;            // [2] decode warps -> MMA: the accumulators have been read
-  uint64_t* cbar = d_free + 2;               // decode warps among themselves
+  uint64_t* d_ready = a_ready + 2;           // [2] MMA -> drain and decode warps: the accumulators are final, the A buffer is free
+  uint64_t* d_free = d_ready + 2;            // [2] drain warps -> MMA: the accumulators have been read
+  uint64_t* cbar = d_free + 2;               // drain warps among themselves
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 512);
   volatile int* abort = reinterpret_cast<volatile int*>(smem + 516);
   volatile int* s_last = reinterpret_cast<volatile int*>(smem + 520);
+  StageMeta* meta = reinterpret_cast<StageMeta*>(smem + 640);  // [kMaxStagesTc]
   const uint32_t stage0 = ptx::smem_addr(smem) + kSmemHeader;
+  const uint32_t meta0 = ptx::smem_addr(smem) + 640;
   float* red = reinterpret_cast<float*>(smem + kSmemHeader + p.stages * p.stage_bytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -521,14 +574,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(&full[s], 1);
-      ptx::mbar_init(&empty[s], 1 + kDecodeWarps);
+      ptx::mbar_init(&empty[s], kSub + kDecodeWarps + kDrainWarps);  // one commit per sub-unit
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&a_ready[b], kDecodeWarps);
       ptx::mbar_init(&d_ready[b], 1);
-      ptx::mbar_init(&d_free[b], kDecodeWarps);
+      ptx::mbar_init(&d_free[b], kDrainWarps);
     }
-    ptx::mbar_init(cbar, kDecodeWarps);
+    ptx::mbar_init(cbar, kDrainWarps);
     *abort = 0;
     *s_last = 0;
     ptx::fence_mbar_init();
@@ -549,13 +602,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
     if (lane == 0 && count > 0) {
       for (int i = 0; i < p.n_items; ++i) ptx::prefetch_tensormap(&p.wmap[i]);
       const Cursor first = locate(p, u0);
+      // what the readers of a stage need to know about its unit; published by the arrive that follows
+      auto describe = [&](int s, const Cursor& c, int idx) {
+        StageMeta m;
+        m.item = c.item;
+        m.tile = c.tile;
+        m.sb = c.sb;
+        m.seg_end = (idx == count - 1 || c.sb == p.item[c.item].nsb - 1) ? 1 : 0;
+        meta[s] = m;
+      };
       // Weights never depend on the kernel before this one, activations do: fill the ring with
       // weights, then wait for that kernel, then fetch the activation tiles of those stages.
       const int pre = count < S ? count : S;
       Cursor c = first;
       for (int i = 0; i < pre; ++i) {
-        ptx::mbar_arrive_expect_tx(&full[i], (uint32_t)((TC_DEBUG(8) ? 0 : kWTileBytes) + (TC_DEBUG(4) ? 0 : kXTileBytes)));
-        if (!TC_DEBUG(8))
+        describe(i, c, i);
+        ptx::mbar_arrive_expect_tx(&full[i], (uint32_t)(kWTileBytes + kXTileBytes));
         ptx::tma_load_2d(smem + kSmemHeader + i * p.stage_bytes, &p.wmap[c.item], F::box_x(c.sb), c.tile * kRows,
                          &full[i]);
         advance(p, c);
@@ -585,7 +647,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
       }
       Cursor c2 = first;
       for (int i = 0; i < pre; ++i) {
-        if (!TC_DEBUG(4))
         ptx::bulk_g2s(smem + kSmemHeader + i * p.stage_bytes + kWTileBytes,
                       p.item[c2.item].xprep + (size_t)c2.sb * kXTileBytes, kXTileBytes, &full[i]);
         advance(p, c2);
@@ -595,163 +656,176 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
         if (!wait_bar(&empty[s], ((idx / S) - 1) & 1, abort, 0x10000u | (unsigned)s)) break;
         TC_STAMP(true, idx, 0);
         uint8_t* dst = smem + kSmemHeader + s * p.stage_bytes;
-        ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)((TC_DEBUG(8) ? 0 : kWTileBytes) + (TC_DEBUG(4) ? 0 : kXTileBytes)));
-        if (!TC_DEBUG(8)) ptx::tma_load_2d(dst, &p.wmap[c.item], F::box_x(c.sb), c.tile * kRows, &full[s]);
-        if (!TC_DEBUG(4)) ptx::bulk_g2s(dst + kWTileBytes, p.item[c.item].xprep + (size_t)c.sb * kXTileBytes, kXTileBytes, &full[s]);
+        describe(s, c, idx);
+        ptx::mbar_arrive_expect_tx(&full[s], (uint32_t)(kWTileBytes + kXTileBytes));
+        ptx::tma_load_2d(dst, &p.wmap[c.item], F::box_x(c.sb), c.tile * kRows, &full[s]);
+        ptx::bulk_g2s(dst + kWTileBytes, p.item[c.item].xprep + (size_t)c.sb * kXTileBytes, kXTileBytes, &full[s]);
         advance(p, c);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+  } else if (warp >= kMmaWarp) {
+    // ---------------- MMA issuers ----------------
+    // Two threads (in warps of different schedulers) take alternate sub-units, i.e. one accumulator
+    // set and one A buffer each: the waits and commits one of them executes around its batch of MMAs
+    // (several hundred cycles, during which its own MMAs have long drained from the pipe) overlap
+    // the other one's MMAs.
+    {
       uint32_t idesc;
       asm volatile("mov.b32 %0, %1;" : "=r"(idesc) : "n"(kIdesc));
-      int s = 0, full_phase = 0, step = 0;  // step counts sub-units: buffers alternate between them
-      bool ok = true;
-      for (int idx = 0; idx < count && ok; ++idx) {
-        TC_STAMP(true, idx, 8);
+      const uint32_t leader = lane == 0 ? 1u : 0u;  // the one lane that issues and commits
+      const int which = warp - kMmaWarp;
+      constexpr int kAdvance = 2 / kSub;  // stages between two sub-units of one issuer
+      static_assert(kSub == 1 || kSub == 2, "a staged block is one or two sub-units");
+      int s = (which / kSub) % S, full_phase = 0;
+      for (int step = which; step < count * kSub; step += 2) {
+        const int idx = step / kSub, sub = step % kSub;
+        TC_STAMP(which == 0 && leader, idx, 8);
         if (!wait_bar(&full[s], full_phase, abort, 0x20000u | (unsigned)s)) break;
-        TC_STAMP(true, idx, 9);
+        TC_STAMP(which == 0 && leader, idx, 9);
         const uint64_t xdesc = desc_kmajor(stage0 + s * p.stage_bytes + kWTileBytes);
-#pragma unroll
-        for (int sub = 0; sub < kSub; ++sub, ++step) {
-          const int buf = step & 1, use = step >> 1;
-          if (!wait_bar(&a_ready[buf], use & 1, abort, 0x30000u)) {
-            ok = false;
-            break;
-          }
-          TC_STAMP(true, idx, 10);
-          if (use > 0 && !wait_bar(&d_free[buf], (use - 1) & 1, abort, 0x40000u)) {
-            ok = false;
-            break;
-          }
-          TC_STAMP(true, idx, 1);
-          ptx::tc_fence_after();
-          if (!TC_DEBUG(1)) F::issue(tmem + kColD + buf * kBufCols, tmem + kColA + buf * kBufCols, xdesc, sub, idesc);
-          TC_STAMP(true, idx, 11);
-          if (sub == kSub - 1) ptx::umma_commit(&empty[s]);
-          ptx::umma_commit(&d_ready[buf]);
-          TC_STAMP(true, idx, 2);
-        }
-        if (++s == S) {
-          s = 0;
+        const int buf = step & 1, use = step >> 1;
+        if (!wait_bar(&a_ready[buf], use & 1, abort, 0x30000u)) break;
+        TC_STAMP(which == 0 && leader, idx, 10);
+        if (use > 0 && !wait_bar(&d_free[buf], (use - 1) & 1, abort, 0x40000u)) break;
+        TC_STAMP(leader, idx, 1);
+        ptx::tc_fence_after();
+        F::issue(tmem + kColD + buf * kBufCols, tmem + kColA + buf * kBufCols, xdesc, sub, idesc, leader);
+        umma_commit_if(&empty[s], leader);
+        umma_commit_if(&d_ready[buf], leader);
+        TC_STAMP(leader, idx, 2);
+        __syncwarp();
+        s += kAdvance;
+        if (s >= S) {
+          s -= S;
           full_phase ^= 1;
         }
       }
     }
-  } else {
-    // ---------------- decode warps ----------------
+  } else if (warp < kDecodeWarps) {
+    // ---------------- decode warps: raw blocks -> fp16 A operand in tensor memory ----------------
     const int part = warp >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const int tid = threadIdx.x;  // 0 .. 511
+    const int tid = threadIdx.x;
+    int s = 0, full_phase = 0, step = 0;  // step counts sub-units
+    bool ok = true;
+    for (int idx = 0; idx < count && ok; ++idx) {
+      if (!wait_bar(&full[s], full_phase, abort, 0x70000u | (unsigned)s)) break;
+      TC_STAMP(tid == 0, idx, 3);
+      TC_STAMP(tid == 15 * 32, idx, 13);
+      TC_WALL(tid == 0 && idx == 0, 2);
+      const uint32_t stage = stage0 + s * p.stage_bytes;
+      int offset = 0;
+      if constexpr (FMT == kQ6_K) {
+        int sb;
+        asm volatile("ld.shared.s32 %0, [%1];" : "=r"(sb) : "r"(meta0 + 16 * s + 8));
+        offset = F::box_offset(sb);
+      }
+#pragma unroll
+      for (int sub = 0; sub < kSub; ++sub, ++step) {
+        const int buf = step & 1, use = step >> 1;
+        // the MMAs that read this A buffer two sub-units ago have completed
+        if (use > 0 && !wait_bar(&d_ready[buf], (use - 1) & 1, abort, 0x60000u)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        F::decode(stage + row * F::kBoxBytes, part, sub, offset, tmem + lane_base + kColA + buf * kBufCols);
+        tmem_st_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&a_ready[buf]);
+        TC_STAMP(tid == 0, idx, 4);
+        TC_STAMP(tid == 15 * 32, idx, 12);
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty[s]);  // this warp is done with the stage
+      if (++s == S) {
+        s = 0;
+        full_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- drain warps: accumulators -> scaled running sums -> outputs ----------------
+    const int dw = warp - kDecodeWarps;
+    const int half = dw >> 2, quarter = dw & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int tid = threadIdx.x - kDecodeThreads;  // 0 .. 255
     ptx::grid_dependency_wait();  // outputs and scratch may still be in use by the kernel before
     DecodeSync ds{cbar, abort, s_last, 0u};
     float acc[16];
 #pragma unroll
     for (int b = 0; b < 16; ++b) acc[b] = 0.f;
-
-    // the accumulators of unit `idx` (its MMAs ran while the unit after it was decoded)
-    auto drain_unit = [&](int nb, int at_step, const UnitScales& sc) -> bool {
-      const int buf = at_step & 1;
-      if (!wait_bar(&d_ready[buf], (at_step >> 1) & 1, abort, 0x60000u)) return false;
-      TC_STAMP(tid == 0, at_step, 5);
-      ptx::tc_fence_after();
-      const uint32_t d = tmem + lane_base + kColD + buf * kBufCols;
-#ifdef TB200_TC_ONLY16
-      drain<16>(d, part, sc, acc);
-#else
-      switch (nb) {
-        case 1: drain<1>(d, part, sc, acc); break;
-        case 2: drain<2>(d, part, sc, acc); break;
-        case 4: drain<4>(d, part, sc, acc); break;
-        case 8: drain<8>(d, part, sc, acc); break;
-        default: drain<16>(d, part, sc, acc); break;
-      }
-#endif
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&d_free[buf]);
-      TC_STAMP(tid == 0, at_step, 6);
-      return true;
-    };
-    // this thread's sums of the segment that ended -> staging buffer, then the CTA-wide part
-    auto end_segment = [&](const Cursor& at, int sb0) -> bool {
-      const int nb = p.item[at.item].nb;
-#pragma unroll
-      for (int b = 0; b < 16; ++b) {
-        if (b < nb) red[(part * nb + b) * kRows + row] = acc[b];
-        acc[b] = 0.f;
-      }
-      return finish_segment(p, at, sb0, u0, red, ds);
-    };
-
-    Cursor cur = count > 0 ? locate(p, u0) : Cursor{0, 0, 0};
-    Cursor prev = cur;  // the block whose sub-unit is still in the tensor core
-    int seg_sb0 = cur.sb;
-    UnitScales sc_prev{};
+    int seg_sb0 = -1;
     bool ok = true;
-    int s = 0, full_phase = 0, step = 0;  // step counts sub-units
+    int s = 0, full_phase = 0, step = 0;
     for (int idx = 0; idx < count && ok; ++idx) {
-      if (!wait_bar(&full[s], full_phase, abort, 0x70000u | (unsigned)s)) {
-        ok = false;
-        break;
-      }
-      TC_STAMP(tid == 0, idx, 3);
-      TC_WALL(tid == 0 && idx == 0, 2);
+      if (!wait_bar(&full[s], full_phase, abort, 0x70000u | (unsigned)s)) break;
       const uint32_t stage = stage0 + s * p.stage_bytes;
-      const int offset = F::box_offset(cur.sb);
-      const int nb_cur = p.item[cur.item].nb;
+      const uint4 mraw = ptx::lds128(meta0 + 16 * s);
+      const Cursor at{(int)mraw.x, (int)mraw.y, (int)mraw.z};
+      const bool seg_end = mraw.w != 0;
+      if (seg_sb0 < 0) seg_sb0 = at.sb;
+      const int nb = p.item[at.item].nb;
+      const int offset = F::box_offset(at.sb);
+      const uint32_t sums = stage + kWTileBytes + kXMainBytes;
 #pragma unroll
-      for (int sub = 0; sub < kSub && ok; ++sub, ++step) {
-        UnitScales sc_cur{};
-        if (!TC_DEBUG(2))
-          F::decode(stage + row * F::kBoxBytes, part, sub, offset, tmem + lane_base + kColA + (step & 1) * kBufCols, sc_cur);
-        tmem_st_wait();
+      for (int sub = 0; sub < kSub; ++sub, ++step) {
+        const int buf = step & 1, use = step >> 1;
+        UnitScales sc[2];
+        F::scales2(stage + row * F::kBoxBytes, half, sub, offset, sc);
+        const int group = (F::kSumGroups / kSub) * sub + 4 * half;
+        if (!wait_bar(&d_ready[buf], use & 1, abort, 0x60000u)) {
+          ok = false;
+          break;
+        }
+        TC_STAMP(tid == 0, idx, 5);
+        ptx::tc_fence_after();
+        const uint32_t d = tmem + lane_base + kColD + buf * kBufCols;
+        switch (nb) {
+          case 1: drain<1>(d, 2 * half, sc[0], acc); drain<1>(d, 2 * half + 1, sc[1], acc); break;
+          case 2: drain<2>(d, 2 * half, sc[0], acc); drain<2>(d, 2 * half + 1, sc[1], acc); break;
+          case 4: drain<4>(d, 2 * half, sc[0], acc); drain<4>(d, 2 * half + 1, sc[1], acc); break;
+          case 8: drain<8>(d, 2 * half, sc[0], acc); drain<8>(d, 2 * half + 1, sc[1], acc); break;
+          default: drain<16>(d, 2 * half, sc[0], acc); drain<16>(d, 2 * half + 1, sc[1], acc); break;
+        }
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&a_ready[step & 1]);
-        TC_STAMP(tid == 0, idx, 4);
-        if (step > 0) {
-          // the sub-unit before: its MMAs ran while this one was decoded
-          ok = drain_unit(p.item[prev.item].nb, step - 1, sc_prev);
-          if (ok && sub == 0 && (cur.item != prev.item || cur.tile != prev.tile)) {
-            ok = end_segment(prev, seg_sb0);
-            seg_sb0 = cur.sb;
-          }
+        if (lane == 0) ptx::mbar_arrive(&d_free[buf]);  // the tensor core may overwrite this accumulator set
+        // the Sx terms need nothing from the tensor core: they come after it has been released
+        switch (nb) {
+          case 1: correct<1>(sums, group, sc[0], acc); correct<1>(sums, group + 2, sc[1], acc); break;
+          case 2: correct<2>(sums, group, sc[0], acc); correct<2>(sums, group + 2, sc[1], acc); break;
+          case 4: correct<4>(sums, group, sc[0], acc); correct<4>(sums, group + 2, sc[1], acc); break;
+          case 8: correct<8>(sums, group, sc[0], acc); correct<8>(sums, group + 2, sc[1], acc); break;
+          default: correct<16>(sums, group, sc[0], acc); correct<16>(sums, group + 2, sc[1], acc); break;
         }
-        if (!ok) break;
-        // the Sx terms of this sub-unit need nothing from the tensor core
-        const uint32_t sums = stage + kWTileBytes + kXMainBytes;
-        const int group = (F::kSumGroups / kSub) * sub + 2 * part;
-#ifdef TB200_TC_ONLY16
-        correct<16>(sums, group, sc_cur, acc);
-#else
-        switch (nb_cur) {
-          case 1: correct<1>(sums, group, sc_cur, acc); break;
-          case 2: correct<2>(sums, group, sc_cur, acc); break;
-          case 4: correct<4>(sums, group, sc_cur, acc); break;
-          case 8: correct<8>(sums, group, sc_cur, acc); break;
-          default: correct<16>(sums, group, sc_cur, acc); break;
-        }
-#endif
-        sc_prev = sc_cur;
-        prev = cur;
+        TC_STAMP(tid == 0, idx, 6);
       }
+      if (!ok) break;
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[s]);  // this warp is done with the stage
-      advance(p, cur);
+      if (seg_end) {
+        // this thread's sums of the segment -> staging buffer, then the CTA-wide part
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+          if (b < nb) red[(half * nb + b) * kRows + row] = acc[b];
+          acc[b] = 0.f;
+        }
+        ok = finish_segment(p, at, seg_sb0, u0, red, ds);
+        seg_sb0 = -1;
+      }
       if (++s == S) {
         s = 0;
         full_phase ^= 1;
       }
     }
     TC_WALL(tid == 0, 3);
-    if (ok && count > 0) {
-      ok = drain_unit(p.item[prev.item].nb, step - 1, sc_prev);
-      if (ok) ok = end_segment(prev, seg_sb0);
-    }
-    TC_WALL(tid == 0, 5);
+#ifdef TB200_TC_TRACE
+    if (p.trace && tid == 0) atomicMax(reinterpret_cast<unsigned long long*>(p.trace + 63 * 16 + 7), (unsigned long long)ptx::global_timer_ns());
+#endif
   }
 
   ptx::tc_fence_before();
@@ -768,6 +842,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const __grid_const
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
   TC_WALL(threadIdx.x == 0, 4);
+#ifdef TB200_TC_TRACE
+  if (p.trace && threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned long long*>(p.trace + 63 * 16 + 6), (unsigned long long)ptx::global_timer_ns());
+#endif
   if (threadIdx.x == 0 && (p.sync & kPeerSignal)) {
     // every warp of this CTA has stored what it will store; the last CTA of the grid tells the peers
     unsigned int* mine = p.pads[p.rank];
@@ -807,11 +884,14 @@ struct PrepArgs {
 #define PREP_WALL(slot) do { } while (0)
 #endif
 
+constexpr int kPrepThreads = 1024;
+constexpr int kPrepHeld = 3;  // 16-byte chunks a thread keeps in registers between the two passes over a row
+
 template <int FMT, bool F16>
-__global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) {
+__global__ void __launch_bounds__(kPrepThreads) gemv_tc_prepare_kernel(const PrepArgs a) {
   constexpr int kXTileBytes = TcFormat<FMT>::kXTileBytes;
   constexpr int kSumGroups = TcFormat<FMT>::kSumGroups;
-  __shared__ uint32_t s_max[8];
+  __shared__ uint32_t s_max[kPrepThreads / 32];
   const PrepX px = a.x[blockIdx.y];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
   PREP_WALL(8);
@@ -821,7 +901,7 @@ __global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) 
   const int chunks = px.k >> 3;                  // 8 values = 16 bytes; a multiple of 32
   if (b >= px.m) {
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int c = tid; c < chunks; c += 256) {
+    for (int c = tid; c < chunks; c += kPrepThreads) {
       const int j = c >> 5, k8 = c & 31;
       *reinterpret_cast<uint4*>(px.xprep + (size_t)j * kXTileBytes + k8 * 256 + b * 16) = zero;
       if (k8 < kSumGroups) *reinterpret_cast<float*>(px.xprep + (size_t)j * kXTileBytes + kXMainBytes + k8 * 64 + b * 4) = 0.f;
@@ -829,20 +909,35 @@ __global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) 
     if (tid == 0) px.unscale[b] = 1.f;
     return;
   }
+  // First pass: the row's largest magnitude.  Rows of up to kPrepHeld * kPrepThreads chunks (24576
+  // values) are read once, all loads in flight together, and stay in registers for the second pass:
+  // a loop of dependent round trips to memory was most of this kernel's time on long rows.
   const uint16_t* xr = px.x + (size_t)b * px.k;
+  const bool held = chunks <= kPrepHeld * kPrepThreads;
+  uint4 keep[kPrepHeld];
   uint32_t mx = 0;
-  for (int c = tid; c < chunks; c += 256) {
-    const uint4 v = *reinterpret_cast<const uint4*>(xr + (c << 3));
+  auto magnitude = [&](const uint4& v) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < kPrepHeld; ++i) {
+      const int c = tid + i * kPrepThreads;
+      keep[i] = c < chunks ? *reinterpret_cast<const uint4*>(xr + (c << 3)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kPrepHeld; ++i) magnitude(keep[i]);
+  } else {
+    for (int c = tid; c < chunks; c += kPrepThreads) magnitude(*reinterpret_cast<const uint4*>(xr + (c << 3)));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   if (lane == 0) s_max[tid >> 5] = mx;
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < 8; ++i) mx = max(mx, s_max[i]);
+  for (int i = 0; i < kPrepThreads / 32; ++i) mx = max(mx, s_max[i]);
   // biased exponent of the largest magnitude -> shift that lands it in [2^9, 2^10)
   const int e = F16 ? (int)(mx >> 10) : (int)(mx >> 7);
   const int bias = F16 ? 15 : 127, emax = F16 ? 31 : 255;
@@ -852,8 +947,8 @@ __global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) 
   const float scale = __uint_as_float((uint32_t)(sh + 127) << 23);
   if (tid == 0) px.unscale[b] = __uint_as_float((uint32_t)(127 - sh) << 23);
 
-  for (int c = tid; c < chunks; c += 256) {
-    const uint4 v = *reinterpret_cast<const uint4*>(xr + (c << 3));
+  // Second pass: chunk c of the row (a whole warp at a time: c < chunks is warp-uniform) -> its tile
+  auto emit = [&](int c, const uint4& v) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     float f[8];
 #pragma unroll
@@ -893,6 +988,15 @@ __global__ void __launch_bounds__(256) gemv_tc_prepare_kernel(const PrepArgs a) 
       *reinterpret_cast<uint4*>(tile + cc * 256 + b * 16) = make_uint4(pack(0, 1), pack(2, 3), pack(4, 5), pack(6, 7));
       if ((cc & 1) == 0) *reinterpret_cast<float*>(tile + kXMainBytes + (cc >> 1) * 64 + b * 4) = sum;
     }
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < kPrepHeld; ++i) {
+      const int c = tid + i * kPrepThreads;
+      if (c < chunks) emit(c, keep[i]);
+    }
+  } else {
+    for (int c = tid; c < chunks; c += kPrepThreads) emit(c, *reinterpret_cast<const uint4*>(xr + (c << 3)));
   }
   PREP_WALL(10);
 }
@@ -921,15 +1025,16 @@ static long long* trace_buffer() {
       atexit([] {
         static long long host[64 * 16];
         cudaMemcpy(host, buffer, sizeof(host), cudaMemcpyDeviceToHost);
-        printf("unit: stage free | mma start, issued | warp0 data ready, A stored | acc ready, drained | mma thread: loop top, data seen, A seen, mmas issued\n");
+        printf("unit: stage free | mma start, issued | warp0 data ready, A stored | acc ready, drained | mma thread: loop top, data seen, A seen | warp15 data ready, A stored\n");
         const long long t0 = host[3];
         const long long* w = host + 63 * 16;
-        printf("wall clock (ns after prepare entry): prepare past wait %lld, prepare end %lld | gemv entry %lld, past wait %lld, first data %lld, loop end %lld, segment done %lld, exit %lld\n",
-               w[9] - w[8], w[10] - w[8], w[0] - w[8], w[1] - w[8], w[2] - w[8], w[3] - w[8], w[5] - w[8], w[4] - w[8]);
+        printf("wall clock (ns after prepare entry): prepare past wait %lld, prepare end %lld | gemv entry %lld, past wait %lld, first data %lld, loop end %lld, last loop end of any CTA %lld, exit %lld\n",
+               w[9] - w[8], w[10] - w[8], w[0] - w[8], w[1] - w[8], w[2] - w[8], w[3] - w[8], w[7] - w[8], w[4] - w[8]);
+        printf("last CTA to leave: %lld\n", w[6] - w[8]);
         for (int i = 0; i < 63 && host[i * 16 + 3]; ++i) {
           const long long* h = host + i * 16;
-          printf("%3d: %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld %7lld %7lld\n", i, h[0] ? h[0] - t0 : 0,
-                 h[1] - t0, h[2] - t0, h[3] - t0, h[4] - t0, h[5] - t0, h[6] - t0, h[8] - t0, h[9] - t0, h[10] - t0, h[11] - t0);
+          printf("%3d: %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld | %7lld %7lld %7lld | %7lld %7lld\n", i, h[0] ? h[0] - t0 : 0,
+                 h[1] - t0, h[2] - t0, h[3] - t0, h[4] - t0, h[5] - t0, h[6] - t0, h[8] - t0, h[9] - t0, h[10] - t0, h[13] - t0, h[12] - t0);
         }
       });
     }
@@ -1006,7 +1111,7 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
   // ---- activations -> fp16 tiles (one small kernel for the whole list) ----
   PrepArgs prep{};
 #ifdef TB200_TC_TRACE
-  prep.trace = getenv("TB200_TC_NOTRACE") ? nullptr : trace_buffer();
+  prep.trace = trace_buffer();
 #endif
   int n_x = 0;
   for (int i = 0; i < count; ++i) {
@@ -1025,7 +1130,7 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
   {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(16, (unsigned)n_x);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(kPrepThreads);
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
@@ -1070,7 +1175,7 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
   p.n_items = count;
   p.total_units = L.total_units;
   p.stage_bytes = kRows * box_bytes(items[0].fmt) + x_tile_bytes(items[0].fmt);
-  p.red_floats = kParts * max_nb * kRows;
+  p.red_floats = kHalves * max_nb * kRows;
   const int spare = dev->max_smem_optin - kSmemHeader - p.red_floats * 4;
   p.stages = spare / p.stage_bytes;
   if (p.stages > kMaxStagesTc) p.stages = kMaxStagesTc;
@@ -1088,11 +1193,6 @@ cudaError_t launch_gemv_tc(const TcLaunchItem* items, int count, void* scratch, 
   }
 #ifdef TB200_TC_TRACE
   p.trace = trace_buffer();
-  {
-    const char* dbg = getenv("TB200_TC_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-    if (getenv("TB200_TC_NOTRACE")) p.trace = nullptr;
-  }
 #endif
   auto kernel = items[0].fmt == kQ6_K ? gemv_tc_kernel<kQ6_K> : gemv_tc_kernel<kQ4_K>;
   e = allow_full_shared_memory(kernel);
