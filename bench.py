@@ -616,6 +616,7 @@ def run_gpu(args):
     if not args.skip_big_prefill:
         m = BIG_PREFILL_M
         side = torch.cuda.Stream(device)
+        compute = (torch.cuda.Stream(device), torch.cuda.Stream(device))
         for label, name, n, k in BIG_PREFILL:
             n_local = n // world
             w = synth.make_weights(name, n_local, k, seed=900 + rank, device=device)
@@ -636,18 +637,24 @@ def run_gpu(args):
                 kern.launch(x, w, out_local)
 
             def with_gather():
-                # chunk i's all-gather (and its rearrangement into row-major [M, N]) runs on a side
-                # stream while chunk i + 1's GEMM runs on the main one
+                # The GEMM runs in chunks of rows that alternate between two compute streams, so two
+                # chunks share the SMs at any time (a chunk alone would leave most of them idle where a
+                # rank has few weight tiles); chunk i's all-gather and its rearrangement into row-major
+                # [M, N] run on a side stream while the chunks after it compute.
                 cur = torch.cuda.current_stream(device)
-                side.wait_stream(cur)
+                for st in (compute[0], compute[1], side):
+                    st.wait_stream(cur)
                 for c in range(chunks):
-                    kerns.launch(x[c * mc:(c + 1) * mc], w, out_local[c * mc:(c + 1) * mc])
-                    events[c].record(cur)
+                    st = compute[c & 1]
+                    with torch.cuda.stream(st):
+                        kerns.launch(x[c * mc:(c + 1) * mc], w, out_local[c * mc:(c + 1) * mc])
+                        events[c].record(st)
                     side.wait_event(events[c])
                     with torch.cuda.stream(side):
                         dist.all_gather_into_tensor(gathered[c].view(world * mc, n_local), out_local[c * mc:(c + 1) * mc])
                         out_full[c * mc:(c + 1) * mc].view(mc, world, n_local).copy_(gathered[c].permute(1, 0, 2))
-                cur.wait_stream(side)
+                for st in (compute[0], compute[1], side):
+                    cur.wait_stream(st)
 
             row = {"projection": label, "format": name, "m": m, "n": n, "k": k, "n_local": n_local}
             for key, fn in (("kernel_us", kernel_only), ("gathered_us", with_gather)):
@@ -674,8 +681,9 @@ def run_gpu(args):
                 recv = (world - 1) * m * n_local * 4
                 row["gather_bytes_received_per_gpu"] = recv
                 row["gather_floor_us_at_770GBs"] = recv / 770e9 * 1e6
-                row["note"] = ("N-sharded; fp32 outputs all-gathered with NCCL in 4 chunks of rows on a side stream and "
-                               "rearranged to row-major [M, N]; the floor is the bytes a GPU must receive over NVLink")
+                row["note"] = ("N-sharded; the GEMM runs in 4 chunks of rows on two alternating streams, each chunk's fp32 output "
+                               "is all-gathered with NCCL on a side stream and rearranged to row-major [M, N]; the floor is the "
+                               "bytes a GPU must receive over NVLink")
             big_prefill.append(row)
             del w, x, out_local, gathered, out_full
         torch.cuda.empty_cache()

@@ -93,6 +93,7 @@ template <int FMT> struct Decoder;
 
 template <> struct Decoder<kQ4_K> {
   static constexpr int kShare = 1;  // k-blocks served by one fetch
+  static constexpr int kAhead = 1;  // fetches in flight ahead of the decode (deeper was measured no faster)
   // thread t -> row t/2, half h = t%2: 32 weights of group 2p+h (p = kb%4), i.e. the low / high
   // nibbles of quant bytes 32p .. 32p+31 of super-block kb/4.
   struct Ctx {
@@ -187,6 +188,7 @@ template <> struct Decoder<kQ6_K> {
   // Two consecutive k-blocks read the same words (the even one their low nibbles / low qh bit pairs,
   // the odd one the high ones), so the words are fetched once per pair.
   static constexpr int kShare = 2;
+  static constexpr int kAhead = 2;  // fetches in flight ahead of the decode
   struct Ctx {
     const uint8_t* wrow[kPasses];
     int row0, i;  // first row of the thread (pass p adds 32 p), word index 0..7
@@ -368,16 +370,20 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
     constexpr int kStep = C::kGroups * D::kShare;
     // K is a multiple of 256, so the k-blocks come in whole units of kShare that share one fetch,
     // and in whole rounds of one unit per group
-    typename D::Raw raw = D::fetch(ctx, group * D::kShare);
+    // The loads of a unit are issued kAhead units before it is decoded (clamped on the last ones): one
+    // unit ahead left the decode warps waiting on memory for most of their stall cycles.
+    constexpr int kAhead = D::kAhead;
+    typename D::Raw raw[kAhead];
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) raw[a] = D::fetch(ctx, min(group * D::kShare + a * kStep, k_blocks - 1));
     for (int kb0 = group * D::kShare; kb0 < k_blocks && ok; kb0 += kStep) {
-      // start the loads of this group's next unit before decoding this one (clamped on the last)
-      const typename D::Raw next = D::fetch(ctx, min(kb0 + kStep, k_blocks - 1));
+      const typename D::Raw next = D::fetch(ctx, min(kb0 + kAhead * kStep, k_blocks - 1));
 #pragma unroll
       for (int j = 0; j < D::kShare; ++j) {
         const int kb = kb0 + j;
         const int s = kb % C::kAStages;
         typename D::Out decoded;
-        D::decode(ctx, raw, kb, decoded);
+        D::decode(ctx, raw[0], kb, decoded);
         if (kb >= C::kAStages && !ptx::mbar_wait(&empty_a[s], ((kb / C::kAStages) - 1) & 1)) {
           report_timeout(0x30000u | (unsigned)kb);
           ok = false;
@@ -387,7 +393,9 @@ __device__ __forceinline__ void gemm_tcgen05_body(const CUtensorMap& tmap_x, con
         ptx::fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
         ptx::mbar_arrive(&full_a[s]);
       }
-      raw = next;
+#pragma unroll
+      for (int a = 0; a + 1 < kAhead; ++a) raw[a] = raw[a + 1];
+      raw[kAhead - 1] = next;
     }
     if (ok) {
       if (!ptx::mbar_wait(acc_full, 0)) {
