@@ -393,7 +393,7 @@ def run_gpu(args):
         # dram__bytes_read.sum + dram__bytes_write.sum of one captured 38,191,104-byte launch
         # (profiles/gemv_q4k_batch1_18944x3584.md: 38,245,120 B, i.e. no re-reads), scaled to the weight
         # bytes of an average launch of this run (traffic is proportional to the rows streamed)
-        "traffic": round(launch_bytes_local * 38245120 / 38191104),
+        "traffic": round(launch_bytes_local * 38265344 / 38191104),
         "algorithmic_bytes_per_launch": launch_bytes_local,
         "note": f"average over the {launches_per_step} GEMV launches of a step (batch 1/4/16, gate and up grouped "
                 f"into one launch), gaps between launches included; best batch ({best['batch']}) reaches "
