@@ -54,6 +54,10 @@ PREFILL_M = (256, 512, 2048)
 LAYER = (("q", 4096, 4096, "q4_k", 0), ("k", 1024, 4096, "q4_k", 0), ("v", 1024, 4096, "q4_k", 0),
          ("o", 4096, 4096, "q4_k", 1), ("gate", 12288, 4096, "q4_k", 2), ("up", 12288, 4096, "q4_k", 2),
          ("down", 4096, 12288, "q6_k", 3))
+# the same layer as the runtime holds it: q, k, v rows concatenated into one weight and gate, up into another when the
+# model is loaded (GGUF rows are independent of each other), so a layer is four launches
+LAYER_FUSED = (("qkv", 6144, 4096, "q4_k", 0), ("o", 4096, 4096, "q4_k", 1), ("gate_up", 24576, 4096, "q4_k", 2),
+               ("down", 4096, 12288, "q6_k", 3))
 LAYERS = 36
 BIG_PREFILL = (("gate_up", "q4_k", 28672, 8192), ("down", "q6_k", 8192, 28672))
 BIG_PREFILL_M = 4096
@@ -430,9 +434,17 @@ def run_gpu(args):
     # ---- end to end: host buffers in, host buffers out, every step ----
     x_live = {b: [acts[b][0], acts[b][2]] for b in BATCHES}
     x_host = {b: [a.cpu().pin_memory() for a in x_live[b]] for b in BATCHES}
-    y_host = {b: [torch.empty(tuple(o.shape), dtype=torch.float32).pin_memory() for o in graph_outs[0][b]] for b in BATCHES}
+    # one GPU: the whole result comes back; N-sharded: every rank reads back the columns it computed (its window
+    # of each gathered output), so the host-side result is the concatenation of the ranks' buffers and the
+    # read-back uses every GPU's own PCIe link instead of rank 0's alone
+    def window(t):
+        n_local = t.shape[1] // world
+        return t[:, rank * n_local:(rank + 1) * n_local]
+
+    y_host = {b: [torch.empty(tuple(window(o).shape), dtype=torch.float32).pin_memory() for o in graph_outs[0][b]]
+              for b in BATCHES}
     h2d = sum(t.numel() * t.element_size() for b in BATCHES for t in x_host[b])
-    d2h = sum(t.numel() * 4 for b in BATCHES for t in y_host[b])
+    d2h = sum(t.numel() * 4 for b in BATCHES for t in y_host[b]) * world  # all ranks together
 
     # Every step copies every activation in from pinned host memory (on every rank: activations are
     # replicated) and every result back out (on rank 0: one copy of the result is what a caller
@@ -455,13 +467,12 @@ def run_gpu(args):
         # the output copy that replay i of a batch graph writes: the copies alternate from slot to slot
         return lists[b].outputs((i % ring) % 2 if world > 1 else 0)
 
-    def e2e_step(i):
+    def e2e_step_batches(i):
         for b in order:
             stream.wait_event(ev_in[b])
             stream.wait_event(ev_out[b])
             with torch.cuda.stream(stream):
                 batch_graphs[b][i % ring].replay()
-                final_wait()
                 ev_done[b].record(stream)
             if rank == 0:
                 s_out.wait_event(ev_done[b])
@@ -472,7 +483,42 @@ def run_gpu(args):
             s_in.wait_event(ev_done[b])
             copy_in(b)  # the next step's inputs of this batch
 
+    # N-sharded runs: the gathered outputs exist in two copies that alternate from step to step, so a
+    # whole step goes out as ONE graph launch and ONE wait for the peers' stores, and its results travel
+    # to the host while the next step computes into the other copy.
+    step_in = torch.cuda.Event()
+    step_done = [torch.cuda.Event(), torch.cuda.Event()]
+    step_out = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def copy_in_all():
+        with torch.cuda.stream(s_in):
+            for b in BATCHES:
+                for dst, src in zip(x_live[b], x_host[b]):
+                    dst.copy_(src, non_blocking=True)
+            step_in.record(s_in)
+
+    def e2e_step_sharded(i):
+        par = i & 1
+        stream.wait_event(step_in)         # this step's inputs have arrived
+        stream.wait_event(step_out[par])   # the output copy this step overwrites has been read out
+        with torch.cuda.stream(stream):
+            graphs[i % ring].replay()
+            step_done[par].record(stream)
+        s_in.wait_event(step_done[par])
+        copy_in_all()                       # the next step's inputs
+        # a rank's own columns are written by its own kernels: they are complete when its step is
+        s_out.wait_event(step_done[par])
+        with torch.cuda.stream(s_out):
+            for b in BATCHES:
+                for dst, src in zip(y_host[b], graph_outs[i % ring][b]):
+                    dst.copy_(window(src), non_blocking=True)
+            step_out[par].record(s_out)
+
+    e2e_step = e2e_step_sharded if world > 1 else e2e_step_batches
+
     def e2e_drain():
+        with torch.cuda.stream(stream):
+            final_wait()
         for st in (stream, s_in, s_out):
             st.synchronize()
 
@@ -480,6 +526,9 @@ def run_gpu(args):
     for b in BATCHES:
         ev_out[b].record(s_out)
         copy_in(b)
+    for ev in step_out:
+        ev.record(s_out)
+    copy_in_all()
     for i in range(4):
         e2e_step(i)
     e2e_drain()
@@ -491,8 +540,10 @@ def run_gpu(args):
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e = {"value": step_bytes_total * args.steps / e2e_s / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "note": "activations from pinned host memory on every rank and the results back to it on rank 0, every "
-                   "step, on copy streams ordered by events per batch (largest batch first); weights resident"}
+           "note": "activations from pinned host memory on every rank and the results back to it, every step, on copy "
+                   "streams ordered by events (one GPU: per batch, largest batch first; N-sharded: one graph launch per "
+                   "step, every rank reads back the columns it computed while the next step computes into the other "
+                   "copy of the outputs; d2h bytes are the sum over ranks); weights resident"}
 
     # free the weight ring before the next parts
     del weights, graphs, batch_graphs, graph_outs
@@ -540,28 +591,29 @@ def run_gpu(args):
         del ws, dense
     torch.cuda.empty_cache()
 
-    # ---- the 36-layer decode step: 252 projections per step, two calls per layer ----
+    # ---- the 36-layer decode step: 252 projections per step as four launches per layer, two calls per layer ----
     decode_step = []
     if not args.skip_decode_step:
         layer_bytes = sum(tb.weight_bytes(f, n, k) for _, n, k, f, _ in LAYER)
+        assert layer_bytes == sum(tb.weight_bytes(f, n, k) for _, n, k, f, _ in LAYER_FUSED)
         layer_w = [[synth.make_weights(f, n // world, k, seed=5000 + 10 * layer + j + 100 * rank, device=device)
-                    for j, (_, n, k, f, _) in enumerate(LAYER)] for layer in range(LAYERS)]
+                    for j, (_, n, k, f, _) in enumerate(LAYER_FUSED)] for layer in range(LAYERS)]
         step_arena = PeerArena(48 << 20, device, rank, world) if world > 1 else None
         step_pads = step_arena.pad_ptrs() if world > 1 else None
         for b in (1, 16):
             xs = {g: synth.make_activations(b, k, seed=40 + g, device=device)
                   for g, k in ((0, 4096), (1, 4096), (2, 4096), (3, 12288))}
-            # the q4_k projections of a layer in one list (q+k and gate+up pair up), the q6_k down projection in its own
-            q4 = ShardedGemvList([(xs[g], layer_w[0][j], f, n, k) for j, (_, n, k, f, g) in enumerate(LAYER) if f == "q4_k"],
+            # the q4_k weights of a layer in one list, the q6_k down projection in its own
+            q4 = ShardedGemvList([(xs[g], layer_w[0][j], f, n, k) for j, (_, n, k, f, g) in enumerate(LAYER_FUSED) if f == "q4_k"],
                                  step_arena, rank, world)
-            q6 = ShardedGemvList([(xs[3], layer_w[0][6], "q6_k", LAYER[6][1], LAYER[6][2])], step_arena, rank, world)
+            q6 = ShardedGemvList([(xs[3], layer_w[0][3], "q6_k", LAYER_FUSED[3][1], LAYER_FUSED[3][2])], step_arena, rank, world)
 
             def whole_step():
                 for layer in range(LAYERS):
-                    for j in range(6):
+                    for j in range(3):
                         q4.rebind(j, w=layer_w[layer][j])
                     q4.forward()
-                    q6.rebind(0, w=layer_w[layer][6])
+                    q6.rebind(0, w=layer_w[layer][3])
                     q6.forward()
 
             def step_wait():
@@ -605,8 +657,11 @@ def run_gpu(args):
                 "ms": t_ms, "gbps": total / (t_ms * 1e-3) / 1e9,
                 "frac_of_hbm_peak": total / world / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                 "e2e_ms": e2e_ms, "e2e_gbps": total / (e2e_ms * 1e-3) / 1e9,
-                "note": "q/k/v, o, gate/up in Q4_K (q+k and gate+up as grouped launches), down in Q6_K; projections "
-                        "only (no attention or glue); 121.5 MB of distinct weights per layer, so every launch streams from HBM"})
+                "launches_per_layer": 4,
+                "note": "q/k/v, o, gate/up in Q4_K, down in Q6_K; the rows of q, k, v live in one 6144-row weight and those of "
+                        "gate, up in one 24576-row weight (concatenated at load time), so a layer is four GEMV launches; "
+                        "projections only (no attention or glue); 121.5 MB of distinct weights per layer, so every launch "
+                        "streams from HBM"})
             del q4, q6, gs
         del layer_w
         torch.cuda.empty_cache()

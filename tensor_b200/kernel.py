@@ -47,7 +47,7 @@ class GgufKernel:
         self._scratch = None
         if op == "gemv" and torch.cuda.is_available():
             with torch.cuda.device(self.device):
-                need = ops.gemv_scratch_bytes(self.format, self.m, self.n, self.k)
+                need = ops.gemv_scratch_bytes(self.format, self.m, self.n, self.k, variant=variant, x_dtype=self.x_dtype)
             if need:
                 self._scratch = torch.zeros(need, dtype=torch.uint8, device=self.device)
 

@@ -14,6 +14,7 @@ from .formats import get_format
 
 _TORCH_DTYPE_IDS = {torch.uint8: 3, torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
 _VARIANTS = {"auto": 0, "simple": 1, "fast": 2, "mma": 3, "tc": 4, 0: 0, 1: 1, 2: 2, 3: 3, 4: 4}
+_X_DTYPE_NAMES = {"float16": 10, "float32": 11, "bfloat16": 13, torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
 GEMV_LIST_MAX = 12
 
 
@@ -63,9 +64,16 @@ def weight_bytes(encoding, n: int, k: int) -> int:
     return get_format(encoding).weight_bytes(n, k)
 
 
-def gemv_scratch_bytes(encoding, m: int, n: int, k: int) -> int:
-    """Scratch the GEMV can use at this shape on the current device (0: never splits K)."""
-    return int(lib().tb200_gguf_gemv_scratch_bytes(get_format(encoding).type_id, m, n, k))
+def gemv_scratch_bytes(encoding, m: int, n: int, k: int, variant="auto", x_dtype="bfloat16") -> int:
+    """Scratch the GEMV can use at this shape on the current device (0: never splits K).  The tensor-memory
+    kernel (``variant="tc"``) keeps its converted activations and partial sums there and cannot run without it."""
+    fmt = get_format(encoding)
+    if _VARIANTS[variant] == _VARIANTS["tc"]:
+        item = abi.TB200GemvItem()
+        item.format, item.x_dtype = fmt.type_id, _X_DTYPE_NAMES[x_dtype]
+        item.m, item.n, item.k, item.out_count, item.out_ld = m, n, k, 1, n
+        return int(lib().tb200_gguf_gemv_list_scratch_bytes(ctypes.byref(item), 1))
+    return int(lib().tb200_gguf_gemv_scratch_bytes(fmt.type_id, m, n, k))
 
 
 def gemv_plan(encoding, m: int, n: int, k: int, scratch_bytes: int = 1 << 40) -> dict:
