@@ -292,8 +292,20 @@ def run_gpu(args):
     ring += ring % 2  # even: the two output copies of the N-sharded lists alternate from slot to slot
     weights = [[synth.make_weights(fmt, n // world, k, seed=1000 * slot + 10 * j + rank, device=device)
                 for j, (_, n, k) in enumerate(SHAPES)] for slot in range(ring)]
-    acts = {b: [synth.make_activations(b, k, seed=7 * b + j, device=device) for j, (_, _, k) in enumerate(SHAPES)]
-            for b in BATCHES}
+    # the activations of a step are views of ONE device buffer, so that they arrive from the host in one copy
+    acts_src = {b: [synth.make_activations(b, k, seed=7 * b + j, device=device) for j, (_, _, k) in enumerate(SHAPES)]
+                for b in BATCHES}
+    x_all = torch.empty(sum(acts_src[b][j].numel() for b in BATCHES for j in (0, 2)), dtype=torch.bfloat16, device=device)
+    acts, taken = {}, 0
+    for b in BATCHES:
+        acts[b] = [None, None, None]
+        for j in (0, 2):  # gate and up read the same activations
+            t = acts_src[b][j]
+            acts[b][j] = x_all[taken:taken + t.numel()].view_as(t)
+            acts[b][j].copy_(t)
+            taken += t.numel()
+        acts[b][1] = acts[b][0]
+    del acts_src
     # gate and up read the same activations: neighbours in the list, one grouped launch
     lists = {b: ShardedGemvList([(acts[b][0], weights[0][0], fmt, SHAPES[0][1], SHAPES[0][2]),
                                  (acts[b][0], weights[0][1], fmt, SHAPES[1][1], SHAPES[1][2]),
@@ -432,8 +444,6 @@ def run_gpu(args):
             cases.append(single_case(f"q4_k gate 18944x3584 alone, batch {b}", "q4_k", 18944, 3584, b, torch.bfloat16, 11))
 
     # ---- end to end: host buffers in, host buffers out, every step ----
-    x_live = {b: [acts[b][0], acts[b][2]] for b in BATCHES}
-    x_host = {b: [a.cpu().pin_memory() for a in x_live[b]] for b in BATCHES}
     # one GPU: the whole result comes back; N-sharded: every rank reads back the columns it computed (its window
     # of each gathered output), so the host-side result is the concatenation of the ranks' buffers and the
     # read-back uses every GPU's own PCIe link instead of rank 0's alone
@@ -441,63 +451,29 @@ def run_gpu(args):
         n_local = t.shape[1] // world
         return t[:, rank * n_local:(rank + 1) * n_local]
 
-    y_host = {b: [torch.empty(tuple(window(o).shape), dtype=torch.float32).pin_memory() for o in graph_outs[0][b]]
-              for b in BATCHES}
-    h2d = sum(t.numel() * t.element_size() for b in BATCHES for t in x_host[b])
-    d2h = sum(t.numel() * 4 for b in BATCHES for t in y_host[b]) * world  # all ranks together
+    x_host = x_all.cpu().pin_memory()
+    y_elems = sum(window(o).numel() for b in BATCHES for o in graph_outs[0][b])
+    y_stage = torch.empty(y_elems, dtype=torch.float32, device=device)  # a step's results, gathered for one copy out
+    y_host = torch.empty(y_elems, dtype=torch.float32).pin_memory()
+    h2d = x_host.numel() * x_host.element_size()
+    d2h = y_elems * 4 * world  # all ranks together
 
     # Every step copies every activation in from pinned host memory (on every rank: activations are
-    # replicated) and every result back out (on rank 0: one copy of the result is what a caller
-    # receives).  The copies ride on two side streams ordered by events per batch: the largest batch
-    # runs first, so its outputs travel while the smaller batches compute, and the inputs of the next
-    # step's batch b go in as soon as this step's batch b has been computed.
+    # replicated) and every result back out, on two side streams ordered by events.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    order = sorted(BATCHES, reverse=True)
-    ev_in = {b: torch.cuda.Event() for b in BATCHES}
-    ev_out = {b: torch.cuda.Event() for b in BATCHES}
-    ev_done = {b: torch.cuda.Event() for b in BATCHES}
 
-    def copy_in(b):
-        with torch.cuda.stream(s_in):
-            for dst, src in zip(x_live[b], x_host[b]):
-                dst.copy_(src, non_blocking=True)
-            ev_in[b].record(s_in)
-
-    def outs_of(b, i):
-        # the output copy that replay i of a batch graph writes: the copies alternate from slot to slot
-        return lists[b].outputs((i % ring) % 2 if world > 1 else 0)
-
-    def e2e_step_batches(i):
-        for b in order:
-            stream.wait_event(ev_in[b])
-            stream.wait_event(ev_out[b])
-            with torch.cuda.stream(stream):
-                batch_graphs[b][i % ring].replay()
-                ev_done[b].record(stream)
-            if rank == 0:
-                s_out.wait_event(ev_done[b])
-                with torch.cuda.stream(s_out):
-                    for dst, src in zip(y_host[b], outs_of(b, i)):
-                        dst.copy_(src, non_blocking=True)
-                    ev_out[b].record(s_out)
-            s_in.wait_event(ev_done[b])
-            copy_in(b)  # the next step's inputs of this batch
-
-    # N-sharded runs: the gathered outputs exist in two copies that alternate from step to step, so a
-    # whole step goes out as ONE graph launch and ONE wait for the peers' stores, and its results travel
-    # to the host while the next step computes into the other copy.
+    # The outputs exist in two copies that alternate from step to step, so a whole step goes out as ONE
+    # graph launch, and its results travel to the host while the next step computes into the other copy.
     step_in = torch.cuda.Event()
     step_done = [torch.cuda.Event(), torch.cuda.Event()]
     step_out = [torch.cuda.Event(), torch.cuda.Event()]
 
     def copy_in_all():
         with torch.cuda.stream(s_in):
-            for b in BATCHES:
-                for dst, src in zip(x_live[b], x_host[b]):
-                    dst.copy_(src, non_blocking=True)
+            x_all.copy_(x_host, non_blocking=True)
             step_in.record(s_in)
 
-    def e2e_step_sharded(i):
+    def e2e_step(i):
         par = i & 1
         stream.wait_event(step_in)         # this step's inputs have arrived
         stream.wait_event(step_out[par])   # the output copy this step overwrites has been read out
@@ -509,12 +485,9 @@ def run_gpu(args):
         # a rank's own columns are written by its own kernels: they are complete when its step is
         s_out.wait_event(step_done[par])
         with torch.cuda.stream(s_out):
-            for b in BATCHES:
-                for dst, src in zip(y_host[b], graph_outs[i % ring][b]):
-                    dst.copy_(window(src), non_blocking=True)
+            torch.cat([window(o).reshape(-1) for b in BATCHES for o in graph_outs[i % ring][b]], out=y_stage)
+            y_host.copy_(y_stage, non_blocking=True)
             step_out[par].record(s_out)
-
-    e2e_step = e2e_step_sharded if world > 1 else e2e_step_batches
 
     def e2e_drain():
         with torch.cuda.stream(stream):
@@ -523,9 +496,6 @@ def run_gpu(args):
             st.synchronize()
 
     torch.cuda.synchronize(device)
-    for b in BATCHES:
-        ev_out[b].record(s_out)
-        copy_in(b)
     for ev in step_out:
         ev.record(s_out)
     copy_in_all()
@@ -541,9 +511,9 @@ def run_gpu(args):
     e2e = {"value": step_bytes_total * args.steps / e2e_s / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "note": "activations from pinned host memory on every rank and the results back to it, every step, on copy "
-                   "streams ordered by events (one GPU: per batch, largest batch first; N-sharded: one graph launch per "
-                   "step, every rank reads back the columns it computed while the next step computes into the other "
-                   "copy of the outputs; d2h bytes are the sum over ranks); weights resident"}
+                   "streams ordered by events: one graph launch per step, its results (N-sharded: the columns each rank "
+                   "computed; d2h bytes are the sum over ranks) read back while the next step computes into the other "
+                   "copy of the outputs; weights resident"}
 
     # free the weight ring before the next parts
     del weights, graphs, batch_graphs, graph_outs

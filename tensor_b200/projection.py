@@ -297,7 +297,8 @@ class ShardedGemvList:
     ``[n, k]`` weight, ``x`` the replicated ``[m, k]`` activations.  Every rank ends with every full
     ``[m, n]`` output: the kernels store their columns into all ranks' outputs (peer-mapped memory of
     ``arena``), the first launch of a call waits for the peers' previous signal, the last one signals.
-    Outputs exist twice and calls alternate between the copies (see :class:`FusedGatherGroup`).
+    Outputs exist twice and calls alternate between the copies (see :class:`FusedGatherGroup`; on one GPU the
+    second copy lets a step's results be read out while the next step computes).
     With ``world == 1`` no arena is needed and the outputs are ordinary tensors."""
 
     def __init__(self, specs, arena=None, rank: int = 0, world: int = 1, variant="auto"):
@@ -316,7 +317,7 @@ class ShardedGemvList:
                 raise ValueError(f"raw holds {raw.numel()} bytes; {n_local} rows of K={k} need {fmt.weight_bytes(n_local, k)}")
             m = x.numel() // k
             self.weight_bytes_local += raw.numel()
-            for copy in range(2 if world > 1 else 1):
+            for copy in range(2):
                 if world > 1:
                     offset = arena.take(m * n * 4)
                     out = arena.view(offset, (m, n))
