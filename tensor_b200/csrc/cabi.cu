@@ -314,6 +314,17 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (int32_t s = require_device(error, &dev)) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint8_t* wp = static_cast<const uint8_t*>(w);
+  // Q6_K at batch 1: the integer dot-product kernel (measured about three times as fast as the tensor-memory
+  // kernel there).  Not on N-sharded launches: the peer signalling lives in the other kernels.
+  if (format == kQ6_K && m == 1 && (variant == TB200_VARIANT_AUTO || variant == TB200_VARIANT_FAST) &&
+      !(peers && peers->flags) && gemv_dp4a_supported(format, x_dtype, m, n, k)) {
+    const long long need = gemv_dp4a_scratch_bytes(n, k, *dev);
+    if (need == 0 || (scratch && scratch_bytes >= need)) {
+      cudaError_t e = launch_gemv_dp4a(x_dtype, x, wp, out, n, k, scratch, scratch_bytes, st);
+      if (e != cudaSuccess) return cuda_fail(error, "integer dot-product GEMV launch", e);
+      return ok(error);
+    }
+  }
   // The tensor-memory kernel: on request, and by default for Q6_K, which has no other pipelined GEMV
   // (measured 1.0x .. 10x faster than the SIMT kernels there).  For Q4_K it is measured slower than the
   // mma.sync pipeline at every batch on B200, so the default never picks it.

@@ -1,0 +1,327 @@
+// Batch-1 decode GEMV for Q6_K on the integer dot-product units: out[n] = sum_k dequant(w[n, k]) * x[k].
+//
+// Replaces the reference's `gemv_packed` (benchmarks/kernels/showcase/kernels.py:116-119) for the Q6_K
+// projections of a decoder at batch 1, where no tensor-core form pays: at one activation row an MMA
+// wastes all but one of its columns, and the 6-bit decode costs more than the dot product itself.
+//
+// Regime: HBM-bound, so everything serves streaming 210-byte blocks with as few instructions per
+// weight as possible, all of them exact.
+//
+//  * Activations as 8-bit integers, without rounding: the CTA converts all K activations once.  Every
+//    run of 32 values is scaled by the power of two that puts its largest magnitude in [32, 64) and split into three signed 8-bit limbs, x = l0 + l1 / 2^7 + l2 / 2^14 (exact for
+//    every value within 2^-12 of the run's largest, 2^-21 of it in absolute terms otherwise).
+//  * Weights as the signed bytes q - 32: nibble | bit pair << 4, minus 32, four at a time.
+//  * `dp4a` (four 8-bit products per lane and instruction) against each limb, int32 sums per
+//    16-weight scale group; the limbs are joined with two shifts, and d * scale is applied in fp32.
+//  * A warp owns eight consecutive blocks of every row it takes (1680 bytes, a multiple of 16): it copies
+//    them into shared memory with 16-byte asynchronous copies, three rows ahead, perfectly coalesced
+//    whatever the 2-byte alignment of the blocks; four lanes share a block (64 weights each: both
+//    nibbles of 32 `ql` bytes) and read it back through aligned words and a funnel shift of 0 or 16 bits.
+//    The lanes keep their 64 activations (48 registers of limbs) for the whole launch.
+//  * The warps that share a row meet every eight rows (hardware named barrier) and add their sums in
+//    warp order: deterministic, no scratch, no atomics.
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kMaxWarps = 16;               // warps per CTA at most
+constexpr int kSegBlocks = 8;               // blocks of a row one warp takes: 8 x 210 = 1680 bytes, a multiple of 16
+constexpr int kSegBytes = kSegBlocks * 210;
+constexpr int kSegChunks = kSegBytes / 16;  // 105 16-byte copies
+constexpr int kStages = 3;                  // row segments in flight per warp
+constexpr int kBatch = 8;                   // rows between two meetings of the warps that share a row
+
+struct DpArgs {
+  const uint16_t* x;   // [k] bf16 or fp16
+  const uint8_t* w;    // [n, k] raw Q6_K blocks
+  float* outs[kMaxOutputs];
+  int n_out;
+  long long row_bytes;
+  int n, k, warps_per_row, streams, rows_per_cta;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void stream_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// 32 bytes of shared memory from a 2-byte aligned address: nine aligned words, re-joined by a funnel shift of
+// 0 or 16 bits (the same code for every lane; only the shift differs)
+__device__ __forceinline__ void lds32_unaligned(uint32_t addr, uint32_t shift, uint32_t (&out)[8]) {
+  const uint32_t base = addr & ~3u;
+  uint32_t w[9];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(base + 4 * i));
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = __funnelshift_r(w[i], w[i + 1], shift);
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
+// This lane's 64 weights of one staged block against its activations.  `blk`: the block in shared memory; h, jj:
+// which 32 `ql` bytes (64 h + 32 jj) the lane owns.  xa / xb: limbs of the activations that meet the low / high
+// nibbles; ua / ub: the factors that undo their scales.
+__device__ __forceinline__ float block_part(uint32_t blk, uint32_t shift, int h, int jj, const uint32_t (&xa)[3][8],
+                                            const uint32_t (&xb)[3][8], float ua, float ub) {
+  uint32_t ql[8], qh[8];
+  lds32_unaligned(blk + 64 * h + 32 * jj, shift, ql);
+  lds32_unaligned(blk + 128 + 32 * h, shift, qh);
+  const uint32_t sca = lds_u16(blk + 192 + 8 * h + 2 * jj);      // scales of the two groups of the low nibbles
+  const uint32_t scb = lds_u16(blk + 192 + 8 * h + 2 * jj + 4);  // ... of the high nibbles
+  const float d = __half2float(__ushort_as_half((unsigned short)lds_u16(blk + 208)));
+  int sa[2][3] = {{0, 0, 0}, {0, 0, 0}}, sb[2][3] = {{0, 0, 0}, {0, 0, 0}};
+  const int sh_a = 2 * jj, sh_b = 2 * jj + 4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t qa = __vsub4((ql[i] & 0x0F0F0F0Fu) | (((qh[i] >> sh_a) & 0x03030303u) << 4), 0x20202020u);
+    const uint32_t qb = __vsub4(((ql[i] >> 4) & 0x0F0F0F0Fu) | (((qh[i] >> sh_b) & 0x03030303u) << 4), 0x20202020u);
+    const int g = i >> 2;  // words 0..3: the first 16 weights of the run, one scale group
+#pragma unroll
+    for (int l = 0; l < 3; ++l) {
+      sa[g][l] = __dp4a((int)qa, (int)xa[l][i], sa[g][l]);
+      sb[g][l] = __dp4a((int)qb, (int)xb[l][i], sb[g][l]);
+    }
+  }
+  float ta = 0.f, tb = 0.f;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int ja = (sa[g][0] << 14) + (sa[g][1] << 7) + sa[g][2];
+    const int jb = (sb[g][0] << 14) + (sb[g][1] << 7) + sb[g][2];
+    ta = fmaf((float)(int)(signed char)((sca >> (8 * g)) & 0xFF), (float)ja, ta);
+    tb = fmaf((float)(int)(signed char)((scb >> (8 * g)) & 0xFF), (float)jb, tb);
+  }
+  return d * (ta * ua + tb * ub);
+}
+
+// Shared memory: limbs of all K activations [3][k], the factors of their runs of 32 [k / 32], the sums the
+// warps of a row exchange, then per warp kStages row segments.
+template <bool F16>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const DpArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint8_t* xl = smem;                                                      // [3][k]
+  float* unscale = reinterpret_cast<float*>(smem + 3 * (size_t)a.k);       // [k / 32]
+  float* red = unscale + a.k / 32;                                         // [2][kMaxWarps][kBatch]
+  uint8_t* stages = reinterpret_cast<uint8_t*>(red + 2 * kMaxWarps * kBatch);  // 16-byte aligned: k is a multiple of 2048
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int threads = blockDim.x;
+
+  ptx::grid_launch_dependents();
+
+  // ---- which rows and which eight blocks of them this warp streams ----
+  const int stream = warp / a.warps_per_row, seg = warp % a.warps_per_row;
+  const int row0 = blockIdx.x * a.rows_per_cta;
+  const int row_end = min(a.n, row0 + a.rows_per_cta);
+  const int my_rows = row0 + stream < row_end ? (row_end - row0 - stream + a.streams - 1) / a.streams : 0;
+  const uint8_t* src0 = a.w + (size_t)(row0 + stream) * a.row_bytes + (size_t)seg * kSegBytes;
+  const size_t row_step = (size_t)a.streams * a.row_bytes;
+  const uint32_t stage0 = ptx::smem_addr(stages) + (uint32_t)warp * (kStages * kSegBytes);
+  auto fetch = [&](int i) {  // row i of this warp's sequence -> stage i % kStages (weights never depend on the kernel before)
+    if (i < my_rows) {
+      const uint8_t* src = src0 + (size_t)i * row_step;
+      const uint32_t dst = stage0 + (uint32_t)(i % kStages) * kSegBytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int chunk = lane + 32 * c;
+        if (chunk < kSegChunks) cp_async16(dst + 16 * chunk, src + 16 * chunk);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) fetch(i);
+
+  // ---- all K activations -> three 8-bit limbs per value (they may come from the kernel before) ----
+  ptx::grid_dependency_wait();
+  for (int v0 = 8 * tid; v0 < a.k; v0 += 8 * threads) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(a.x + v0);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t mx = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));  // a run of 32 values is four neighbouring threads
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const int e = F16 ? (int)(mx >> 10) : (int)(mx >> 7);
+    const int bias = F16 ? 15 : 127, emax = F16 ? 31 : 255;
+    int sh = 0;
+    if (e > 0 && e < emax) sh = bias + 5 - e;
+    sh = sh > 100 ? 100 : (sh < -100 ? -100 : sh);
+    const float scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+    // a run that holds a NaN or an infinity has no limbs: its factor makes every output NaN
+    if ((tid & 3) == 0)
+      unscale[v0 >> 5] = e >= emax ? __uint_as_float(0x7FC00000u) : __uint_as_float((uint32_t)(127 - sh - 14) << 23);
+    uint32_t limb[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float f;
+      if constexpr (F16) {
+        f = __half2float(__ushort_as_half((unsigned short)((w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu)));
+      } else {
+        f = __uint_as_float((i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16));
+      }
+      f *= scale;
+      const float x = fabsf(f) < 64.f ? f : 0.f;  // only a non-finite value can fail this
+      const float l0 = rintf(x);
+      const float r1 = (x - l0) * 128.f;
+      const float l1 = rintf(r1);
+      const float l2 = rintf((r1 - l1) * 128.f);
+      limb[0][i >> 2] |= ((uint32_t)(int)l0 & 0xFFu) << (8 * (i & 3));
+      limb[1][i >> 2] |= ((uint32_t)(int)l1 & 0xFFu) << (8 * (i & 3));
+      limb[2][i >> 2] |= ((uint32_t)(int)l2 & 0xFFu) << (8 * (i & 3));
+    }
+#pragma unroll
+    for (int l = 0; l < 3; ++l) *reinterpret_cast<uint2*>(xl + (size_t)l * a.k + v0) = make_uint2(limb[l][0], limb[l][1]);
+  }
+  __syncthreads();
+
+  // ---- this lane's 64 activations: block 8 seg + lane / 4 of a row, `ql` bytes 64 h + 32 jj ----
+  const int bi = lane >> 2, u4 = lane & 3;
+  const int h = u4 >> 1, jj = u4 & 1;
+  const int run_a = 256 * (kSegBlocks * seg + bi) + 128 * h + 32 * jj, run_b = run_a + 64;
+  uint32_t xa[3][8], xb[3][8];
+#pragma unroll
+  for (int l = 0; l < 3; ++l) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 va = *reinterpret_cast<const uint4*>(xl + (size_t)l * a.k + run_a + 16 * i);
+      const uint4 vb = *reinterpret_cast<const uint4*>(xl + (size_t)l * a.k + run_b + 16 * i);
+      xa[l][4 * i] = va.x, xa[l][4 * i + 1] = va.y, xa[l][4 * i + 2] = va.z, xa[l][4 * i + 3] = va.w;
+      xb[l][4 * i] = vb.x, xb[l][4 * i + 1] = vb.y, xb[l][4 * i + 2] = vb.z, xb[l][4 * i + 3] = vb.w;
+    }
+  }
+  const float ua = unscale[run_a >> 5], ub = unscale[run_b >> 5];
+  const uint32_t blk_off = 210u * (uint32_t)bi;          // this lane's block inside a staged segment
+  const uint32_t shift = (blk_off & 2u) * 8u;            // segments start on 16-byte boundaries
+
+  // ---- rows: kBatch at a time, then the warps of a row add their sums in warp order ----
+  const int batches = ((a.rows_per_cta + a.streams - 1) / a.streams + kBatch - 1) / kBatch;  // the same for every warp of the CTA
+  int buf = 0;
+  for (int b = 0; b < batches; ++b, buf ^= 1) {
+    float part[kBatch];
+#pragma unroll
+    for (int r = 0; r < kBatch; ++r) {
+      const int i = b * kBatch + r;
+      fetch(i + kStages - 1);
+      cp_async_wait<kStages - 1>();
+      __syncwarp();
+      part[r] = i < my_rows ? block_part(stage0 + (uint32_t)(i % kStages) * kSegBytes + blk_off, shift, h, jj, xa, xb, ua, ub) : 0.f;
+      __syncwarp();  // every lane is done with the stage before the next fetch overwrites it
+    }
+    // sum over the 32 lanes, for the eight rows at once: lane r ends up with row r's sum
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {  // fold 8 -> 4: the upper half-warp keeps rows 4..7
+      const float send = (lane & 16) ? part[r] : part[r + 4];
+      const float keep = (lane & 16) ? part[r + 4] : part[r];
+      part[r] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {  // 4 -> 2
+      const float send = (lane & 8) ? part[r] : part[r + 2];
+      const float keep = (lane & 8) ? part[r + 2] : part[r];
+      part[r] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    {  // 2 -> 1
+      const float send = (lane & 4) ? part[0] : part[1];
+      const float keep = (lane & 4) ? part[1] : part[0];
+      part[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    part[0] += __shfl_xor_sync(0xffffffffu, part[0], 2);
+    part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
+    // lanes with the same bits 4, 3, 2 hold the same row: row index = 4 * bit4 + 2 * bit3 + bit2
+    if ((lane & 3) == 0) red[(buf * kMaxWarps + warp) * kBatch + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = part[0];
+    if (a.warps_per_row > 1) stream_sync(1 + stream, a.warps_per_row * 32);
+    else __syncwarp();
+    if (seg == 0 && lane < kBatch) {
+      const int i = b * kBatch + lane;
+      if (i < my_rows) {
+        float total = 0.f;
+        for (int wi = 0; wi < a.warps_per_row; ++wi) total += red[(buf * kMaxWarps + warp + wi) * kBatch + lane];
+        const long long row = row0 + stream + (long long)i * a.streams;
+        for (int d = 0; d < a.n_out; ++d) a.outs[d][row] = total;
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+struct DpPlan {
+  int warps_per_row, streams, rows_per_cta, grid;
+  size_t smem;
+};
+bool dp_plan(long long n, long long k, const DeviceInfo& dev, DpPlan& plan) {
+  const int nsb = (int)(k / 256);
+  if (nsb % kSegBlocks) return false;
+  plan.warps_per_row = nsb / kSegBlocks;
+  if (plan.warps_per_row > kMaxWarps) return false;
+  plan.streams = kMaxWarps / plan.warps_per_row;
+  // one CTA per SM (the register file holds no second one): the rows in as many chunks as there are SMs
+  long long rows = (n + dev.sm_count - 1) / dev.sm_count;
+  if (rows < plan.streams) rows = plan.streams;
+  plan.rows_per_cta = (int)rows;
+  plan.grid = (int)((n + rows - 1) / rows);
+  plan.smem = 3 * (size_t)k + (size_t)(k / 32) * 4 + 2 * kMaxWarps * kBatch * 4 +
+              (size_t)plan.streams * plan.warps_per_row * kStages * kSegBytes;
+  return plan.smem <= (size_t)dev.max_smem_optin;
+}
+
+}  // namespace
+
+bool gemv_dp4a_supported(int fmt, int xt, long long m, long long n, long long k) {
+  if (fmt != kQ6_K || m != 1) return false;
+  if (xt != kBF16 && xt != kF16) return false;
+  if (n < 1 || n > (1LL << 30) || k < 2048 || k % 2048 || k > 32768) return false;  // rows of whole 8-block segments
+  return true;
+}
+
+long long gemv_dp4a_scratch_bytes(long long, long long, const DeviceInfo&) { return 0; }
+
+cudaError_t launch_gemv_dp4a(int xt, const void* x, const uint8_t* w, const OutSpec& out, long long n, long long k,
+                             void*, long long, cudaStream_t stream) {
+  cudaError_t e;
+  const DeviceInfo* dev = device_info(&e);
+  if (!dev) return e;
+  DpPlan plan;
+  if (!dp_plan(n, k, *dev, plan)) return cudaErrorInvalidValue;
+  if (out.count < 1 || out.count > kMaxOutputs) return cudaErrorInvalidValue;
+  DpArgs a{};
+  a.x = static_cast<const uint16_t*>(x);
+  a.w = w;
+  for (int d = 0; d < out.count; ++d) a.outs[d] = out.ptr[d];
+  a.n_out = out.count;
+  a.row_bytes = row_bytes(kQ6_K, k);
+  a.n = (int)n;
+  a.k = (int)k;
+  a.warps_per_row = plan.warps_per_row;
+  a.streams = plan.streams;
+  a.rows_per_cta = plan.rows_per_cta;
+  auto kernel = xt == kF16 ? gemv_q6k_dp4a_kernel<true> : gemv_q6k_dp4a_kernel<false>;
+  e = allow_full_shared_memory(kernel);
+  if (e != cudaSuccess) return e;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  cfg.blockDim = dim3((unsigned)(plan.streams * plan.warps_per_row * 32));
+  cfg.dynamicSmemBytes = plan.smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+}  // namespace tb200

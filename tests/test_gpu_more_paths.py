@@ -74,6 +74,48 @@ def test_q6k_down_projection_shape():
     _case("q6_k", 1, 4096, 12288, "bf16", "auto")
 
 
+# ---- Q6_K at batch 1: the integer dot-product kernel (what "auto" picks there) --------------------
+
+@pytest.mark.parametrize("n,k,xdt", [(8, 2048, "bf16"), (520, 2048, "bf16"), (300, 4096, "f16"), (4096, 12288, "bf16"),
+                                     (1000, 6144, "bf16"), (33, 18432, "f16"), (5000, 32768, "bf16")])
+def test_q6k_batch1_integer_dot_product(n, k, xdt):
+    """One, two, three, six, nine and sixteen warps per row (K = 2048 ... 32768), row counts that leave the last
+    CTA and the last batch ragged; a second launch must give the same bits."""
+    raw = oracle.make_weights("q6_k", n, k, seed=n + k)
+    x = oracle.make_activations(1, k, seed=n + k + 1, dtype=xdt)
+    want = c_oracle.gemv(x, raw, "q6_k", n, k)
+    kern = tb.gguf(1, n, k, "q6_k", x_dtype={"bf16": "bfloat16", "f16": "float16"}[xdt], op="gemv")
+    xd, wd = to_dev(x, TORCH_X[xdt]), to_dev(raw)
+    results = []
+    for _ in range(2):
+        out = torch.full((1, n), float("nan"), device=dev())
+        kern.launch(xd, wd, out)
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert oracle.rel_frobenius(got, want) < 3e-5  # operands are exact to 2^-21 of a run's largest activation
+        results.append(got)
+    assert np.array_equal(results[0], results[1])
+    # scaled (by a power of two: exact in the activation type) and zero activations
+    kern.launch(xd * -2, wd, out)
+    assert oracle.rel_frobenius(out.cpu().numpy(), -2 * want) < 3e-5
+    kern.launch(torch.zeros_like(xd), wd, out)
+    assert float(out.abs().max()) == 0.0
+
+
+def test_q6k_batch1_tiny_and_huge_activations():
+    """A run of 32 activations is scaled by its own power of two: magnitudes far apart between runs survive."""
+    n, k = 64, 2048
+    raw = oracle.make_weights("q6_k", n, k, seed=5)
+    x = oracle.make_activations(1, k, seed=6, dtype="bf16")  # fp32 values that are exact in bf16
+    x[:, :512] *= np.float32(2.0 ** -40)                      # powers of two keep them so
+    x[:, 512:1024] *= np.float32(2.0 ** 30)
+    xd = to_dev(x, torch.bfloat16)
+    want = c_oracle.gemv(x, raw, "q6_k", n, k)
+    out = torch.full((1, n), float("nan"), device=dev())
+    tb.gguf(1, n, k, "q6_k", op="gemv").launch(xd, to_dev(raw), out)
+    assert oracle.rel_frobenius(out.cpu().numpy(), want) < 3e-5
+
+
 # ---- the persistent tcgen05 / TMEM kernel ---------------------------------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 256), (2, 128, 3584), (4, 300, 1024), (8, 1000, 2048), (16, 2048, 3584),
