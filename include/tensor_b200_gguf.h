@@ -99,7 +99,10 @@ typedef struct TensorErrorV1 {
 #define TB200_VARIANT_FAST 2   /* a pipelined tensor-core kernel or an error: GEMV bulk-copy ring + mma.sync, GEMM tcgen05 */
 #define TB200_VARIANT_MMA 3    /* GEMV only: the same as FAST */
 #define TB200_VARIANT_TC 4     /* GEMV only: the persistent tcgen05 / TMEM kernel (Q4_K, Q6_K; needs scratch), or an
-                                * error.  AUTO picks it for Q6_K; for Q4_K the mma.sync pipeline measures faster */
+                                * error.  AUTO picks it for Q6_K above one activation row; for Q4_K the mma.sync
+                                * pipeline measures faster */
+#define TB200_VARIANT_DP4A 5   /* GEMV only, m = 1, Q4_K / Q6_K: integer dot products against the activations split into
+                                * three exact 8-bit limbs (no scratch), or an error.  AUTO picks it for Q6_K at m = 1 */
 
 /* Library / ABI version: (major << 16) | minor. */
 int32_t tb200_gguf_version(void);

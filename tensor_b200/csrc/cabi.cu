@@ -314,17 +314,19 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (int32_t s = require_device(error, &dev)) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint8_t* wp = static_cast<const uint8_t*>(w);
-  // Q6_K at batch 1: the integer dot-product kernel (measured about three times as fast as the tensor-memory
-  // kernel there).  Not on N-sharded launches: the peer signalling lives in the other kernels.
-  if (format == kQ6_K && m == 1 && (variant == TB200_VARIANT_AUTO || variant == TB200_VARIANT_FAST) &&
-      !(peers && peers->flags) && gemv_dp4a_supported(format, x_dtype, m, n, k)) {
-    const long long need = gemv_dp4a_scratch_bytes(n, k, *dev);
-    if (need == 0 || (scratch && scratch_bytes >= need)) {
-      cudaError_t e = launch_gemv_dp4a(x_dtype, x, wp, out, n, k, scratch, scratch_bytes, st);
-      if (e != cudaSuccess) return cuda_fail(error, "integer dot-product GEMV launch", e);
-      return ok(error);
-    }
+  // Batch 1 of Q6_K (and of Q4_K on request, variant "dp4a"): the integer dot-product kernel, measured about 2.4
+  // times as fast as the tensor-memory kernel for Q6_K (for Q4_K the mma.sync pipeline stays ahead).
+  const bool dp_default = format == kQ6_K && (variant == TB200_VARIANT_AUTO || variant == TB200_VARIANT_FAST);
+  if ((dp_default || variant == TB200_VARIANT_DP4A) && gemv_dp4a_supported(format, x_dtype, m, n, k)) {
+    cudaError_t e = launch_gemv_dp4a(format, x_dtype, x, wp, out, n, k, st, peers);
+    if (e == cudaSuccess) return ok(error);
+    if (e != cudaErrorInvalidValue) return cuda_fail(error, "integer dot-product GEMV launch", e);
   }
+  if (variant == TB200_VARIANT_DP4A)
+    return fail(error, TENSOR_ERROR_ARGUMENT,
+                "the integer dot-product GEMV takes Q4_K or Q6_K at m = 1 with 2-byte activations, K a multiple of 256 "
+                "(2048 for Q6_K) up to 32768 (format %d, dtype %d, m=%lld, n=%lld, k=%lld)",
+                format, x_dtype, (long long)m, (long long)n, (long long)k);
   // The tensor-memory kernel: on request, and by default for Q6_K, which has no other pipelined GEMV
   // (measured 1.0x .. 10x faster than the SIMT kernels there).  For Q4_K it is measured slower than the
   // mma.sync pipeline at every batch on B200, so the default never picks it.
@@ -399,7 +401,7 @@ int32_t check_gemv_scalars(TensorErrorV1* error, int32_t format, int32_t x_dtype
   if (int32_t s = check_shape(error, format, m, n, k)) return s;
   if (x_dtype != TENSOR_FLOAT16 && x_dtype != TENSOR_BFLOAT16 && x_dtype != TENSOR_FLOAT32)
     return fail(error, TENSOR_ERROR_ARGUMENT, "activation dtype %d is not float16, bfloat16 or float32", x_dtype);
-  if (variant < 0 || variant > TB200_VARIANT_TC) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (variant < 0 || variant > TB200_VARIANT_DP4A) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
   return TENSOR_OK;
 }
 
@@ -849,7 +851,7 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
                              void* stream, TensorErrorV1* error) {
   static_assert(TB200_GEMV_LIST_MAX == kTcMaxItems, "list length");
   if (int32_t s = check_list(error, items, count)) return s;
-  if (variant < 0 || variant > TB200_VARIANT_TC) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
+  if (variant < 0 || variant > TB200_VARIANT_DP4A) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown variant %d", variant);
   if (int32_t s = check_pointer(error, "scratch", scratch, 256, false)) return s;
   if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
   if (sync & ~(TB200_PEER_WAIT | TB200_PEER_SIGNAL)) return fail(error, TENSOR_ERROR_ARGUMENT, "unknown sync bits 0x%x", sync);
@@ -887,7 +889,7 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   for (int i = 0; i < count;) {
     const bool pair = i + 1 < count && list[i + 1].x_share == i && items[i + 1].format == items[i].format &&
                       items[i + 1].out_count == items[i].out_count && items[i + 1].out_ld == items[i].out_ld &&
-                      variant != TB200_VARIANT_SIMPLE;
+                      variant != TB200_VARIANT_SIMPLE && variant != TB200_VARIANT_DP4A;
     const int step = pair ? 2 : 1;
     const int flags = (i == 0 ? peers.flags & kPeerWait : 0) | (i + step >= count ? peers.flags & kPeerSignal : 0);
     if (pair) {

@@ -1,4 +1,4 @@
-// Batch-1 decode GEMV for Q6_K on the integer dot-product units: out[n] = sum_k dequant(w[n, k]) * x[k].
+// Batch-1 decode GEMV for Q6_K and Q4_K on the integer dot-product units: out[n] = sum_k dequant(w[n, k]) * x[k].
 //
 // Replaces the reference's `gemv_packed` (benchmarks/kernels/showcase/kernels.py:116-119) for the Q6_K
 // projections of a decoder at batch 1, where no tensor-core form pays: at one activation row an MMA
@@ -20,6 +20,8 @@
 //    The lanes keep their 64 activations (48 registers of limbs) for the whole launch.
 //  * The warps that share a row meet every eight rows (hardware named barrier) and add their sums in
 //    warp order: deterministic, no scratch, no atomics.
+//  * N-sharded launches: the sums go to the same columns of every rank's output (peer stores), one thread
+//    per CTA waits (bounded) for the peers' signal before the activations are read, the last CTA signals.
 #include <cuda_fp16.h>
 
 #include <cstdint>
@@ -32,10 +34,9 @@ namespace tb200 {
 namespace {
 
 constexpr int kMaxWarps = 16;               // warps per CTA at most
-constexpr int kSegBlocks = 8;               // blocks of a row one warp takes: 8 x 210 = 1680 bytes, a multiple of 16
-constexpr int kSegBytes = kSegBlocks * 210;
-constexpr int kSegChunks = kSegBytes / 16;  // 105 16-byte copies
+constexpr int kSegBlocks = 8;               // blocks of a row one warp takes: 8 x 210 = 1680 or 8 x 144 = 1152 bytes, multiples of 16
 constexpr int kStages = 3;                  // row segments in flight per warp
+__host__ __device__ constexpr int dp_block_bytes(int fmt) { return fmt == kQ6_K ? 210 : 144; }
 constexpr int kBatch = 8;                   // rows between two meetings of the warps that share a row
 
 struct DpArgs {
@@ -44,7 +45,11 @@ struct DpArgs {
   float* outs[kMaxOutputs];
   int n_out;
   long long row_bytes;
-  int n, k, warps_per_row, streams, rows_per_cta;
+  int n, k, nsb, warps_per_row, streams, rows_per_cta;
+  // N-sharded launches: signal pads of all ranks (this rank's own is waited on), what to do, and for how long
+  unsigned int* pads[kMaxOutputs];
+  int rank, world, sync;
+  unsigned long long wait_limit_ns;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -108,14 +113,55 @@ __device__ __forceinline__ float block_part(uint32_t blk, uint32_t shift, int h,
   return d * (ta * ua + tb * ub);
 }
 
+// The same for a Q4_K block: the lane owns quant bytes 32 p .. 32 p + 31, whose low nibbles are scale group 2 p
+// and whose high nibbles are group 2 p + 1; sxa / sxb: the sums of the activations that meet them (for the
+// dmin * min terms).  The 6-bit scales and mins come out of the 12 packed bytes with per-lane sources, shifts
+// and masks, so that lanes of the lower and the upper half of a block run the same code.
+struct Q4Lane {
+  int p;
+  bool upper;          // groups 4..7: low four bits in bytes 8..11, high two bits on top of bytes 0..7
+  uint32_t sh, m_lo, m_hi;
+};
+__device__ __forceinline__ float block_part_q4k(uint32_t blk, const Q4Lane& ln, const uint32_t (&xa)[3][8],
+                                                const uint32_t (&xb)[3][8], float ua, float ub, float sxa, float sxb) {
+  const uint4 hdr = ptx::lds128(blk);
+  const uint4 q0 = ptx::lds128(blk + 16 + 32 * ln.p), q1 = ptx::lds128(blk + 32 + 32 * ln.p);
+  const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+  int sa[3] = {0, 0, 0}, sb[3] = {0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t lo = words[i] & 0x0F0F0F0Fu, hi = (words[i] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int l = 0; l < 3; ++l) {
+      sa[l] = __dp4a((int)lo, (int)xa[l][i], sa[l]);
+      sb[l] = __dp4a((int)hi, (int)xb[l][i], sb[l]);
+    }
+  }
+  // scales / mins of groups 2p (low nibbles) and 2p + 1 (high nibbles)
+  const uint32_t sc_src = ln.upper ? hdr.w : hdr.y, mn_src = ln.upper ? (hdr.w >> 4) : hdr.z;
+  const uint32_t sc_lo = ((sc_src >> ln.sh) & ln.m_lo) | (((hdr.y >> (ln.sh + 6)) & ln.m_hi) << 4);
+  const uint32_t sc_hi = ((sc_src >> (ln.sh + 8)) & ln.m_lo) | (((hdr.y >> (ln.sh + 14)) & ln.m_hi) << 4);
+  const uint32_t mn_lo = ((mn_src >> ln.sh) & ln.m_lo) | (((hdr.z >> (ln.sh + 6)) & ln.m_hi) << 4);
+  const uint32_t mn_hi = ((mn_src >> (ln.sh + 8)) & ln.m_lo) | (((hdr.z >> (ln.sh + 14)) & ln.m_hi) << 4);
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // d, dmin
+  const int ja = (sa[0] << 14) + (sa[1] << 7) + sa[2];
+  const int jb = (sb[0] << 14) + (sb[1] << 7) + sb[2];
+  const float dots = (float)sc_lo * ((float)ja * ua) + (float)sc_hi * ((float)jb * ub);
+  const float mins = (float)mn_lo * sxa + (float)mn_hi * sxb;
+  return dd.x * dots - dd.y * mins;
+}
+
 // Shared memory: limbs of all K activations [3][k], the factors of their runs of 32 [k / 32], the sums the
 // warps of a row exchange, then per warp kStages row segments.
-template <bool F16>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const DpArgs a) {
+template <int FMT, bool F16>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpArgs a) {
+  constexpr int kBlockBytes = dp_block_bytes(FMT);
+  constexpr int kSegBytes = kSegBlocks * kBlockBytes;
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* xl = smem;                                                      // [3][k]
   float* unscale = reinterpret_cast<float*>(smem + 3 * (size_t)a.k);       // [k / 32]
-  float* red = unscale + a.k / 32;                                         // [2][kMaxWarps][kBatch]
+  float* xsum = unscale + a.k / 32;                                        // [k / 32]: sums of the runs (Q4_K's min terms)
+  float* red = xsum + a.k / 32;                                            // [2][kMaxWarps][kBatch]
   uint8_t* stages = reinterpret_cast<uint8_t*>(red + 2 * kMaxWarps * kBatch);  // 16-byte aligned: k is a multiple of 2048
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int threads = blockDim.x;
@@ -130,6 +176,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
   const uint8_t* src0 = a.w + (size_t)(row0 + stream) * a.row_bytes + (size_t)seg * kSegBytes;
   const size_t row_step = (size_t)a.streams * a.row_bytes;
   const uint32_t stage0 = ptx::smem_addr(stages) + (uint32_t)warp * (kStages * kSegBytes);
+  const int seg_blocks = min(kSegBlocks, a.nsb - kSegBlocks * seg);  // the last warp of a row may have fewer
+  const int seg_chunks = seg_blocks * kBlockBytes / 16;               // a whole number: 8 x 210 or any number of 144
   auto fetch = [&](int i) {  // row i of this warp's sequence -> stage i % kStages (weights never depend on the kernel before)
     if (i < my_rows) {
       const uint8_t* src = src0 + (size_t)i * row_step;
@@ -137,7 +185,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int chunk = lane + 32 * c;
-        if (chunk < kSegChunks) cp_async16(dst + 16 * chunk, src + 16 * chunk);
+        if (chunk < seg_chunks) cp_async16(dst + 16 * chunk, src + 16 * chunk);
       }
     }
     cp_async_commit();
@@ -147,6 +195,29 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
 
   // ---- all K activations -> three 8-bit limbs per value (they may come from the kernel before) ----
   ptx::grid_dependency_wait();
+  if (a.sync & kPeerWait) {
+    // until every peer has signalled as often as this rank has: their stores into the activations this launch
+    // reads have landed (bounded; gives up with status 0x80000 | peer)
+    if (tid == 0) {
+      const unsigned int* mine = a.pads[a.rank];
+      const unsigned int expected = *reinterpret_cast<const volatile unsigned int*>(mine + 32);
+      const unsigned long long t0 = ptx::global_timer_ns();
+      for (int peer = 0; peer < a.world; ++peer) {
+        if (peer == a.rank) continue;
+        for (;;) {
+          unsigned int seen;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + peer) : "memory");
+          if ((int)(seen - expected) >= 0) break;
+          if (ptx::global_timer_ns() - t0 > a.wait_limit_ns) {
+            report_timeout(0x80000u | (unsigned)peer);
+            break;
+          }
+          __nanosleep(100);
+        }
+      }
+    }
+    __syncthreads();
+  }
   for (int v0 = 8 * tid; v0 < a.k; v0 += 8 * threads) {
     const uint4 raw = *reinterpret_cast<const uint4*>(a.x + v0);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -165,6 +236,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
     if ((tid & 3) == 0)
       unscale[v0 >> 5] = e >= emax ? __uint_as_float(0x7FC00000u) : __uint_as_float((uint32_t)(127 - sh - 14) << 23);
     uint32_t limb[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
+    float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float f;
@@ -179,19 +251,30 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
       const float r1 = (x - l0) * 128.f;
       const float l1 = rintf(r1);
       const float l2 = rintf((r1 - l1) * 128.f);
+      sum += l0 + l1 * (1.f / 128.f) + l2 * (1.f / 16384.f);
       limb[0][i >> 2] |= ((uint32_t)(int)l0 & 0xFFu) << (8 * (i & 3));
       limb[1][i >> 2] |= ((uint32_t)(int)l1 & 0xFFu) << (8 * (i & 3));
       limb[2][i >> 2] |= ((uint32_t)(int)l2 & 0xFFu) << (8 * (i & 3));
     }
 #pragma unroll
     for (int l = 0; l < 3; ++l) *reinterpret_cast<uint2*>(xl + (size_t)l * a.k + v0) = make_uint2(limb[l][0], limb[l][1]);
+    if constexpr (FMT == kQ4_K) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if ((tid & 3) == 0) xsum[v0 >> 5] = e >= emax ? __uint_as_float(0x7FC00000u) : sum * __uint_as_float((uint32_t)(127 - sh) << 23);
+    }
   }
   __syncthreads();
 
-  // ---- this lane's 64 activations: block 8 seg + lane / 4 of a row, `ql` bytes 64 h + 32 jj ----
+  // ---- this lane's 64 activations: a quarter (u4) of block 8 seg + lane / 4 of a row ----
+  // Q6_K: `ql` bytes 64 h + 32 jj, whose low nibbles are elements 128 h + 32 jj .. and whose high nibbles are
+  // the elements 64 further on.  Q4_K: quant bytes 32 u4 .., low nibbles = elements 64 u4 .., high = 32 further on.
   const int bi = lane >> 2, u4 = lane & 3;
+  const bool has_block = bi < seg_blocks;
   const int h = u4 >> 1, jj = u4 & 1;
-  const int run_a = 256 * (kSegBlocks * seg + bi) + 128 * h + 32 * jj, run_b = run_a + 64;
+  const int block0 = 256 * (kSegBlocks * seg + (has_block ? bi : 0));
+  const int run_a = FMT == kQ6_K ? block0 + 128 * h + 32 * jj : block0 + 64 * u4;
+  const int run_b = FMT == kQ6_K ? run_a + 64 : run_a + 32;
   uint32_t xa[3][8], xb[3][8];
 #pragma unroll
   for (int l = 0; l < 3; ++l) {
@@ -204,8 +287,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
     }
   }
   const float ua = unscale[run_a >> 5], ub = unscale[run_b >> 5];
-  const uint32_t blk_off = 210u * (uint32_t)bi;          // this lane's block inside a staged segment
-  const uint32_t shift = (blk_off & 2u) * 8u;            // segments start on 16-byte boundaries
+  const float sxa = xsum[run_a >> 5], sxb = xsum[run_b >> 5];  // read for Q4_K only
+  const uint32_t blk_off = (uint32_t)kBlockBytes * (uint32_t)bi;  // this lane's block inside a staged segment
+  const uint32_t shift = (blk_off & 2u) * 8u;                     // Q6_K: segments start on 16-byte boundaries
+  Q4Lane q4;
+  q4.p = u4;
+  q4.upper = u4 >= 2;
+  q4.sh = 16u * (uint32_t)(u4 & 1);
+  q4.m_lo = q4.upper ? 15u : 63u;
+  q4.m_hi = q4.upper ? 3u : 0u;
 
   // ---- rows: kBatch at a time, then the warps of a row add their sums in warp order ----
   const int batches = ((a.rows_per_cta + a.streams - 1) / a.streams + kBatch - 1) / kBatch;  // the same for every warp of the CTA
@@ -218,7 +308,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
       fetch(i + kStages - 1);
       cp_async_wait<kStages - 1>();
       __syncwarp();
-      part[r] = i < my_rows ? block_part(stage0 + (uint32_t)(i % kStages) * kSegBytes + blk_off, shift, h, jj, xa, xb, ua, ub) : 0.f;
+      const uint32_t blk = stage0 + (uint32_t)(i % kStages) * kSegBytes + blk_off;
+      float v = 0.f;
+      if (i < my_rows && has_block) {
+        if constexpr (FMT == kQ6_K) v = block_part(blk, shift, h, jj, xa, xb, ua, ub);
+        else v = block_part_q4k(blk, q4, xa, xb, ua, ub, sxa, sxb);
+      }
+      part[r] = v;
       __syncwarp();  // every lane is done with the stage before the next fetch overwrites it
     }
     // sum over the 32 lanes, for the eight rows at once: lane r ends up with row r's sum
@@ -256,16 +352,32 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_q6k_dp4a_kernel(const 
     }
   }
   cp_async_wait<0>();
+  if (a.sync & kPeerSignal) {
+    // every warp of this CTA has stored what it will store; the last CTA of the grid tells the peers
+    __syncthreads();
+    if (tid == 0) {
+      unsigned int* mine = a.pads[a.rank];
+      __threadfence();
+      if (atomicAdd(mine + 34, 1u) == gridDim.x - 1) {
+        __threadfence_system();
+        mine[34] = 0u;
+        const unsigned int epoch = mine[32] + 1u;
+        mine[32] = epoch;
+        for (int peer = 0; peer < a.world; ++peer)
+          if (peer != a.rank)
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.pads[peer] + a.rank), "r"(epoch) : "memory");
+      }
+    }
+  }
 }
 
 struct DpPlan {
   int warps_per_row, streams, rows_per_cta, grid;
   size_t smem;
 };
-bool dp_plan(long long n, long long k, const DeviceInfo& dev, DpPlan& plan) {
+bool dp_plan(int fmt, long long n, long long k, const DeviceInfo& dev, DpPlan& plan) {
   const int nsb = (int)(k / 256);
-  if (nsb % kSegBlocks) return false;
-  plan.warps_per_row = nsb / kSegBlocks;
+  plan.warps_per_row = (nsb + kSegBlocks - 1) / kSegBlocks;
   if (plan.warps_per_row > kMaxWarps) return false;
   plan.streams = kMaxWarps / plan.warps_per_row;
   // one CTA per SM (the register file holds no second one): the rows in as many chunks as there are SMs
@@ -273,42 +385,55 @@ bool dp_plan(long long n, long long k, const DeviceInfo& dev, DpPlan& plan) {
   if (rows < plan.streams) rows = plan.streams;
   plan.rows_per_cta = (int)rows;
   plan.grid = (int)((n + rows - 1) / rows);
-  plan.smem = 3 * (size_t)k + (size_t)(k / 32) * 4 + 2 * kMaxWarps * kBatch * 4 +
-              (size_t)plan.streams * plan.warps_per_row * kStages * kSegBytes;
+  plan.smem = 3 * (size_t)k + 2 * (size_t)(k / 32) * 4 + 2 * kMaxWarps * kBatch * 4 +
+              (size_t)plan.streams * plan.warps_per_row * kStages * kSegBlocks * dp_block_bytes(fmt);
   return plan.smem <= (size_t)dev.max_smem_optin;
 }
 
 }  // namespace
 
 bool gemv_dp4a_supported(int fmt, int xt, long long m, long long n, long long k) {
-  if (fmt != kQ6_K || m != 1) return false;
+  if ((fmt != kQ6_K && fmt != kQ4_K) || m != 1) return false;
   if (xt != kBF16 && xt != kF16) return false;
-  if (n < 1 || n > (1LL << 30) || k < 2048 || k % 2048 || k > 32768) return false;  // rows of whole 8-block segments
+  if (n < 1 || n > (1LL << 30) || k < 256 || k % 256 || k > 32768) return false;
+  if (fmt == kQ6_K && k % 2048) return false;  // rows of whole 8-block segments: every segment starts on a 16-byte boundary
   return true;
 }
 
 long long gemv_dp4a_scratch_bytes(long long, long long, const DeviceInfo&) { return 0; }
 
-cudaError_t launch_gemv_dp4a(int xt, const void* x, const uint8_t* w, const OutSpec& out, long long n, long long k,
-                             void*, long long, cudaStream_t stream) {
+cudaError_t launch_gemv_dp4a(int fmt, int xt, const void* x, const uint8_t* w, const OutSpec& out, long long n,
+                             long long k, cudaStream_t stream, const PeerSync* peers) {
   cudaError_t e;
   const DeviceInfo* dev = device_info(&e);
   if (!dev) return e;
   DpPlan plan;
-  if (!dp_plan(n, k, *dev, plan)) return cudaErrorInvalidValue;
+  if (!dp_plan(fmt, n, k, *dev, plan)) return cudaErrorInvalidValue;
   if (out.count < 1 || out.count > kMaxOutputs) return cudaErrorInvalidValue;
   DpArgs a{};
   a.x = static_cast<const uint16_t*>(x);
   a.w = w;
   for (int d = 0; d < out.count; ++d) a.outs[d] = out.ptr[d];
   a.n_out = out.count;
-  a.row_bytes = row_bytes(kQ6_K, k);
+  a.row_bytes = row_bytes(fmt, k);
   a.n = (int)n;
   a.k = (int)k;
+  a.nsb = (int)(k / 256);
   a.warps_per_row = plan.warps_per_row;
   a.streams = plan.streams;
   a.rows_per_cta = plan.rows_per_cta;
-  auto kernel = xt == kF16 ? gemv_q6k_dp4a_kernel<true> : gemv_q6k_dp4a_kernel<false>;
+  a.wait_limit_ns = peer_wait_limit_ns();
+  if (peers && peers->flags) {
+    if (peers->world < 1 || peers->world > kMaxOutputs || peers->rank < 0 || peers->rank >= peers->world)
+      return cudaErrorInvalidValue;
+    for (int i = 0; i < peers->world; ++i) a.pads[i] = peers->pads[i];
+    a.rank = peers->rank;
+    a.world = peers->world;
+    a.sync = peers->flags;
+  }
+  void (*kernel)(const DpArgs) =
+      fmt == kQ6_K ? (xt == kF16 ? gemv_dp4a_kernel<kQ6_K, true> : gemv_dp4a_kernel<kQ6_K, false>)
+                   : (xt == kF16 ? gemv_dp4a_kernel<kQ4_K, true> : gemv_dp4a_kernel<kQ4_K, false>);
   e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
   cudaLaunchAttribute attr[1];

@@ -140,12 +140,11 @@ struct TcLaunchItem {
   long long m, n, k;
   int x_share;
 };
-// Q6_K at batch 1 on the integer dot-product units (gemv_dp4a.cu): activations as three exact 8-bit limbs.
-// Scratch (counters + K-slice partial sums, zeroed before first use) is needed when K exceeds 4096.
+// Q6_K and Q4_K at batch 1 on the integer dot-product units (gemv_dp4a.cu): activations as three exact 8-bit
+// limbs; no scratch.
 bool gemv_dp4a_supported(int fmt, int xt, long long m, long long n, long long k);
-long long gemv_dp4a_scratch_bytes(long long n, long long k, const DeviceInfo& dev);
-cudaError_t launch_gemv_dp4a(int xt, const void* x, const uint8_t* w, const OutSpec& out, long long n, long long k,
-                             void* scratch, long long scratch_bytes, cudaStream_t stream);
+cudaError_t launch_gemv_dp4a(int fmt, int xt, const void* x, const uint8_t* w, const OutSpec& out, long long n,
+                             long long k, cudaStream_t stream, const PeerSync* peers = nullptr);
 
 bool gemv_tc_supported(int fmt, int xt, long long m, long long n, long long k);
 // Scratch a list needs (arrival counters, partial sums of row tiles that span CTAs, converted

@@ -13,7 +13,7 @@ from ._native import lib, raise_for_status
 from .formats import get_format
 
 _TORCH_DTYPE_IDS = {torch.uint8: 3, torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
-_VARIANTS = {"auto": 0, "simple": 1, "fast": 2, "mma": 3, "tc": 4, 0: 0, 1: 1, 2: 2, 3: 3, 4: 4}
+_VARIANTS = {"auto": 0, "simple": 1, "fast": 2, "mma": 3, "tc": 4, "dp4a": 5, 0: 0, 1: 1, 2: 2, 3: 3, 4: 4, 5: 5}
 _X_DTYPE_NAMES = {"float16": 10, "float32": 11, "bfloat16": 13, torch.float16: 10, torch.float32: 11, torch.bfloat16: 13}
 GEMV_LIST_MAX = 12
 

@@ -102,6 +102,29 @@ def test_q6k_batch1_integer_dot_product(n, k, xdt):
     assert float(out.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("n,k,xdt", [(64, 256, "bf16"), (300, 1024, "f16"), (1000, 2304, "bf16"), (18944, 3584, "bf16"),
+                                     (3584, 18944, "bf16"), (777, 32768, "f16")])
+def test_q4k_batch1_integer_dot_product(n, k, xdt):
+    """The same kernel on Q4_K blocks (an explicit variant): rows whose last warp holds fewer than eight blocks,
+    one to sixteen warps per row."""
+    raw = oracle.make_weights("q4_k", n, k, seed=n + k)
+    x = oracle.make_activations(1, k, seed=n + k + 1, dtype=xdt)
+    want = c_oracle.gemv(x, raw, "q4_k", n, k)
+    kern = tb.gguf(1, n, k, "q4_k", x_dtype={"bf16": "bfloat16", "f16": "float16"}[xdt], op="gemv", variant="dp4a")
+    xd, wd = to_dev(x, TORCH_X[xdt]), to_dev(raw)
+    results = []
+    for _ in range(2):
+        out = torch.full((1, n), float("nan"), device=dev())
+        kern.launch(xd, wd, out)
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert oracle.rel_frobenius(got, want) < 3e-5
+        results.append(got)
+    assert np.array_equal(results[0], results[1])
+    kern.launch(torch.zeros_like(xd), wd, out)
+    assert float(out.abs().max()) == 0.0
+
+
 def test_q6k_batch1_tiny_and_huge_activations():
     """A run of 32 activations is scaled by its own power of two: magnitudes far apart between runs survive."""
     n, k = 64, 2048

@@ -115,6 +115,42 @@ def _rank_main(rank, world, port, result_path):
         for t in range(calls):
             ok &= bool(torch.equal(snaps[t], want[2] * float(2 ** (t % 3))))
         ok &= tb.device_status() == 0
+    # Q6_K under N-sharding: batch 1 runs on the integer dot-product kernel (peer stores + signalling inside
+    # it; rows are summed in a fixed order, so the gathered result is bit-identical to the local one),
+    # batch 4 on the persistent tensor-memory kernel (its segment order may differ: close)
+    n6, k6 = 2048, 4096
+    full6 = synth.make_weights("q6_k", n6, k6, seed=77, device=dev)
+    for m in (1, 4):
+        x6 = synth.make_activations(m, k6, seed=78 + m, device=dev)
+        kern = tb.gguf(m, n6 // world, k6, "q6_k", op="gemv", device=dev)
+        want6 = torch.cat([kern(x6, shard_weight_bytes(full6, "q6_k", n6, k6, r, world).clone()) for r in range(world)], dim=1)
+        lin6 = QuantLinear(shard_weight_bytes(full6, "q6_k", n6, k6, rank, world).clone(), "q6_k", n6, k6, m,
+                           rank=rank, world=world)
+        chain6 = FusedGatherGroup([lin6], arena, fold_sync=True)
+        for copy in range(2):
+            for t in chain6.outputs(copy):
+                t.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        calls = 8
+        snaps = torch.zeros((calls,) + tuple(want6.shape), device=dev)
+        scaled = [(x6.float() * float(2 ** (t % 3))).to(torch.bfloat16) for t in range(calls)]
+        for t in range(calls):
+            out = chain6.forward([scaled[t]])[0]
+            chain6.wait()
+            if rank == 1:
+                for _ in range(2):
+                    ballast = ballast @ ballast * 1e-4
+            snaps[t].copy_(out)
+        torch.cuda.synchronize()
+        for t in range(calls):
+            ref = want6 * float(2 ** (t % 3))
+            if m == 1:
+                ok &= bool(torch.equal(snaps[t], ref))
+            else:
+                ok &= not bool(torch.isnan(snaps[t]).any())
+                ok &= float((snaps[t] - ref).norm() / ref.norm()) < 2e-5
+        ok &= tb.device_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()
