@@ -557,7 +557,7 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
   for (int i = 0; i < out_count; ++i)
     if (!outs1[i] || !outs2[i]) return fail(error, TENSOR_ERROR_ARGUMENT, "a destination of rank slot %d is null", i);
   const int64_t n = n1 + n2;
-  if (m > 0 && n1 > 0 && n2 > 0 && variant != TB200_VARIANT_SIMPLE) {
+  if (m > 0 && n1 > 0 && n2 > 0 && variant != TB200_VARIANT_SIMPLE && variant != TB200_VARIANT_DP4A) {
     PeerSync peers{};
     if (sync) {
       if (int32_t s = check_pads(error, pads, rank, world)) return s;

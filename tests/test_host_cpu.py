@@ -228,5 +228,5 @@ def test_gemv_pair_validates_before_touching_a_device():
     assert call(fmt=7) == 2
     assert call(k=100) == 2
     assert call(n2=-1) == 2
-    assert call(variant=5) == 2
+    assert call(variant=6) == 2
     assert call() == 3  # well-formed: stops at the missing device, never computes on the CPU
