@@ -101,8 +101,9 @@ typedef struct TensorErrorV1 {
 #define TB200_VARIANT_TC 4     /* GEMV only: the persistent tcgen05 / TMEM kernel (Q4_K, Q6_K; needs scratch), or an
                                 * error.  AUTO picks it for Q6_K above one activation row; for Q4_K the mma.sync
                                 * pipeline measures faster */
-#define TB200_VARIANT_DP4A 5   /* GEMV only, m = 1, Q4_K / Q6_K: integer dot products against the activations split into
-                                * three exact 8-bit limbs (no scratch), or an error.  AUTO picks it for Q6_K at m = 1 */
+#define TB200_VARIANT_DP4A 5   /* GEMV only, m = 1, every format: integer dot products against the activations split into
+                                * three exact 8-bit limbs (no scratch), or an error.  AUTO picks it at m = 1 for Q6_K,
+                                * Q8_0 and Q4_0 */
 
 /* Library / ABI version: (major << 16) | minor. */
 int32_t tb200_gguf_version(void);

@@ -314,9 +314,11 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (int32_t s = require_device(error, &dev)) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint8_t* wp = static_cast<const uint8_t*>(w);
-  // Batch 1 of Q6_K (and of Q4_K on request, variant "dp4a"): the integer dot-product kernel, measured about 2.4
-  // times as fast as the tensor-memory kernel for Q6_K (for Q4_K the mma.sync pipeline stays ahead).
-  const bool dp_default = format == kQ6_K && (variant == TB200_VARIANT_AUTO || variant == TB200_VARIANT_FAST);
+  // Batch 1 of Q6_K, Q8_0 and Q4_0 (and of Q4_K on request, variant "dp4a"): the integer dot-product kernel,
+  // measured about 2.4 times as fast as the tensor-memory kernel for Q6_K (for Q4_K the mma.sync pipeline stays
+  // ahead; FAST / MMA still name the bulk-copy ring for the formats it covers).
+  const bool dp_default = (format == kQ6_K && (variant == TB200_VARIANT_AUTO || variant == TB200_VARIANT_FAST)) ||
+                          ((format == kQ8_0 || format == kQ4_0) && variant == TB200_VARIANT_AUTO);
   if ((dp_default || variant == TB200_VARIANT_DP4A) && gemv_dp4a_supported(format, x_dtype, m, n, k)) {
     cudaError_t e = launch_gemv_dp4a(format, x_dtype, x, wp, out, n, k, st, peers);
     if (e == cudaSuccess) return ok(error);
@@ -324,7 +326,7 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   }
   if (variant == TB200_VARIANT_DP4A)
     return fail(error, TENSOR_ERROR_ARGUMENT,
-                "the integer dot-product GEMV takes Q4_K or Q6_K at m = 1 with 2-byte activations, K a multiple of 256 "
+                "the integer dot-product GEMV takes m = 1 with 2-byte activations, K a multiple of 256 "
                 "(2048 for Q6_K) up to 32768 (format %d, dtype %d, m=%lld, n=%lld, k=%lld)",
                 format, x_dtype, (long long)m, (long long)n, (long long)k);
   // The tensor-memory kernel: on request, and by default for Q6_K, which has no other pipelined GEMV

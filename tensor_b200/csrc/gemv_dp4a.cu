@@ -34,9 +34,10 @@ namespace tb200 {
 namespace {
 
 constexpr int kMaxWarps = 16;               // warps per CTA at most
-constexpr int kSegBlocks = 8;               // blocks of a row one warp takes: 8 x 210 = 1680 or 8 x 144 = 1152 bytes, multiples of 16
+constexpr int kSegBlocks = 8;               // 256-weight blocks of a row one warp takes: 8 x 210 = 1680, 8 x 144 = 1152 or 8 x 272 = 2176 bytes, multiples of 16
 constexpr int kStages = 3;                  // row segments in flight per warp
-__host__ __device__ constexpr int dp_block_bytes(int fmt) { return fmt == kQ6_K ? 210 : 144; }
+// bytes of 256 weights: one Q6_K or Q4_K block, eight Q8_0 or Q4_0 blocks
+__host__ __device__ constexpr int dp_block_bytes(int fmt) { return fmt == kQ6_K ? 210 : fmt == kQ8_0 ? 272 : 144; }
 constexpr int kBatch = 8;                   // rows between two meetings of the warps that share a row
 
 struct DpArgs {
@@ -78,11 +79,22 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
   return v;
 }
 
+// four unsigned bytes against four signed bytes
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int join_limbs(const int (&s)[3]) { return (s[0] << 14) + (s[1] << 7) + s[2]; }
+
 // This lane's 64 weights of one staged block against its activations.  `blk`: the block in shared memory; h, jj:
 // which 32 `ql` bytes (64 h + 32 jj) the lane owns.  xa / xb: limbs of the activations that meet the low / high
-// nibbles; ua / ub: the factors that undo their scales.
+// nibbles; ua / ub: the factors that undo their scales; ca / cb: 32 x the joined limb sums of the four 16-value
+// groups (the weights stay unsigned, q = nibble | bit pair << 4, and sum (q - 32) x = sum q x - 32 sum x, all in
+// integers).  The bit pairs reach bits 4-5 of their bytes by one rotation of the `qh` word.
 __device__ __forceinline__ float block_part(uint32_t blk, uint32_t shift, int h, int jj, const uint32_t (&xa)[3][8],
-                                            const uint32_t (&xb)[3][8], float ua, float ub) {
+                                            const uint32_t (&xb)[3][8], float ua, float ub, const int (&ca)[2],
+                                            const int (&cb)[2]) {
   uint32_t ql[8], qh[8];
   lds32_unaligned(blk + 64 * h + 32 * jj, shift, ql);
   lds32_unaligned(blk + 128 + 32 * h, shift, qh);
@@ -90,27 +102,75 @@ __device__ __forceinline__ float block_part(uint32_t blk, uint32_t shift, int h,
   const uint32_t scb = lds_u16(blk + 192 + 8 * h + 2 * jj + 4);  // ... of the high nibbles
   const float d = __half2float(__ushort_as_half((unsigned short)lds_u16(blk + 208)));
   int sa[2][3] = {{0, 0, 0}, {0, 0, 0}}, sb[2][3] = {{0, 0, 0}, {0, 0, 0}};
-  const int sh_a = 2 * jj, sh_b = 2 * jj + 4;
+  const uint32_t rot_a = (uint32_t)(2 * jj + 28) & 31u, rot_b = (uint32_t)(2 * jj);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint32_t qa = __vsub4((ql[i] & 0x0F0F0F0Fu) | (((qh[i] >> sh_a) & 0x03030303u) << 4), 0x20202020u);
-    const uint32_t qb = __vsub4(((ql[i] >> 4) & 0x0F0F0F0Fu) | (((qh[i] >> sh_b) & 0x03030303u) << 4), 0x20202020u);
+    const uint32_t qa = (ql[i] & 0x0F0F0F0Fu) | (__funnelshift_r(qh[i], qh[i], rot_a) & 0x30303030u);
+    const uint32_t qb = ((ql[i] >> 4) & 0x0F0F0F0Fu) | (__funnelshift_r(qh[i], qh[i], rot_b) & 0x30303030u);
     const int g = i >> 2;  // words 0..3: the first 16 weights of the run, one scale group
 #pragma unroll
     for (int l = 0; l < 3; ++l) {
-      sa[g][l] = __dp4a((int)qa, (int)xa[l][i], sa[g][l]);
-      sb[g][l] = __dp4a((int)qb, (int)xb[l][i], sb[g][l]);
+      sa[g][l] = dp4a_us(qa, xa[l][i], sa[g][l]);
+      sb[g][l] = dp4a_us(qb, xb[l][i], sb[g][l]);
     }
   }
   float ta = 0.f, tb = 0.f;
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
-    const int ja = (sa[g][0] << 14) + (sa[g][1] << 7) + sa[g][2];
-    const int jb = (sb[g][0] << 14) + (sb[g][1] << 7) + sb[g][2];
+    const int ja = join_limbs(sa[g]) - ca[g];
+    const int jb = join_limbs(sb[g]) - cb[g];
     ta = fmaf((float)(int)(signed char)((sca >> (8 * g)) & 0xFF), (float)ja, ta);
     tb = fmaf((float)(int)(signed char)((scb >> (8 * g)) & 0xFF), (float)jb, tb);
   }
   return d * (ta * ua + tb * ub);
+}
+
+// Q8_0: the lane owns two 34-byte blocks (fp16 d, 32 signed bytes) at `part` = block + 68 * (lane % 4), a 4-byte
+// aligned address: the first block's quants sit 2 bytes off the word grid, the second block's on it.
+__device__ __forceinline__ float block_part_q80(uint32_t part, const uint32_t (&xa)[3][8], const uint32_t (&xb)[3][8],
+                                                float ua, float ub) {
+  uint32_t w[17];
+#pragma unroll
+  for (int i = 0; i < 17; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(part + 4 * i));
+  int sa[3] = {0, 0, 0}, sb[3] = {0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t qa = __funnelshift_r(w[i], w[i + 1], 16), qb = w[9 + i];
+#pragma unroll
+    for (int l = 0; l < 3; ++l) {
+      sa[l] = __dp4a((int)qa, (int)xa[l][i], sa[l]);
+      sb[l] = __dp4a((int)qb, (int)xb[l][i], sb[l]);
+    }
+  }
+  const float d0 = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+  const float d1 = __half2float(__ushort_as_half((unsigned short)(w[8] >> 16)));
+  return d0 * ((float)join_limbs(sa) * ua) + d1 * ((float)join_limbs(sb) * ub);
+}
+
+// Q4_0: two 18-byte blocks (fp16 d, 16 bytes: low nibbles = weights 0..15, high nibbles = weights 16..31, each
+// minus 8) at `part` = block + 36 * (lane % 4); ca / cb: 8 x the joined limb sums of the two runs.
+__device__ __forceinline__ float block_part_q40(uint32_t part, const uint32_t (&xa)[3][8], const uint32_t (&xb)[3][8],
+                                                float ua, float ub, int ca, int cb) {
+  uint32_t w[9];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(part + 4 * i));
+  int sa[3] = {0, 0, 0}, sb[3] = {0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t qa = __funnelshift_r(w[i], w[i + 1], 16), qb = w[5 + i];
+    const uint32_t qa_lo = qa & 0x0F0F0F0Fu, qa_hi = (qa >> 4) & 0x0F0F0F0Fu;
+    const uint32_t qb_lo = qb & 0x0F0F0F0Fu, qb_hi = (qb >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int l = 0; l < 3; ++l) {
+      sa[l] = dp4a_us(qa_lo, xa[l][i], sa[l]);
+      sa[l] = dp4a_us(qa_hi, xa[l][4 + i], sa[l]);
+      sb[l] = dp4a_us(qb_lo, xb[l][i], sb[l]);
+      sb[l] = dp4a_us(qb_hi, xb[l][4 + i], sb[l]);
+    }
+  }
+  const float d0 = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+  const float d1 = __half2float(__ushort_as_half((unsigned short)(w[4] >> 16)));
+  return d0 * ((float)(join_limbs(sa) - ca) * ua) + d1 * ((float)(join_limbs(sb) - cb) * ub);
 }
 
 // The same for a Q4_K block: the lane owns quant bytes 32 p .. 32 p + 31, whose low nibbles are scale group 2 p
@@ -151,8 +211,9 @@ __device__ __forceinline__ float block_part_q4k(uint32_t blk, const Q4Lane& ln, 
   return dd.x * dots - dd.y * mins;
 }
 
-// Shared memory: limbs of all K activations [3][k], the factors of their runs of 32 [k / 32], the sums the
-// warps of a row exchange, then per warp kStages row segments.
+// Shared memory: limbs of all K activations [3][k], the factors of their runs of 32 [k / 32], the sums of the
+// runs and the integer limb sums of the groups of 16 (for mins and offsets), the sums the warps of a row
+// exchange, then per warp kStages row segments.
 template <int FMT, bool F16>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpArgs a) {
   constexpr int kBlockBytes = dp_block_bytes(FMT);
@@ -161,7 +222,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
   uint8_t* xl = smem;                                                      // [3][k]
   float* unscale = reinterpret_cast<float*>(smem + 3 * (size_t)a.k);       // [k / 32]
   float* xsum = unscale + a.k / 32;                                        // [k / 32]: sums of the runs (Q4_K's min terms)
-  float* red = xsum + a.k / 32;                                            // [2][kMaxWarps][kBatch]
+  int* jsum = reinterpret_cast<int*>(xsum + a.k / 32);                     // [k / 16]: joined limb sums of the groups of 16
+  float* red = reinterpret_cast<float*>(jsum + a.k / 16);                  // [2][kMaxWarps][kBatch]
   uint8_t* stages = reinterpret_cast<uint8_t*>(red + 2 * kMaxWarps * kBatch);  // 16-byte aligned: k is a multiple of 2048
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int threads = blockDim.x;
@@ -183,7 +245,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
       const uint8_t* src = src0 + (size_t)i * row_step;
       const uint32_t dst = stage0 + (uint32_t)(i % kStages) * kSegBytes;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < (kSegBytes / 16 + 31) / 32; ++c) {
         const int chunk = lane + 32 * c;
         if (chunk < seg_chunks) cp_async16(dst + 16 * chunk, src + 16 * chunk);
       }
@@ -237,6 +299,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
       unscale[v0 >> 5] = e >= emax ? __uint_as_float(0x7FC00000u) : __uint_as_float((uint32_t)(127 - sh - 14) << 23);
     uint32_t limb[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
     float sum = 0.f;
+    int joined = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float f;
@@ -252,12 +315,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
       const float l1 = rintf(r1);
       const float l2 = rintf((r1 - l1) * 128.f);
       sum += l0 + l1 * (1.f / 128.f) + l2 * (1.f / 16384.f);
+      joined += ((int)l0 << 14) + ((int)l1 << 7) + (int)l2;
       limb[0][i >> 2] |= ((uint32_t)(int)l0 & 0xFFu) << (8 * (i & 3));
       limb[1][i >> 2] |= ((uint32_t)(int)l1 & 0xFFu) << (8 * (i & 3));
       limb[2][i >> 2] |= ((uint32_t)(int)l2 & 0xFFu) << (8 * (i & 3));
     }
 #pragma unroll
     for (int l = 0; l < 3; ++l) *reinterpret_cast<uint2*>(xl + (size_t)l * a.k + v0) = make_uint2(limb[l][0], limb[l][1]);
+    if constexpr (FMT == kQ6_K || FMT == kQ4_0) {
+      joined += __shfl_xor_sync(0xffffffffu, joined, 1);  // a group of 16 values is two neighbouring threads
+      if ((tid & 1) == 0) jsum[v0 >> 4] = joined;
+    }
     if constexpr (FMT == kQ4_K) {
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -269,6 +337,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
   // ---- this lane's 64 activations: a quarter (u4) of block 8 seg + lane / 4 of a row ----
   // Q6_K: `ql` bytes 64 h + 32 jj, whose low nibbles are elements 128 h + 32 jj .. and whose high nibbles are
   // the elements 64 further on.  Q4_K: quant bytes 32 u4 .., low nibbles = elements 64 u4 .., high = 32 further on.
+  // Q8_0 / Q4_0: two blocks of 32, elements 64 u4 .. and 64 u4 + 32 ...
   const int bi = lane >> 2, u4 = lane & 3;
   const bool has_block = bi < seg_blocks;
   const int h = u4 >> 1, jj = u4 & 1;
@@ -288,6 +357,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
   }
   const float ua = unscale[run_a >> 5], ub = unscale[run_b >> 5];
   const float sxa = xsum[run_a >> 5], sxb = xsum[run_b >> 5];  // read for Q4_K only
+  int ca[2] = {0, 0}, cb[2] = {0, 0};                          // offsets: 32 sum x per group of 16 (Q6_K), 8 sum x per run (Q4_0)
+  if constexpr (FMT == kQ6_K) {
+    ca[0] = 32 * jsum[run_a >> 4], ca[1] = 32 * jsum[(run_a >> 4) + 1];
+    cb[0] = 32 * jsum[run_b >> 4], cb[1] = 32 * jsum[(run_b >> 4) + 1];
+  } else if constexpr (FMT == kQ4_0) {
+    ca[0] = 8 * (jsum[run_a >> 4] + jsum[(run_a >> 4) + 1]);
+    cb[0] = 8 * (jsum[run_b >> 4] + jsum[(run_b >> 4) + 1]);
+  }
   const uint32_t blk_off = (uint32_t)kBlockBytes * (uint32_t)bi;  // this lane's block inside a staged segment
   const uint32_t shift = (blk_off & 2u) * 8u;                     // Q6_K: segments start on 16-byte boundaries
   Q4Lane q4;
@@ -311,8 +388,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
       const uint32_t blk = stage0 + (uint32_t)(i % kStages) * kSegBytes + blk_off;
       float v = 0.f;
       if (i < my_rows && has_block) {
-        if constexpr (FMT == kQ6_K) v = block_part(blk, shift, h, jj, xa, xb, ua, ub);
-        else v = block_part_q4k(blk, q4, xa, xb, ua, ub, sxa, sxb);
+        if constexpr (FMT == kQ6_K) v = block_part(blk, shift, h, jj, xa, xb, ua, ub, ca, cb);
+        else if constexpr (FMT == kQ4_K) v = block_part_q4k(blk, q4, xa, xb, ua, ub, sxa, sxb);
+        else if constexpr (FMT == kQ8_0) v = block_part_q80(blk + 68u * (uint32_t)u4, xa, xb, ua, ub);
+        else v = block_part_q40(blk + 36u * (uint32_t)u4, xa, xb, ua, ub, ca[0], cb[0]);
       }
       part[r] = v;
       __syncwarp();  // every lane is done with the stage before the next fetch overwrites it
@@ -385,7 +464,7 @@ bool dp_plan(int fmt, long long n, long long k, const DeviceInfo& dev, DpPlan& p
   if (rows < plan.streams) rows = plan.streams;
   plan.rows_per_cta = (int)rows;
   plan.grid = (int)((n + rows - 1) / rows);
-  plan.smem = 3 * (size_t)k + 2 * (size_t)(k / 32) * 4 + 2 * kMaxWarps * kBatch * 4 +
+  plan.smem = 3 * (size_t)k + 2 * (size_t)(k / 32) * 4 + (size_t)(k / 16) * 4 + 2 * kMaxWarps * kBatch * 4 +
               (size_t)plan.streams * plan.warps_per_row * kStages * kSegBlocks * dp_block_bytes(fmt);
   return plan.smem <= (size_t)dev.max_smem_optin;
 }
@@ -393,7 +472,7 @@ bool dp_plan(int fmt, long long n, long long k, const DeviceInfo& dev, DpPlan& p
 }  // namespace
 
 bool gemv_dp4a_supported(int fmt, int xt, long long m, long long n, long long k) {
-  if ((fmt != kQ6_K && fmt != kQ4_K) || m != 1) return false;
+  if ((fmt != kQ6_K && fmt != kQ4_K && fmt != kQ8_0 && fmt != kQ4_0) || m != 1) return false;
   if (xt != kBF16 && xt != kF16) return false;
   if (n < 1 || n > (1LL << 30) || k < 256 || k % 256 || k > 32768) return false;
   if (fmt == kQ6_K && k % 2048) return false;  // rows of whole 8-block segments: every segment starts on a 16-byte boundary
@@ -431,9 +510,12 @@ cudaError_t launch_gemv_dp4a(int fmt, int xt, const void* x, const uint8_t* w, c
     a.world = peers->world;
     a.sync = peers->flags;
   }
+  const bool f16 = xt == kF16;
   void (*kernel)(const DpArgs) =
-      fmt == kQ6_K ? (xt == kF16 ? gemv_dp4a_kernel<kQ6_K, true> : gemv_dp4a_kernel<kQ6_K, false>)
-                   : (xt == kF16 ? gemv_dp4a_kernel<kQ4_K, true> : gemv_dp4a_kernel<kQ4_K, false>);
+      fmt == kQ6_K   ? (f16 ? gemv_dp4a_kernel<kQ6_K, true> : gemv_dp4a_kernel<kQ6_K, false>)
+      : fmt == kQ4_K ? (f16 ? gemv_dp4a_kernel<kQ4_K, true> : gemv_dp4a_kernel<kQ4_K, false>)
+      : fmt == kQ8_0 ? (f16 ? gemv_dp4a_kernel<kQ8_0, true> : gemv_dp4a_kernel<kQ8_0, false>)
+                     : (f16 ? gemv_dp4a_kernel<kQ4_0, true> : gemv_dp4a_kernel<kQ4_0, false>);
   e = allow_full_shared_memory(kernel);
   if (e != cudaSuccess) return e;
   cudaLaunchAttribute attr[1];

@@ -125,6 +125,35 @@ def test_q4k_batch1_integer_dot_product(n, k, xdt):
     assert float(out.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("encoding", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("n,k,xdt", [(64, 256, "bf16"), (300, 1024, "f16"), (1000, 2304, "bf16"), (4096, 4096, "bf16"),
+                                     (4096, 12288, "f16"), (555, 32768, "bf16")])
+def test_blocks_of_32_batch1_integer_dot_product(encoding, n, k, xdt):
+    """Q8_0 and Q4_0 on the integer dot-product kernel (eight blocks of 32 stand for one block of 256): against
+    the oracle, finite, bit-identical from launch to launch, and the same answer as the explicit variant."""
+    raw = oracle.make_weights(encoding, n, k, seed=n + k)
+    x = oracle.make_activations(1, k, seed=n + k + 1, dtype=xdt)
+    want = c_oracle.gemv(x, raw, encoding, n, k)
+    x_dtype = {"bf16": "bfloat16", "f16": "float16"}[xdt]
+    xd, wd = to_dev(x, TORCH_X[xdt]), to_dev(raw)
+    results = []
+    for variant in ("dp4a", "dp4a", "auto"):
+        kern = tb.gguf(1, n, k, encoding, x_dtype=x_dtype, op="gemv", variant=variant)
+        out = torch.full((1, n), float("nan"), device=dev())
+        kern.launch(xd, wd, out)
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert oracle.rel_frobenius(got, want) < 3e-5
+        results.append(got)
+    assert np.array_equal(results[0], results[1])
+    kern.launch(torch.zeros_like(xd), wd, out)
+    assert float(out.abs().max()) == 0.0
+    # twice the activations (exact in bf16 / fp16): twice the result, bit for bit
+    kern = tb.gguf(1, n, k, encoding, x_dtype=x_dtype, op="gemv", variant="dp4a")
+    kern.launch((xd.float() * -2.0).to(xd.dtype), wd, out)
+    assert np.array_equal(out.cpu().numpy(), results[0] * np.float32(-2.0))
+
+
 def test_q6k_batch1_tiny_and_huge_activations():
     """A run of 32 activations is scaled by its own power of two: magnitudes far apart between runs survive."""
     n, k = 64, 2048
