@@ -84,7 +84,8 @@ def workload_config(world: int):
         "format": FORMAT, "batches": list(BATCHES), "activations": "bf16", "output": "fp32",
         "l2": "weights rotate over a ring of sets > 3x L2; every launch streams from HBM",
         "parallelism": f"N-sharded x{world}" + ("" if world == 1 else
-            " + peer stores in the GEMV epilogue over NVLink, signal/wait between ranks inside the same launches"),
+            " + peer stores in the GEMV epilogue over NVLink, signal/wait between ranks inside the same launches "
+            "(the nine projections of a step go out as one list: one wait and one signal per step)"),
     }
 
 
@@ -311,10 +312,21 @@ def run_gpu(args):
                                  (acts[b][0], weights[0][1], fmt, SHAPES[1][1], SHAPES[1][2]),
                                  (acts[b][2], weights[0][2], fmt, SHAPES[2][1], SHAPES[2][2])],
                                 arena, rank, world) for b in BATCHES}
+    # The three batches of a step are independent of one another: the step issues all nine projections as ONE
+    # list, so an N-sharded step waits for its peers once and signals them once (the per-batch lists above
+    # serve the per-batch rows).
+    step_list = ShardedGemvList([(acts[b][0 if j < 2 else 2], weights[0][j], fmt, SHAPES[j][1], SHAPES[j][2])
+                                 for b in BATCHES for j in range(3)], arena, rank, world)
     launches_per_step = 2 * len(BATCHES)
     prepare_per_step = 2 * sum(1 for b in BATCHES if b > 1)  # activation conversion ahead of batched GEMVs
 
     def step(slot, batches=BATCHES):
+        if tuple(batches) == tuple(BATCHES):
+            for i in range(len(BATCHES)):
+                for j in range(3):
+                    step_list.rebind(3 * i + j, w=weights[slot][j])
+            flat = step_list.forward()
+            return {b: flat[3 * i:3 * i + 3] for i, b in enumerate(BATCHES)}
         outs = {}
         for b in batches:
             for j in range(3):
@@ -438,8 +450,8 @@ def run_gpu(args):
                 "frac_of_hbm_peak": nbytes / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], "samples": len(samples)}
 
     if world == 1:
-        cases.append(single_case("q8_0 4096x4096 fp16 (first configuration)", "q8_0", 4096, 4096, 1, torch.float16, 24))
-        cases.append(single_case("q6_k down 4096x12288 bf16", "q6_k", 4096, 12288, 1, torch.bfloat16, 12))
+        cases.append(single_case("q8_0 4096x4096 fp16 (first configuration; gemv_dp4a_kernel)", "q8_0", 4096, 4096, 1, torch.float16, 24))
+        cases.append(single_case("q6_k down 4096x12288 bf16 (gemv_dp4a_kernel)", "q6_k", 4096, 12288, 1, torch.bfloat16, 12))
         for b in BATCHES:
             cases.append(single_case(f"q4_k gate 18944x3584 alone, batch {b}", "q4_k", 18944, 3584, b, torch.bfloat16, 11))
 
@@ -628,7 +640,8 @@ def run_gpu(args):
                 "frac_of_hbm_peak": total / world / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                 "e2e_ms": e2e_ms, "e2e_gbps": total / (e2e_ms * 1e-3) / 1e9,
                 "launches_per_layer": 4,
-                "note": "q/k/v, o, gate/up in Q4_K, down in Q6_K; the rows of q, k, v live in one 6144-row weight and those of "
+                "note": "q/k/v, o, gate/up in Q4_K (gemv_mma_kernel), down in Q6_K (batch 1: gemv_dp4a_kernel, batch 16: "
+                        "gemv_tc_kernel); the rows of q, k, v live in one 6144-row weight and those of "
                         "gate, up in one 24576-row weight (concatenated at load time), so a layer is four GEMV launches; "
                         "projections only (no attention or glue); 121.5 MB of distinct weights per layer, so every launch "
                         "streams from HBM"})
