@@ -1255,6 +1255,10 @@ GemvPlan plan_gemv_fast(int fmt, int xt, long long m, long long n, long long k,
       // time ~ bytes the busiest SM streams, plus the partial-sum traffic and sync of a split
       double cost = (double)per_sm * tiles_per_cta * per * block_bytes(fmt) * kTileRows;
       if (splits > 1) cost += per_sm * ((double)tiles_per_cta * kTileRows * m * 4 * 2 + 2000.0 * tiles_per_cta);
+      // ... and the latency of its extra phase (partial sums out, counter, the last CTA's sum): about 2 us,
+      // in bytes an SM streams meanwhile (fewer at larger batches, where the decode sets the pace).  Measured
+      // at batch 1: 3072 x 4096 runs 4.4 us unsplit and 11.6 us on the split this term now rules out.
+      if (splits > 1) cost += m == 1 ? 50000.0 : m <= 4 ? 40000.0 : m <= 8 ? 30000.0 : 20000.0;
       // per-row bulk copies of ~2 KB run far below HBM speed (each costs a few hundred cycles)
       if (splits > 1 && !tma_ok(fmt, per)) cost *= 3.0;
       // the decode warps are latency-bound: a second CTA on the SM is worth more than a perfect split
