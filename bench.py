@@ -6,7 +6,7 @@
 Workload (``config.workload``): the decode configuration the headline metric is quoted on --
 Q4_K GEMVs of one decoder MLP, gate and up ``[18944 x 3584]`` and down ``[3584 x 18944]``, at batch
 1, 4 and 16, bf16 activations ~ N(0,1), fp32 outputs.  One *step* is those nine GEMVs over one set
-of weights.  Weights rotate over a ring of sets larger than three times the L2 cache, so every
+of weights, issued as one list (six launches: gate and up share their activations).  Weights rotate over a ring of sets larger than three times the L2 cache, so every
 launch streams its weights from HBM.  Data is synthetic (seeded, with the stated distributions).
 
 ``value``  = raw quantised weight bytes of a step / device time, inputs resident in HBM (CUDA
@@ -27,7 +27,8 @@ launch streams its weights from HBM.  Data is synthetic (seeded, with the stated
 
 With N > 1 (torchrun, one process per GPU) every weight is column-sharded along N over the ranks;
 total work is fixed (strong scaling).  Decode GEMVs store their columns straight into every rank's
-output over NVLink (peer-mapped memory) with the cross-GPU ordering folded into the launches.
+output over NVLink (peer-mapped memory) with the cross-GPU ordering folded into the launches: the
+first launch of a list waits for the peers' previous signal, the last one signals.
 """
 
 from __future__ import annotations
