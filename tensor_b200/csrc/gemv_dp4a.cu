@@ -1,16 +1,20 @@
-// Batch-1 decode GEMV for Q6_K and Q4_K on the integer dot-product units: out[n] = sum_k dequant(w[n, k]) * x[k].
+// Batch-1 decode GEMV for Q6_K, Q8_0, Q4_0 and Q4_K on the integer dot-product units:
+// out[n] = sum_k dequant(w[n, k]) * x[k].
 //
-// Replaces the reference's `gemv_packed` (benchmarks/kernels/showcase/kernels.py:116-119) for the Q6_K
-// projections of a decoder at batch 1, where no tensor-core form pays: at one activation row an MMA
-// wastes all but one of its columns, and the 6-bit decode costs more than the dot product itself.
+// Replaces the reference's `gemv_packed` (benchmarks/kernels/showcase/kernels.py:116-119) at batch 1, where no
+// tensor-core form pays for these formats: at one activation row an MMA wastes all but one of its columns, the
+// 6-bit decode of Q6_K costs more than the dot product itself, and Q8_0 weights are 8-bit integers already.
 //
-// Regime: HBM-bound, so everything serves streaming 210-byte blocks with as few instructions per
-// weight as possible, all of them exact.
+// Regime: HBM-bound, so everything serves streaming the raw blocks (Q6_K below; the other formats differ in
+// the unpacking only) with as few instructions per weight as possible, all of them exact.
 //
 //  * Activations as 8-bit integers, without rounding: the CTA converts all K activations once.  Every
-//    run of 32 values is scaled by the power of two that puts its largest magnitude in [32, 64) and split into three signed 8-bit limbs, x = l0 + l1 / 2^7 + l2 / 2^14 (exact for
-//    every value within 2^-12 of the run's largest, 2^-21 of it in absolute terms otherwise).
-//  * Weights as the signed bytes q - 32: nibble | bit pair << 4, minus 32, four at a time.
+//    run of 32 values is scaled by the power of two that puts its largest magnitude in [32, 64); 2^14 times
+//    the scaled value, rounded to an integer q of at most 21 bits, is split into three signed limbs of 7 + 7
+//    + 7 bits, q = l0 2^14 + l1 2^7 + l2 (exact for every value within 2^-12 of the run's largest, within
+//    2^-21 of it in absolute terms otherwise).
+//  * Weights as unsigned bytes, nibble | bit pair << 4 four at a time; the offset of 32 (8 for Q4_0) is taken
+//    out in integers against the limb sums of the activations: sum (q - 32) x = sum q x - 32 sum x.
 //  * `dp4a` (four 8-bit products per lane and instruction) against each limb, int32 sums per
 //    16-weight scale group; the limbs are joined with two shifts, and d * scale is applied in fp32.
 //  * A warp owns eight consecutive blocks of every row it takes (1680 bytes, a multiple of 16): it copies
@@ -292,13 +296,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
     const int bias = F16 ? 15 : 127, emax = F16 ? 31 : 255;
     int sh = 0;
     if (e > 0 && e < emax) sh = bias + 5 - e;
-    sh = sh > 100 ? 100 : (sh < -100 ? -100 : sh);
-    const float scale = __uint_as_float((uint32_t)(sh + 127) << 23);
+    sh = sh > 112 ? 112 : (sh < -125 ? -125 : sh);  // both factors stay normal numbers; every finite bf16 run fits
+    // value * 2^(sh + 14), rounded to an integer q of at most 21 bits: l2 and l1 are its two low groups of
+    // seven bits read as signed numbers, l0 what is left, so q = l0 2^14 + l1 2^7 + l2 exactly
+    const float scale14 = __uint_as_float((uint32_t)(sh + 14 + 127) << 23);
     // a run that holds a NaN or an infinity has no limbs: its factor makes every output NaN
     if ((tid & 3) == 0)
       unscale[v0 >> 5] = e >= emax ? __uint_as_float(0x7FC00000u) : __uint_as_float((uint32_t)(127 - sh - 14) << 23);
     uint32_t limb[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
-    float sum = 0.f;
     int joined = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -308,18 +313,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_dp4a_kernel(const DpAr
       } else {
         f = __uint_as_float((i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16));
       }
-      f *= scale;
-      const float x = fabsf(f) < 64.f ? f : 0.f;  // only a non-finite value can fail this
-      const float l0 = rintf(x);
-      const float r1 = (x - l0) * 128.f;
-      const float l1 = rintf(r1);
-      const float l2 = rintf((r1 - l1) * 128.f);
-      sum += l0 + l1 * (1.f / 128.f) + l2 * (1.f / 16384.f);
-      joined += ((int)l0 << 14) + ((int)l1 << 7) + (int)l2;
-      limb[0][i >> 2] |= ((uint32_t)(int)l0 & 0xFFu) << (8 * (i & 3));
-      limb[1][i >> 2] |= ((uint32_t)(int)l1 & 0xFFu) << (8 * (i & 3));
-      limb[2][i >> 2] |= ((uint32_t)(int)l2 & 0xFFu) << (8 * (i & 3));
+      const int q = __float2int_rn(f * scale14);
+      const int l2 = (int)((uint32_t)q << 25) >> 25;
+      const int q1 = (q - l2) >> 7;
+      const int l1 = (int)((uint32_t)q1 << 25) >> 25;
+      const int l0 = (q1 - l1) >> 7;
+      joined = (int)((uint32_t)joined + (uint32_t)q);  // (a non-finite value saturates q; its run's factor is NaN)
+      constexpr uint32_t kInsert[4] = {0x3214u, 0x3240u, 0x3410u, 0x4210u};  // byte 0 of the limb into byte i % 4
+      limb[0][i >> 2] = __byte_perm(limb[0][i >> 2], (uint32_t)l0, kInsert[i & 3]);
+      limb[1][i >> 2] = __byte_perm(limb[1][i >> 2], (uint32_t)l1, kInsert[i & 3]);
+      limb[2][i >> 2] = __byte_perm(limb[2][i >> 2], (uint32_t)l2, kInsert[i & 3]);
     }
+    float sum = (float)joined * (1.f / 16384.f);
 #pragma unroll
     for (int l = 0; l < 3; ++l) *reinterpret_cast<uint2*>(xl + (size_t)l * a.k + v0) = make_uint2(limb[l][0], limb[l][1]);
     if constexpr (FMT == kQ6_K || FMT == kQ4_0) {
