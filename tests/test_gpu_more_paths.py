@@ -154,6 +154,25 @@ def test_blocks_of_32_batch1_integer_dot_product(encoding, n, k, xdt):
     assert np.array_equal(out.cpu().numpy(), results[0] * np.float32(-2.0))
 
 
+@pytest.mark.parametrize("encoding,k", [("q6_k", 2048), ("q8_0", 256), ("q4_0", 768), ("q4_k", 512)])
+@pytest.mark.parametrize("n", [1, 3, 149])
+def test_integer_dot_product_few_rows_and_nan(encoding, k, n):
+    """Fewer rows than a CTA has row streams, and one row more than there are SMs; a NaN among the activations
+    reaches every output, as it does in the reference arithmetic."""
+    raw = oracle.make_weights(encoding, n, k, seed=n + k)
+    x = oracle.make_activations(1, k, seed=n + k + 1, dtype="bf16")
+    want = c_oracle.gemv(x, raw, encoding, n, k)
+    kern = tb.gguf(1, n, k, encoding, op="gemv", variant="dp4a")
+    xd, wd = to_dev(x, torch.bfloat16), to_dev(raw)
+    out = torch.full((1, n), float("nan"), device=dev())
+    kern.launch(xd, wd, out)
+    assert oracle.rel_frobenius(out.cpu().numpy(), want) < 3e-5
+    xd[0, k // 2 + 5] = float("nan")
+    kern.launch(xd, wd, out)
+    assert bool(torch.isnan(out).all())
+    assert tb.device_status() == 0
+
+
 def test_q6k_batch1_tiny_and_huge_activations():
     """A run of 32 activations is scaled by its own power of two: magnitudes far apart between runs survive."""
     n, k = 64, 2048
