@@ -294,19 +294,26 @@ def run_gpu(args):
     ring += ring % 2  # even: the two output copies of the N-sharded lists alternate from slot to slot
     weights = [[synth.make_weights(fmt, n // world, k, seed=1000 * slot + 10 * j + rank, device=device)
                 for j, (_, n, k) in enumerate(SHAPES)] for slot in range(ring)]
-    # the activations of a step are views of ONE device buffer, so that they arrive from the host in one copy
+    # the activations of a step are views of ONE device buffer, so that they arrive from the host in one copy;
+    # the buffer exists twice and the weight sets of the ring alternate between the copies (the ring is even),
+    # so the next step's activations can arrive while this step computes
     acts_src = {b: [synth.make_activations(b, k, seed=7 * b + j, device=device) for j, (_, _, k) in enumerate(SHAPES)]
                 for b in BATCHES}
-    x_all = torch.empty(sum(acts_src[b][j].numel() for b in BATCHES for j in (0, 2)), dtype=torch.bfloat16, device=device)
-    acts, taken = {}, 0
-    for b in BATCHES:
-        acts[b] = [None, None, None]
-        for j in (0, 2):  # gate and up read the same activations
-            t = acts_src[b][j]
-            acts[b][j] = x_all[taken:taken + t.numel()].view_as(t)
-            acts[b][j].copy_(t)
-            taken += t.numel()
-        acts[b][1] = acts[b][0]
+    x_elems = sum(acts_src[b][j].numel() for b in BATCHES for j in (0, 2))
+    x_both = [torch.empty(x_elems, dtype=torch.bfloat16, device=device) for _ in range(2)]
+    acts_both = []
+    for x_buf in x_both:
+        views, taken = {}, 0
+        for b in BATCHES:
+            views[b] = [None, None, None]
+            for j in (0, 2):  # gate and up read the same activations
+                t = acts_src[b][j]
+                views[b][j] = x_buf[taken:taken + t.numel()].view_as(t)
+                views[b][j].copy_(t)
+                taken += t.numel()
+            views[b][1] = views[b][0]
+        acts_both.append(views)
+    acts, x_all = acts_both[0], x_both[0]
     del acts_src
     # gate and up read the same activations: neighbours in the list, one grouped launch
     lists = {b: ShardedGemvList([(acts[b][0], weights[0][0], fmt, SHAPES[0][1], SHAPES[0][2]),
@@ -323,9 +330,9 @@ def run_gpu(args):
 
     def step(slot, batches=BATCHES):
         if tuple(batches) == tuple(BATCHES):
-            for i in range(len(BATCHES)):
+            for i, b in enumerate(BATCHES):
                 for j in range(3):
-                    step_list.rebind(3 * i + j, w=weights[slot][j])
+                    step_list.rebind(3 * i + j, x=acts_both[slot % 2][b][0 if j < 2 else 2], w=weights[slot][j])
             flat = step_list.forward()
             return {b: flat[3 * i:3 * i + 3] for i, b in enumerate(BATCHES)}
         outs = {}
@@ -475,26 +482,28 @@ def run_gpu(args):
     # replicated) and every result back out, on two side streams ordered by events.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
-    # The outputs exist in two copies that alternate from step to step, so a whole step goes out as ONE
-    # graph launch, and its results travel to the host while the next step computes into the other copy.
-    step_in = torch.cuda.Event()
+    # The outputs and the activations exist in two copies that alternate from step to step, so a whole step goes
+    # out as ONE graph launch, its results travel to the host while the next step computes into the other copy,
+    # and the next step's activations arrive meanwhile.
+    step_in = [torch.cuda.Event(), torch.cuda.Event()]
     step_done = [torch.cuda.Event(), torch.cuda.Event()]
     step_out = [torch.cuda.Event(), torch.cuda.Event()]
 
-    def copy_in_all():
+    def copy_in(par):
         with torch.cuda.stream(s_in):
-            x_all.copy_(x_host, non_blocking=True)
-            step_in.record(s_in)
+            x_both[par].copy_(x_host, non_blocking=True)
+            step_in[par].record(s_in)
 
     def e2e_step(i):
-        par = i & 1
-        stream.wait_event(step_in)         # this step's inputs have arrived
-        stream.wait_event(step_out[par])   # the output copy this step overwrites has been read out
+        par = i & 1                          # the ring is even: graph i % ring reads activation copy i & 1
+        stream.wait_event(step_in[par])      # this step's inputs have arrived
+        stream.wait_event(step_out[par])     # the output copy this step overwrites has been read out
         with torch.cuda.stream(stream):
             graphs[i % ring].replay()
             step_done[par].record(stream)
-        s_in.wait_event(step_done[par])
-        copy_in_all()                       # the next step's inputs
+        # the next step's inputs, into the copy the previous step has finished reading
+        s_in.wait_event(step_done[par ^ 1])
+        copy_in(par ^ 1)
         # a rank's own columns are written by its own kernels: they are complete when its step is
         s_out.wait_event(step_done[par])
         with torch.cuda.stream(s_out):
@@ -511,7 +520,8 @@ def run_gpu(args):
     torch.cuda.synchronize(device)
     for ev in step_out:
         ev.record(s_out)
-    copy_in_all()
+    step_done[1].record(stream)
+    copy_in(0)
     for i in range(4):
         e2e_step(i)
     e2e_drain()
@@ -524,7 +534,8 @@ def run_gpu(args):
     e2e = {"value": step_bytes_total * args.steps / e2e_s / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "note": "activations from pinned host memory on every rank and the results back to it, every step, on copy "
-                   "streams ordered by events: one graph launch per step, its results (N-sharded: the columns each rank "
+                   "streams ordered by events: one graph launch per step, the next step's activations arriving in a "
+                   "second buffer meanwhile, its results (N-sharded: the columns each rank "
                    "computed; d2h bytes are the sum over ranks) read back while the next step computes into the other "
                    "copy of the outputs; weights resident"}
 
