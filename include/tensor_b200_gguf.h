@@ -269,9 +269,13 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
  * Neighbouring items with the same x pointer, m, k and format run as one grouped launch.
  * variant: TB200_VARIANT_AUTO ... as for tb200_gguf_gemv; TB200_VARIANT_TC runs the whole list as ONE
  * persistent tcgen05 / TMEM launch (Q4_K or Q6_K, 2-byte activations, m <= 16).
- * scratch: tb200_gguf_gemv_list_scratch_bytes, 256-byte aligned, zeroed before first use, not shared
- * with a call that may overlap.  pads / rank / world / sync as in tb200_gguf_gemv_sharded_sync (sync 0
- * on one GPU): the first launch waits, the last one signals. */
+ * scratch: tb200_gguf_gemv_list_scratch_bytes (a slice per launch), 256-byte aligned, zeroed before first
+ * use, not shared with a call that may overlap.  With a slice per launch the activation conversions of
+ * all batched items (m > 1) are issued ahead of the first GEMV, so that the GEMVs follow one another
+ * directly; a smaller buffer that holds the largest single need is accepted (the launches then share it
+ * and every conversion runs right before its GEMV).  pads / rank / world / sync as in
+ * tb200_gguf_gemv_sharded_sync (sync 0 on one GPU): the first launch waits (ahead of the conversions, as a
+ * launch of its own, where there are any), the last one signals. */
 #define TB200_GEMV_LIST_MAX 12
 typedef struct TB200GemvItem {
   int32_t format;  /* TB200_Q4_K ... */

@@ -6,6 +6,7 @@
 // (src/tensor/compiler/cpu.py:60-155): abi version, struct size, argument count / kind / dtype,
 // byte sizes, alignment, device.  Errors are status codes + a message, never C++ exceptions
 // (abi.h:135-141).  There is no CPU fallback: every path below ends in a CUDA launch or an error.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -303,7 +304,8 @@ namespace {
 // Shared by the plain and the sharded entry points: `out` says where the [m, n] result goes.
 int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* w, const OutSpec& out, int64_t m,
                     int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
-                    TensorErrorV1* error, const PeerSync* peers = nullptr, const Schedule* sched = nullptr) {
+                    TensorErrorV1* error, const PeerSync* peers = nullptr, const Schedule* sched = nullptr,
+                    int prep_mode = kPrepNormal) {
   if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
   if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
   for (int i = 0; i < out.count; ++i)
@@ -314,6 +316,19 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (int32_t s = require_device(error, &dev)) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint8_t* wp = static_cast<const uint8_t*>(w);
+  if (prep_mode == kPrepOnly) {
+    // only the conversion launch of the pipelined kernel, where this call would take that kernel and its plan
+    // converts ahead (the same conditions as below lead there)
+    if (format != kQ4_K || m < 2 || variant == TB200_VARIANT_SIMPLE || variant == TB200_VARIANT_TC ||
+        variant == TB200_VARIANT_DP4A)
+      return ok(error);
+    GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev, true, sched);
+    if (plan.supported) {
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, nullptr, nullptr, 0, kPrepOnly);
+      if (e != cudaSuccess) return cuda_fail(error, "activation conversion launch", e);
+    }
+    return ok(error);
+  }
   // Batch 1 of Q6_K, Q8_0 and Q4_0 (and of Q4_K on request, variant "dp4a"): the integer dot-product kernel,
   // measured about 2.4 times as fast as the tensor-memory kernel for Q6_K (for Q4_K the mma.sync pipeline stays
   // ahead; FAST / MMA still name the bulk-copy ring for the formats it covers).
@@ -361,7 +376,17 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (variant != TB200_VARIANT_SIMPLE) {
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev, true, sched);
     if (plan.supported) {
-      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers);
+      // The conversion launch reads the activations ahead of the GEMV's folded wait: where they may come from
+      // the peers, the wait goes out as a launch of its own first.
+      PeerSync after_wait{};
+      if (peers && (peers->flags & kPeerWait) && plan.prep_x_offset && prep_mode == kPrepNormal) {
+        cudaError_t e = launch_peer_barrier(peers->pads, peers->rank, peers->world, kPeerWait, st);
+        if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
+        after_wait = *peers;
+        after_wait.flags &= ~kPeerWait;
+        peers = after_wait.flags ? &after_wait : nullptr;
+      }
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers, nullptr, 0, prep_mode);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch", e);
       return ok(error);
     }
@@ -430,11 +455,11 @@ int32_t tb200_gguf_gemv(int32_t format, int32_t x_dtype, const void* x, const vo
                      error);
 }
 
-int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w,
-                                     float* const* outs, int32_t out_count, int64_t out_ld, int64_t col_offset,
-                                     int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
-                                     int32_t variant, uint32_t* const* pads, int32_t rank, int32_t world,
-                                     int32_t sync, void* stream, TensorErrorV1* error) {
+static int32_t gemv_sharded_impl(int32_t format, int32_t x_dtype, const void* x, const void* w,
+                                 float* const* outs, int32_t out_count, int64_t out_ld, int64_t col_offset,
+                                 int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
+                                 int32_t variant, uint32_t* const* pads, int32_t rank, int32_t world,
+                                 int32_t sync, void* stream, TensorErrorV1* error, int prep_mode) {
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n, k, variant)) return s;
   if (!outs) return fail(error, TENSOR_ERROR_ARGUMENT, "outs is null");
   if (out_count < 1 || out_count > TB200_MAX_PEERS)
@@ -469,7 +494,16 @@ int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void
     return ok(error);
   }
   return gemv_common(format, x_dtype, x, w, spec, m, n, k, scratch, scratch_bytes, variant, stream, error,
-                     peers.flags ? &peers : nullptr);
+                     peers.flags ? &peers : nullptr, nullptr, prep_mode);
+}
+
+int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w,
+                                     float* const* outs, int32_t out_count, int64_t out_ld, int64_t col_offset,
+                                     int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
+                                     int32_t variant, uint32_t* const* pads, int32_t rank, int32_t world,
+                                     int32_t sync, void* stream, TensorErrorV1* error) {
+  return gemv_sharded_impl(format, x_dtype, x, w, outs, out_count, out_ld, col_offset, m, n, k, scratch, scratch_bytes,
+                           variant, pads, rank, world, sync, stream, error, kPrepNormal);
 }
 
 int32_t tb200_gguf_gemv_sharded(int32_t format, int32_t x_dtype, const void* x, const void* w, float* const* outs,
@@ -541,12 +575,12 @@ int32_t tb200_gguf_gemv_pair(int32_t format, int32_t x_dtype, const void* x, con
   return ok(error);
 }
 
-int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w1, int64_t n1,
-                                          const void* w2, int64_t n2, float* const* outs1, float* const* outs2,
-                                          int32_t out_count, int64_t out_ld, int64_t col_offset1, int64_t col_offset2,
-                                          int64_t m, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant,
-                                          uint32_t* const* pads, int32_t rank, int32_t world, int32_t sync,
-                                          void* stream, TensorErrorV1* error) {
+static int32_t gemv_pair_sharded_impl(int32_t format, int32_t x_dtype, const void* x, const void* w1, int64_t n1,
+                                      const void* w2, int64_t n2, float* const* outs1, float* const* outs2,
+                                      int32_t out_count, int64_t out_ld, int64_t col_offset1, int64_t col_offset2,
+                                      int64_t m, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant,
+                                      uint32_t* const* pads, int32_t rank, int32_t world, int32_t sync,
+                                      void* stream, TensorErrorV1* error, int prep_mode) {
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n1, k, variant)) return s;
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n2, k, variant)) return s;
   if (!outs1 || !outs2) return fail(error, TENSOR_ERROR_ARGUMENT, "outs1 and outs2 are required");
@@ -575,7 +609,7 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
     if (scratch_bytes < 0) return fail(error, TENSOR_ERROR_ARGUMENT, "negative scratch size");
     const DeviceInfo* dev;
     if (int32_t s = require_device(error, &dev)) return s;
-    if (variant == TB200_VARIANT_TC) {
+    if (variant == TB200_VARIANT_TC && prep_mode == kPrepNormal) {
       TcLaunchItem pair[2]{};
       for (int i = 0; i < 2; ++i) {
         pair[i].fmt = format;
@@ -611,20 +645,37 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
         spec.ptr[i] = outs1[i] + col_offset1;
         spec.ptr2[i] = outs2[i] + col_offset2;
       }
+      // (the conversion launch reads the activations ahead of the GEMV's folded wait: see gemv_common)
+      if ((peers.flags & kPeerWait) && plan.prep_x_offset && prep_mode == kPrepNormal) {
+        cudaError_t e = launch_peer_barrier(peers.pads, peers.rank, peers.world, kPeerWait, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
+        peers.flags &= ~kPeerWait;
+      }
       cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), spec, m, n, k, scratch,
                                        static_cast<cudaStream_t>(stream), peers.flags ? &peers : nullptr,
-                                       static_cast<const uint8_t*>(w2), n1);
+                                       static_cast<const uint8_t*>(w2), n1, prep_mode);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch (two weights, sharded)", e);
       return ok(error);
     }
   }
   // two launches: the first waits for the peers, the second signals them
-  if (int32_t s = tb200_gguf_gemv_sharded_sync(format, x_dtype, x, w1, outs1, out_count, out_ld, col_offset1, m, n1, k,
-                                               scratch, scratch_bytes, variant, pads, rank, world,
-                                               sync & TB200_PEER_WAIT, stream, error))
+  if (int32_t s = gemv_sharded_impl(format, x_dtype, x, w1, outs1, out_count, out_ld, col_offset1, m, n1, k, scratch,
+                                    scratch_bytes, variant, pads, rank, world, sync & TB200_PEER_WAIT, stream, error,
+                                    prep_mode))
     return s;
-  return tb200_gguf_gemv_sharded_sync(format, x_dtype, x, w2, outs2, out_count, out_ld, col_offset2, m, n2, k, scratch,
-                                      scratch_bytes, variant, pads, rank, world, sync & TB200_PEER_SIGNAL, stream, error);
+  return gemv_sharded_impl(format, x_dtype, x, w2, outs2, out_count, out_ld, col_offset2, m, n2, k, scratch, scratch_bytes,
+                           variant, pads, rank, world, sync & TB200_PEER_SIGNAL, stream, error, prep_mode);
+}
+
+int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w1, int64_t n1,
+                                          const void* w2, int64_t n2, float* const* outs1, float* const* outs2,
+                                          int32_t out_count, int64_t out_ld, int64_t col_offset1, int64_t col_offset2,
+                                          int64_t m, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant,
+                                          uint32_t* const* pads, int32_t rank, int32_t world, int32_t sync,
+                                          void* stream, TensorErrorV1* error) {
+  return gemv_pair_sharded_impl(format, x_dtype, x, w1, n1, w2, n2, outs1, outs2, out_count, out_ld, col_offset1,
+                                col_offset2, m, k, scratch, scratch_bytes, variant, pads, rank, world, sync, stream, error,
+                                kPrepNormal);
 }
 
 int32_t tb200_peer_sync(uint32_t* const* pads, int32_t rank, int32_t world, int32_t mode, void* stream,
@@ -828,6 +879,46 @@ void to_launch_items(const TB200GemvItem* items, int count, TcLaunchItem* out) {
 }
 }  // namespace
 
+namespace {
+// The launches a list becomes when its projections go out one by one: neighbours that share their activations
+// (and format, and output layout) as one grouped launch.  need[u] = scratch of unit u (the larger of the grouped
+// launch's and its members'), rounded up to 256 bytes.
+struct ListUnits {
+  int count;
+  int first[kTcMaxItems];
+  bool pair[kTcMaxItems];
+  long long need[kTcMaxItems];
+  long long total, largest;
+};
+ListUnits list_units(const TB200GemvItem* items, int count, const TcLaunchItem* list, int variant,
+                     const DeviceInfo& dev) {
+  ListUnits u{};
+  for (int i = 0; i < count;) {
+    bool pair = i + 1 < count && list[i + 1].x_share == i && items[i + 1].format == items[i].format &&
+                items[i + 1].out_count == items[i].out_count && items[i + 1].out_ld == items[i].out_ld &&
+                variant != TB200_VARIANT_SIMPLE && variant != TB200_VARIANT_DP4A;
+    long long need = tb200_gguf_gemv_scratch_bytes(items[i].format, items[i].m, items[i].n, items[i].k);
+    if (pair) {
+      // only where the two really run as ONE launch (the pipelined kernel, K not split, the first weight ending on
+      // a tile boundary); otherwise they are two units with a slice each
+      const GemvPlan both = plan_gemv_fast(items[i].format, kBF16, items[i].m, items[i].n + items[i + 1].n, items[i].k,
+                                           (long long)1 << 40, dev);
+      pair = both.supported && both.k_splits == 1 && items[i].n % kGemvTileRows == 0;
+      if (pair) need = both.scratch_bytes;
+    }
+    need = (need + 255) / 256 * 256;
+    u.first[u.count] = i;
+    u.pair[u.count] = pair;
+    u.need[u.count] = need;
+    u.total += need;
+    u.largest = std::max(u.largest, need);
+    ++u.count;
+    i += pair ? 2 : 1;
+  }
+  return u;
+}
+}  // namespace
+
 int64_t tb200_gguf_gemv_list_scratch_bytes(const TB200GemvItem* items, int32_t count) {
   if (!items || count < 1 || count > TB200_GEMV_LIST_MAX) return 0;
   cudaError_t e;
@@ -835,17 +926,11 @@ int64_t tb200_gguf_gemv_list_scratch_bytes(const TB200GemvItem* items, int32_t c
   if (!dev) return 0;
   TcLaunchItem list[kTcMaxItems];
   to_launch_items(items, count, list);
-  long long need = gemv_tc_scratch_bytes(list, count, *dev);
-  // launched one by one (or two by two) the projections share the scratch: the largest need counts
-  for (int i = 0; i < count; ++i) {
-    long long single = tb200_gguf_gemv_scratch_bytes(items[i].format, items[i].m, items[i].n, items[i].k);
-    if (i + 1 < count && list[i + 1].x_share == i && items[i + 1].format == items[i].format) {
-      const long long both = tb200_gguf_gemv_scratch_bytes(items[i].format, items[i].m, items[i].n + items[i + 1].n, items[i].k);
-      if (both > single) single = both;
-    }
-    if (single > need) need = single;
-  }
-  return need;
+  // Launched one by one (or two by two) every unit gets a slice of its own, so that the activation conversions
+  // of all units can run ahead of the first GEMV; a buffer that only holds the largest unit still works (the
+  // units then share it and every conversion runs right before its GEMV).
+  const ListUnits units = list_units(items, count, list, TB200_VARIANT_AUTO, *dev);
+  return std::max<long long>(gemv_tc_scratch_bytes(list, count, *dev), units.total);
 }
 
 int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* scratch, int64_t scratch_bytes,
@@ -887,28 +972,48 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   }
   // Pipelined launches back to back (each overlaps its predecessor's tail); neighbours that share
   // their activations go out as one grouped launch.  The first launch waits for the peers, the last
-  // one signals them.
-  for (int i = 0; i < count;) {
-    const bool pair = i + 1 < count && list[i + 1].x_share == i && items[i + 1].format == items[i].format &&
-                      items[i + 1].out_count == items[i].out_count && items[i + 1].out_ld == items[i].out_ld &&
-                      variant != TB200_VARIANT_SIMPLE && variant != TB200_VARIANT_DP4A;
-    const int step = pair ? 2 : 1;
-    const int flags = (i == 0 ? peers.flags & kPeerWait : 0) | (i + step >= count ? peers.flags & kPeerSignal : 0);
-    if (pair) {
-      if (int32_t s = tb200_gguf_gemv_pair_sharded_sync(
-              items[i].format, items[i].x_dtype, items[i].x, items[i].w, items[i].n, items[i + 1].w, items[i + 1].n,
-              items[i].outs, items[i + 1].outs, items[i].out_count, items[i].out_ld, 0, 0, items[i].m, items[i].k,
-              scratch, scratch_bytes, variant, pads, rank, world > 0 ? world : 1, flags, stream, error))
-        return s;
-    } else {
-      PeerSync each = peers;
-      each.flags = flags;
-      if (int32_t s = gemv_common(items[i].format, items[i].x_dtype, items[i].x, items[i].w, list[i].out, items[i].m,
-                                  items[i].n, items[i].k, scratch, scratch_bytes, variant, stream, error,
-                                  each.flags ? &each : nullptr))
-        return s;
+  // one signals them.  Where the scratch holds a slice per unit, the activation conversions of all
+  // units (batches above 1) go out first, so that no small launch sits between two GEMVs; they read the
+  // activations, so an N-sharded list then waits for its peers with a launch of its own before them.
+  const ListUnits units = list_units(items, count, list, variant, *dev);
+  const bool slices = scratch && units.total <= scratch_bytes && units.count > 1;
+  uint8_t* const base = static_cast<uint8_t*>(scratch);
+  auto launch_unit = [&](int u, long long offset, long long bytes, int flags, int prep_mode) -> int32_t {
+    const int i = units.first[u];
+    void* sc = scratch ? base + offset : nullptr;
+    if (units.pair[u])
+      return gemv_pair_sharded_impl(items[i].format, items[i].x_dtype, items[i].x, items[i].w, items[i].n, items[i + 1].w,
+                                    items[i + 1].n, items[i].outs, items[i + 1].outs, items[i].out_count, items[i].out_ld,
+                                    0, 0, items[i].m, items[i].k, sc, bytes, variant, pads, rank, world > 0 ? world : 1,
+                                    flags, stream, error, prep_mode);
+    PeerSync each = peers;
+    each.flags = flags;
+    return gemv_common(items[i].format, items[i].x_dtype, items[i].x, items[i].w, list[i].out, items[i].m, items[i].n,
+                       items[i].k, sc, bytes, variant, stream, error, each.flags ? &each : nullptr, nullptr, prep_mode);
+  };
+  bool hoist = false;
+  if (slices)
+    for (int i = 0; i < count; ++i) hoist |= items[i].m > 1 && items[i].format == kQ4_K;
+  int wait_flag = peers.flags & kPeerWait;
+  if (hoist) {
+    if (wait_flag) {
+      cudaError_t e = launch_peer_barrier(peers.pads, peers.rank, peers.world, kPeerWait, st);
+      if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
+      wait_flag = 0;
     }
-    i += step;
+    long long offset = 0;
+    for (int u = 0; u < units.count; ++u) {
+      if (int32_t s = launch_unit(u, offset, units.need[u], 0, kPrepOnly)) return s;
+      offset += units.need[u];
+    }
+  }
+  long long offset = 0;
+  for (int u = 0; u < units.count; ++u) {
+    const int flags = (u == 0 ? wait_flag : 0) | (u + 1 == units.count ? peers.flags & kPeerSignal : 0);
+    if (int32_t s = launch_unit(u, slices ? offset : 0, slices ? units.need[u] : scratch_bytes, flags,
+                                hoist ? kPrepDone : kPrepNormal))
+      return s;
+    offset += units.need[u];
   }
   return ok(error);
 }

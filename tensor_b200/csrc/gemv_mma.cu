@@ -1365,8 +1365,10 @@ bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n,
 
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
-                             cudaStream_t stream, const PeerSync* peers, const uint8_t* w2, long long n1) {
+                             cudaStream_t stream, const PeerSync* peers, const uint8_t* w2, long long n1,
+                             int prep_mode) {
   if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
+  if (prep_mode == kPrepOnly && !plan.prep_x_offset) return cudaSuccess;  // this plan converts inside the GEMV
   // a second weight is fetched tile by tile from its own base: K must not be split (the split
   // path addresses rows through one tensor map) and the first weight must end on a tile boundary
   if (w2 && (plan.k_splits != 1 || n1 <= 0 || n1 >= n || n1 % kTileRows)) return cudaErrorInvalidValue;
@@ -1424,10 +1426,13 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     cfg.attrs = attr;
     cfg.numAttrs = plan.overlap ? 1 : 0;
     const uint16_t* xin = static_cast<const uint16_t*>(x);
-    cudaError_t e = xt == kF16
-                        ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m, (int)k, ntb)
-                        : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, unscale, (int)m, (int)k, ntb);
-    if (e != cudaSuccess) return e;
+    if (prep_mode != kPrepDone) {
+      cudaError_t e = xt == kF16
+                          ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m, (int)k, ntb)
+                          : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, unscale, (int)m, (int)k, ntb);
+      if (e != cudaSuccess) return e;
+    }
+    if (prep_mode == kPrepOnly) return cudaSuccess;
     a.x16 = x16;
     a.x_table = table;
     a.x_unscale = unscale;

@@ -114,10 +114,14 @@ struct PeerSync {
   int world;
   int flags;
 };
+// How a plan that converts the activations ahead of the GEMV (m > 1) does so: with a launch of its own right
+// before the GEMV (normal), only that launch (a list issues the conversions of all its projections first, so
+// that its GEMVs follow one another directly), or not at all because that launch has been made already.
+enum PrepMode : int { kPrepNormal = 0, kPrepOnly = 1, kPrepDone = 2 };
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream, const PeerSync* peers = nullptr, const uint8_t* w2 = nullptr,
-                             long long n1 = 0);
+                             long long n1 = 0, int prep_mode = kPrepNormal);
 // the first bytes of a GEMV scratch buffer: arrival counters that must read zero when a call starts
 constexpr int kGemvCounterBytes = 4096;
 constexpr int kGemvTileRows = 16;  // rows per weight tile of the pipelined GEMV (n1 of a grouped launch is a multiple)

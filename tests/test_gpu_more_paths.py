@@ -259,6 +259,37 @@ def test_gemv_list_mixed_batches(variant):
             assert oracle.rel_frobenius(got, want) < TOL
 
 
+@pytest.mark.parametrize("shared_scratch", [False, True])
+def test_gemv_list_converts_batched_activations_first(shared_scratch):
+    """An MLP at batch 1, 4 and 16 as one list (gate and up share their activations; the down projection splits
+    K): with a scratch slice per launch the conversions of the batched activations run ahead of the first GEMV,
+    with a buffer that only holds the largest need every conversion runs right before its GEMV; both must give
+    the results of single launches, call after call."""
+    entries, wants = [], []
+    for m in (1, 4, 16):
+        xs = {k: oracle.make_activations(m, k, seed=90 + m + k, dtype="bf16") for k in (1024, 6144)}
+        xd = {k: to_dev(v, torch.bfloat16) for k, v in xs.items()}
+        for j, (n, k) in enumerate(((768, 1024), (768, 1024), (256, 6144))):
+            raw = oracle.make_weights("q4_k", n, k, seed=100 + 10 * m + j)
+            entries.append((xd[k], to_dev(raw), "q4_k", n, k, torch.full((m, n), float("nan"), device=dev())))
+            wants.append(c_oracle.gemv(xs[k], raw, "q4_k", n, k))
+    lst = ops.GemvList(entries)
+    if shared_scratch:
+        largest = max(ops.gemv_scratch_bytes("q4_k", e[5].shape[0], e[3], e[4]) for e in entries)
+        pair = ops.gemv_scratch_bytes("q4_k", 16, 1536, 1024)
+        lst.scratch = torch.zeros(max(largest, pair, 256), dtype=torch.uint8, device=dev())
+        assert lst.scratch.numel() < int(ops.lib().tb200_gguf_gemv_list_scratch_bytes(lst._items, len(entries)))
+    for _ in range(3):
+        for e in entries:
+            e[5].fill_(float("nan"))
+        lst.launch()
+        for e, want in zip(entries, wants):
+            got = e[5].cpu().numpy()
+            assert np.isfinite(got).all()
+            assert oracle.rel_frobenius(got, want) < TOL
+    assert tb.device_status() == 0
+
+
 def test_gemv_list_other_formats_fall_back():
     m, n, k = 2, 96, 512
     entries, wants = [], []
