@@ -274,8 +274,8 @@ int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const
  * all batched items (m > 1) are issued ahead of the first GEMV, so that the GEMVs follow one another
  * directly; a smaller buffer that holds the largest single need is accepted (the launches then share it
  * and every conversion runs right before its GEMV).  pads / rank / world / sync as in
- * tb200_gguf_gemv_sharded_sync (sync 0 on one GPU): the first launch waits (ahead of the conversions, as a
- * launch of its own, where there are any), the last one signals. */
+ * tb200_gguf_gemv_sharded_sync (sync 0 on one GPU): the first launch waits (and so does every conversion
+ * launch, which reads activations ahead of it), the last one signals. */
 #define TB200_GEMV_LIST_MAX 12
 typedef struct TB200GemvItem {
   int32_t format;  /* TB200_Q4_K ... */

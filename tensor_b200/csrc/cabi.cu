@@ -324,7 +324,7 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
       return ok(error);
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev, true, sched);
     if (plan.supported) {
-      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, nullptr, nullptr, 0, kPrepOnly);
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers, nullptr, 0, kPrepOnly);
       if (e != cudaSuccess) return cuda_fail(error, "activation conversion launch", e);
     }
     return ok(error);
@@ -376,16 +376,7 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
   if (variant != TB200_VARIANT_SIMPLE) {
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev, true, sched);
     if (plan.supported) {
-      // The conversion launch reads the activations ahead of the GEMV's folded wait: where they may come from
-      // the peers, the wait goes out as a launch of its own first.
-      PeerSync after_wait{};
-      if (peers && (peers->flags & kPeerWait) && plan.prep_x_offset && prep_mode == kPrepNormal) {
-        cudaError_t e = launch_peer_barrier(peers->pads, peers->rank, peers->world, kPeerWait, st);
-        if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
-        after_wait = *peers;
-        after_wait.flags &= ~kPeerWait;
-        peers = after_wait.flags ? &after_wait : nullptr;
-      }
+      // (a conversion launch reads the activations ahead of the GEMV's folded wait: it carries the wait too)
       cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers, nullptr, 0, prep_mode);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch", e);
       return ok(error);
@@ -644,12 +635,6 @@ static int32_t gemv_pair_sharded_impl(int32_t format, int32_t x_dtype, const voi
       for (int i = 0; i < out_count; ++i) {
         spec.ptr[i] = outs1[i] + col_offset1;
         spec.ptr2[i] = outs2[i] + col_offset2;
-      }
-      // (the conversion launch reads the activations ahead of the GEMV's folded wait: see gemv_common)
-      if ((peers.flags & kPeerWait) && plan.prep_x_offset && prep_mode == kPrepNormal) {
-        cudaError_t e = launch_peer_barrier(peers.pads, peers.rank, peers.world, kPeerWait, static_cast<cudaStream_t>(stream));
-        if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
-        peers.flags &= ~kPeerWait;
       }
       cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), spec, m, n, k, scratch,
                                        static_cast<cudaStream_t>(stream), peers.flags ? &peers : nullptr,
@@ -974,7 +959,7 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   // their activations go out as one grouped launch.  The first launch waits for the peers, the last
   // one signals them.  Where the scratch holds a slice per unit, the activation conversions of all
   // units (batches above 1) go out first, so that no small launch sits between two GEMVs; they read the
-  // activations, so an N-sharded list then waits for its peers with a launch of its own before them.
+  // activations, so on an N-sharded list each of them waits for the peers as the first GEMV does.
   const ListUnits units = list_units(items, count, list, variant, *dev);
   const bool slices = scratch && units.total <= scratch_bytes && units.count > 1;
   uint8_t* const base = static_cast<uint8_t*>(scratch);
@@ -994,16 +979,11 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   bool hoist = false;
   if (slices)
     for (int i = 0; i < count; ++i) hoist |= items[i].m > 1 && items[i].format == kQ4_K;
-  int wait_flag = peers.flags & kPeerWait;
+  const int wait_flag = peers.flags & kPeerWait;
   if (hoist) {
-    if (wait_flag) {
-      cudaError_t e = launch_peer_barrier(peers.pads, peers.rank, peers.world, kPeerWait, st);
-      if (e != cudaSuccess) return cuda_fail(error, "peer wait launch", e);
-      wait_flag = 0;
-    }
     long long offset = 0;
     for (int u = 0; u < units.count; ++u) {
-      if (int32_t s = launch_unit(u, offset, units.need[u], 0, kPrepOnly)) return s;
+      if (int32_t s = launch_unit(u, offset, units.need[u], wait_flag, kPrepOnly)) return s;
       offset += units.need[u];
     }
   }

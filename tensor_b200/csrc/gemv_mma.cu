@@ -250,12 +250,35 @@ __device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* sm
 template <bool F16>
 __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
                                                            float* __restrict__ table, float* __restrict__ unscale_out,
-                                                           int m, int k, int ntb) {
+                                                           int m, int k, int ntb, const unsigned int* pad, int rank,
+                                                           int world, unsigned long long wait_limit_ns) {
   // Let the GEMV behind this kernel start at once (it fills its weight ring, then waits for this
   // kernel to complete, which in turn has waited for the kernel before): the trigger must come
   // before the wait, or the GEMV could not be scheduled until the previous kernel has drained.
   if (threadIdx.x == 0) ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();  // x may come from the kernel before; the GEMV before may still read x16
+  if (pad) {
+    // N-sharded launches whose activations may come from the peers: this kernel reads them ahead of the GEMV's
+    // own wait, so it waits itself (`pad` = this rank's signal pad; bounded, status 0x80000 | peer)
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x < 32) {
+      const unsigned int expected = *reinterpret_cast<const volatile unsigned int*>(pad + 32);
+      if (lane < world && lane != rank) {
+        const unsigned long long t0 = ptx::global_timer_ns();
+        for (;;) {
+          unsigned int seen;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(pad + lane) : "memory");
+          if ((int)(seen - expected) >= 0) break;
+          if (ptx::global_timer_ns() - t0 > wait_limit_ns) {
+            report_timeout(0x80000u | (unsigned)lane);
+            break;
+          }
+          __nanosleep(200);
+        }
+      }
+    }
+    __syncthreads();
+  }
   const int chunks = k >> 3;
   const int live = m * chunks;
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1427,9 +1450,11 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     cfg.numAttrs = plan.overlap ? 1 : 0;
     const uint16_t* xin = static_cast<const uint16_t*>(x);
     if (prep_mode != kPrepDone) {
-      cudaError_t e = xt == kF16
-                          ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m, (int)k, ntb)
-                          : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, unscale, (int)m, (int)k, ntb);
+      const unsigned int* pad = (a.sync & kPeerWait) ? a.pads[a.rank] : nullptr;
+      cudaError_t e = xt == kF16 ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m,
+                                                      (int)k, ntb, pad, a.rank, a.world, a.wait_limit_ns)
+                                 : cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<false>, xin, x16, table, unscale, (int)m,
+                                                      (int)k, ntb, pad, a.rank, a.world, a.wait_limit_ns);
       if (e != cudaSuccess) return e;
     }
     if (prep_mode == kPrepOnly) return cudaSuccess;
