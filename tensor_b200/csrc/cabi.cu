@@ -305,7 +305,7 @@ namespace {
 int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* w, const OutSpec& out, int64_t m,
                     int64_t n, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant, void* stream,
                     TensorErrorV1* error, const PeerSync* peers = nullptr, const Schedule* sched = nullptr,
-                    int prep_mode = kPrepNormal) {
+                    int prep_mode = kPrepNormal, PrepJobs* collect = nullptr) {
   if (int32_t s = check_pointer(error, "x", x, 16, k > 0)) return s;
   if (int32_t s = check_pointer(error, "w", w, 16, k > 0)) return s;
   for (int i = 0; i < out.count; ++i)
@@ -324,7 +324,8 @@ int32_t gemv_common(int32_t format, int32_t x_dtype, const void* x, const void* 
       return ok(error);
     GemvPlan plan = plan_gemv_fast(format, x_dtype, m, n, k, scratch ? scratch_bytes : 0, *dev, true, sched);
     if (plan.supported) {
-      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers, nullptr, 0, kPrepOnly);
+      cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, wp, out, m, n, k, scratch, st, peers, nullptr, 0, kPrepOnly,
+                                       collect);
       if (e != cudaSuccess) return cuda_fail(error, "activation conversion launch", e);
     }
     return ok(error);
@@ -450,7 +451,8 @@ static int32_t gemv_sharded_impl(int32_t format, int32_t x_dtype, const void* x,
                                  float* const* outs, int32_t out_count, int64_t out_ld, int64_t col_offset,
                                  int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
                                  int32_t variant, uint32_t* const* pads, int32_t rank, int32_t world,
-                                 int32_t sync, void* stream, TensorErrorV1* error, int prep_mode) {
+                                 int32_t sync, void* stream, TensorErrorV1* error, int prep_mode,
+                                 PrepJobs* collect = nullptr) {
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n, k, variant)) return s;
   if (!outs) return fail(error, TENSOR_ERROR_ARGUMENT, "outs is null");
   if (out_count < 1 || out_count > TB200_MAX_PEERS)
@@ -485,7 +487,7 @@ static int32_t gemv_sharded_impl(int32_t format, int32_t x_dtype, const void* x,
     return ok(error);
   }
   return gemv_common(format, x_dtype, x, w, spec, m, n, k, scratch, scratch_bytes, variant, stream, error,
-                     peers.flags ? &peers : nullptr, nullptr, prep_mode);
+                     peers.flags ? &peers : nullptr, nullptr, prep_mode, collect);
 }
 
 int32_t tb200_gguf_gemv_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w,
@@ -571,7 +573,8 @@ static int32_t gemv_pair_sharded_impl(int32_t format, int32_t x_dtype, const voi
                                       int32_t out_count, int64_t out_ld, int64_t col_offset1, int64_t col_offset2,
                                       int64_t m, int64_t k, void* scratch, int64_t scratch_bytes, int32_t variant,
                                       uint32_t* const* pads, int32_t rank, int32_t world, int32_t sync,
-                                      void* stream, TensorErrorV1* error, int prep_mode) {
+                                      void* stream, TensorErrorV1* error, int prep_mode,
+                                      PrepJobs* collect = nullptr) {
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n1, k, variant)) return s;
   if (int32_t s = check_gemv_scalars(error, format, x_dtype, m, n2, k, variant)) return s;
   if (!outs1 || !outs2) return fail(error, TENSOR_ERROR_ARGUMENT, "outs1 and outs2 are required");
@@ -638,7 +641,7 @@ static int32_t gemv_pair_sharded_impl(int32_t format, int32_t x_dtype, const voi
       }
       cudaError_t e = launch_gemv_fast(plan, format, x_dtype, x, static_cast<const uint8_t*>(w1), spec, m, n, k, scratch,
                                        static_cast<cudaStream_t>(stream), peers.flags ? &peers : nullptr,
-                                       static_cast<const uint8_t*>(w2), n1, prep_mode);
+                                       static_cast<const uint8_t*>(w2), n1, prep_mode, collect);
       if (e != cudaSuccess) return cuda_fail(error, "pipelined GEMV launch (two weights, sharded)", e);
       return ok(error);
     }
@@ -646,10 +649,10 @@ static int32_t gemv_pair_sharded_impl(int32_t format, int32_t x_dtype, const voi
   // two launches: the first waits for the peers, the second signals them
   if (int32_t s = gemv_sharded_impl(format, x_dtype, x, w1, outs1, out_count, out_ld, col_offset1, m, n1, k, scratch,
                                     scratch_bytes, variant, pads, rank, world, sync & TB200_PEER_WAIT, stream, error,
-                                    prep_mode))
+                                    prep_mode, collect))
     return s;
   return gemv_sharded_impl(format, x_dtype, x, w2, outs2, out_count, out_ld, col_offset2, m, n2, k, scratch, scratch_bytes,
-                           variant, pads, rank, world, sync & TB200_PEER_SIGNAL, stream, error, prep_mode);
+                           variant, pads, rank, world, sync & TB200_PEER_SIGNAL, stream, error, prep_mode, collect);
 }
 
 int32_t tb200_gguf_gemv_pair_sharded_sync(int32_t format, int32_t x_dtype, const void* x, const void* w1, int64_t n1,
@@ -958,23 +961,26 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   // Pipelined launches back to back (each overlaps its predecessor's tail); neighbours that share
   // their activations go out as one grouped launch.  The first launch waits for the peers, the last
   // one signals them.  Where the scratch holds a slice per unit, the activation conversions of all
-  // units (batches above 1) go out first, so that no small launch sits between two GEMVs; they read the
-  // activations, so on an N-sharded list each of them waits for the peers as the first GEMV does.
+  // units (batches above 1) go out first, as ONE launch, so that no small launch sits between two GEMVs; it
+  // reads the activations, so on an N-sharded list it waits for the peers as the first GEMV does.
   const ListUnits units = list_units(items, count, list, variant, *dev);
   const bool slices = scratch && units.total <= scratch_bytes && units.count > 1;
   uint8_t* const base = static_cast<uint8_t*>(scratch);
+  PrepJobs conversions{};
   auto launch_unit = [&](int u, long long offset, long long bytes, int flags, int prep_mode) -> int32_t {
+    PrepJobs* collect = prep_mode == kPrepOnly ? &conversions : nullptr;
     const int i = units.first[u];
     void* sc = scratch ? base + offset : nullptr;
     if (units.pair[u])
       return gemv_pair_sharded_impl(items[i].format, items[i].x_dtype, items[i].x, items[i].w, items[i].n, items[i + 1].w,
                                     items[i + 1].n, items[i].outs, items[i + 1].outs, items[i].out_count, items[i].out_ld,
                                     0, 0, items[i].m, items[i].k, sc, bytes, variant, pads, rank, world > 0 ? world : 1,
-                                    flags, stream, error, prep_mode);
+                                    flags, stream, error, prep_mode, collect);
     PeerSync each = peers;
     each.flags = flags;
     return gemv_common(items[i].format, items[i].x_dtype, items[i].x, items[i].w, list[i].out, items[i].m, items[i].n,
-                       items[i].k, sc, bytes, variant, stream, error, each.flags ? &each : nullptr, nullptr, prep_mode);
+                       items[i].k, sc, bytes, variant, stream, error, each.flags ? &each : nullptr, nullptr, prep_mode,
+                       collect);
   };
   bool hoist = false;
   if (slices)
@@ -982,10 +988,14 @@ int32_t tb200_gguf_gemv_list(const TB200GemvItem* items, int32_t count, void* sc
   const int wait_flag = peers.flags & kPeerWait;
   if (hoist) {
     long long offset = 0;
-    for (int u = 0; u < units.count; ++u) {
-      if (int32_t s = launch_unit(u, offset, units.need[u], wait_flag, kPrepOnly)) return s;
+    for (int u = 0; u < units.count; ++u) {  // notes the conversions ...
+      if (int32_t s = launch_unit(u, offset, units.need[u], 0, kPrepOnly)) return s;
       offset += units.need[u];
     }
+    PeerSync first = peers;  // ... and ONE launch runs them, after waiting for the peers like the first GEMV
+    first.flags = wait_flag;
+    cudaError_t e = launch_gemv_prepare_jobs(conversions, wait_flag ? &first : nullptr, st);
+    if (e != cudaSuccess) return cuda_fail(error, "activation conversion launch (list)", e);
   }
   long long offset = 0;
   for (int u = 0; u < units.count; ++u) {

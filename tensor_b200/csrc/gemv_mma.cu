@@ -247,41 +247,39 @@ __device__ __forceinline__ bool stage_activations(const GemvArgs& a, uint8_t* sm
 // is exact for every value within 2^-29 of it), found with warp shuffles alone, and the GEMV undoes
 // it once per item instead of once per group.
 #ifndef TB200_TBIN_WRAPPER
-template <bool F16>
-__global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
-                                                           float* __restrict__ table, float* __restrict__ unscale_out,
-                                                           int m, int k, int ntb, const unsigned int* pad, int rank,
-                                                           int world, unsigned long long wait_limit_ns) {
-  // Let the GEMV behind this kernel start at once (it fills its weight ring, then waits for this
-  // kernel to complete, which in turn has waited for the kernel before): the trigger must come
-  // before the wait, or the GEMV could not be scheduled until the previous kernel has drained.
-  if (threadIdx.x == 0) ptx::grid_launch_dependents();
-  ptx::grid_dependency_wait();  // x may come from the kernel before; the GEMV before may still read x16
-  if (pad) {
-    // N-sharded launches whose activations may come from the peers: this kernel reads them ahead of the GEMV's
-    // own wait, so it waits itself (`pad` = this rank's signal pad; bounded, status 0x80000 | peer)
-    const int lane = threadIdx.x & 31;
-    if (threadIdx.x < 32) {
-      const unsigned int expected = *reinterpret_cast<const volatile unsigned int*>(pad + 32);
-      if (lane < world && lane != rank) {
-        const unsigned long long t0 = ptx::global_timer_ns();
-        for (;;) {
-          unsigned int seen;
-          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(pad + lane) : "memory");
-          if ((int)(seen - expected) >= 0) break;
-          if (ptx::global_timer_ns() - t0 > wait_limit_ns) {
-            report_timeout(0x80000u | (unsigned)lane);
-            break;
-          }
-          __nanosleep(200);
+// N-sharded launches whose activations may come from the peers: the conversion reads them ahead of the GEMV's own
+// wait, so it waits itself (`pad` = this rank's signal pad; bounded, status 0x80000 | peer).
+__device__ __forceinline__ void prepare_wait_peers(const unsigned int* pad, int rank, int world,
+                                                   unsigned long long wait_limit_ns) {
+  if (!pad) return;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    const unsigned int expected = *reinterpret_cast<const volatile unsigned int*>(pad + 32);
+    if (lane < world && lane != rank) {
+      const unsigned long long t0 = ptx::global_timer_ns();
+      for (;;) {
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(pad + lane) : "memory");
+        if ((int)(seen - expected) >= 0) break;
+        if (ptx::global_timer_ns() - t0 > wait_limit_ns) {
+          report_timeout(0x80000u | (unsigned)lane);
+          break;
         }
+        __nanosleep(200);
       }
     }
-    __syncthreads();
   }
+  __syncthreads();
+}
+
+// Block `block` of the `nblocks` that convert one [m, k] activation tensor.
+template <bool F16>
+__device__ __forceinline__ void prepare_body(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
+                                             float* __restrict__ table, float* __restrict__ unscale_out, int m, int k,
+                                             int ntb, int block, int nblocks) {
   const int chunks = k >> 3;
   const int live = m * chunks;
-  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int tid = block * blockDim.x + threadIdx.x;
   if (tid < live) {
     const int b = tid / chunks, c = tid - b * chunks;
     uint4 v = *reinterpret_cast<const uint4*>(x + (long long)b * k + (c << 3));
@@ -316,11 +314,45 @@ __global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __res
   }
   // columns past m: zero sums, unit factors
   const int groups = k >> 5, spare = ntb - m;
-  for (int i = tid; i < groups * spare; i += gridDim.x * blockDim.x) {
+  for (int i = tid; i < groups * spare; i += nblocks * blockDim.x) {
     const int g = i / spare, b = m + (i - g * spare);
     table[(long long)g * ntb + b] = 0.f;
     if ((g & 7) == 0) unscale_out[(long long)(g >> 3) * ntb + b] = 1.f;
   }
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ x16,
+                                                           float* __restrict__ table, float* __restrict__ unscale_out,
+                                                           int m, int k, int ntb, const unsigned int* pad, int rank,
+                                                           int world, unsigned long long wait_limit_ns) {
+  // Let the GEMV behind this kernel start at once (it fills its weight ring, then waits for this
+  // kernel to complete, which in turn has waited for the kernel before): the trigger must come
+  // before the wait, or the GEMV could not be scheduled until the previous kernel has drained.
+  if (threadIdx.x == 0) ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // x may come from the kernel before; the GEMV before may still read x16
+  prepare_wait_peers(pad, rank, world, wait_limit_ns);
+  prepare_body<F16>(x, x16, table, unscale_out, m, k, ntb, (int)blockIdx.x, (int)gridDim.x);
+}
+
+// The conversions of all batched projections of a list as ONE launch ahead of its GEMVs: block ranges per job.
+struct PrepJobsArg {
+  PrepJobs jobs;
+  const unsigned int* pad;
+  int rank, world;
+  unsigned long long wait_limit_ns;
+};
+__global__ void __launch_bounds__(256) gemv_prepare_multi_kernel(const PrepJobsArg a) {
+  if (threadIdx.x == 0) ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
+  prepare_wait_peers(a.pad, a.rank, a.world, a.wait_limit_ns);
+  int block = (int)blockIdx.x, j = 0;
+  while (j + 1 < a.jobs.count && block >= a.jobs.job[j].blocks) block -= a.jobs.job[j++].blocks;
+  const PrepJob& p = a.jobs.job[j];
+  const uint16_t* x = static_cast<const uint16_t*>(p.x);
+  uint16_t* x16 = static_cast<uint16_t*>(p.x16);
+  if (p.f16) prepare_body<true>(x, x16, p.table, p.unscale, p.m, p.k, p.ntb, block, p.blocks);
+  else prepare_body<false>(x, x16, p.table, p.unscale, p.m, p.k, p.ntb, block, p.blocks);
 }
 #endif  // TB200_TBIN_WRAPPER
 
@@ -1386,10 +1418,37 @@ bool gemv_launch_config(const GemvPlan& plan, int fmt, long long m, long long n,
   return true;
 }
 
+cudaError_t launch_gemv_prepare_jobs(const PrepJobs& jobs, const PeerSync* peers, cudaStream_t stream) {
+  if (jobs.count < 1) return cudaSuccess;
+  if (jobs.count > kMaxPrepJobs) return cudaErrorInvalidValue;
+  PrepJobsArg arg{};
+  arg.jobs = jobs;
+  arg.wait_limit_ns = peer_wait_limit_ns();
+  if (peers && (peers->flags & kPeerWait)) {
+    if (peers->world < 1 || peers->world > kMaxOutputs || peers->rank < 0 || peers->rank >= peers->world)
+      return cudaErrorInvalidValue;
+    arg.pad = peers->pads[peers->rank];
+    arg.rank = peers->rank;
+    arg.world = peers->world;
+  }
+  long long blocks = 0;
+  for (int i = 0; i < jobs.count; ++i) blocks += jobs.job[i].blocks;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemv_prepare_multi_kernel, arg);
+}
+
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream, const PeerSync* peers, const uint8_t* w2, long long n1,
-                             int prep_mode) {
+                             int prep_mode, PrepJobs* collect) {
   if (!plan.supported || fmt != kQ4_K) return cudaErrorInvalidValue;
   if (prep_mode == kPrepOnly && !plan.prep_x_offset) return cudaSuccess;  // this plan converts inside the GEMV
   // a second weight is fetched tile by tile from its own base: K must not be split (the split
@@ -1449,7 +1508,20 @@ cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* 
     cfg.attrs = attr;
     cfg.numAttrs = plan.overlap ? 1 : 0;
     const uint16_t* xin = static_cast<const uint16_t*>(x);
-    if (prep_mode != kPrepDone) {
+    if (prep_mode != kPrepDone && collect) {
+      // the caller issues the collected conversions as one launch (launch_gemv_prepare_jobs)
+      if (collect->count >= kMaxPrepJobs) return cudaErrorInvalidValue;
+      PrepJob& job = collect->job[collect->count++];
+      job.x = x;
+      job.x16 = x16;
+      job.table = table;
+      job.unscale = unscale;
+      job.m = (int)m;
+      job.k = (int)k;
+      job.ntb = ntb;
+      job.f16 = xt == kF16;
+      job.blocks = (int)cfg.gridDim.x;
+    } else if (prep_mode != kPrepDone) {
       const unsigned int* pad = (a.sync & kPeerWait) ? a.pads[a.rank] : nullptr;
       cudaError_t e = xt == kF16 ? cudaLaunchKernelEx(&cfg, gemv_prepare_kernel<true>, xin, x16, table, unscale, (int)m,
                                                       (int)k, ntb, pad, a.rank, a.world, a.wait_limit_ns)

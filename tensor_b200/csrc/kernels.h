@@ -118,10 +118,25 @@ struct PeerSync {
 // before the GEMV (normal), only that launch (a list issues the conversions of all its projections first, so
 // that its GEMVs follow one another directly), or not at all because that launch has been made already.
 enum PrepMode : int { kPrepNormal = 0, kPrepOnly = 1, kPrepDone = 2 };
+// With kPrepOnly and a collector the conversion is not launched but noted; launch_gemv_prepare_jobs then runs all
+// noted conversions as one launch (which waits for the peers first where `peers` asks for it).
+constexpr int kMaxPrepJobs = 12;
+struct PrepJob {
+  const void* x;   // [m, k] activations
+  void* x16;       // converted activations, group sums and factors: inside the launch's scratch slice
+  float* table;
+  float* unscale;
+  int m, k, ntb, f16, blocks;
+};
+struct PrepJobs {
+  PrepJob job[kMaxPrepJobs];
+  int count;
+};
+cudaError_t launch_gemv_prepare_jobs(const PrepJobs& jobs, const PeerSync* peers, cudaStream_t stream);
 cudaError_t launch_gemv_fast(const GemvPlan& plan, int fmt, int xt, const void* x, const uint8_t* w,
                              const OutSpec& out, long long m, long long n, long long k, void* scratch,
                              cudaStream_t stream, const PeerSync* peers = nullptr, const uint8_t* w2 = nullptr,
-                             long long n1 = 0, int prep_mode = kPrepNormal);
+                             long long n1 = 0, int prep_mode = kPrepNormal, PrepJobs* collect = nullptr);
 // the first bytes of a GEMV scratch buffer: arrival counters that must read zero when a call starts
 constexpr int kGemvCounterBytes = 4096;
 constexpr int kGemvTileRows = 16;  // rows per weight tile of the pipelined GEMV (n1 of a grouped launch is a multiple)
