@@ -81,7 +81,8 @@ def measured_peaks():
 def workload_config(world: int):
     return {
         "workload": "q4_k decode GEMV: gate/up 18944x3584 + down 3584x18944, batch 1/4/16 (9 GEMVs per step)",
-        "launches": "gate and up share their activations and run as one grouped launch (6 GEMV launches per step)",
+        "launches": "gate and up share their activations and run as one grouped launch (6 GEMV launches per step, behind one "
+                    "launch that converts the batch-4 and batch-16 activations)",
         "format": FORMAT, "batches": list(BATCHES), "activations": "bf16", "output": "fp32",
         "l2": "weights rotate over a ring of sets > 3x L2; every launch streams from HBM",
         "parallelism": f"N-sharded x{world}" + ("" if world == 1 else
@@ -326,7 +327,7 @@ def run_gpu(args):
     step_list = ShardedGemvList([(acts[b][0 if j < 2 else 2], weights[0][j], fmt, SHAPES[j][1], SHAPES[j][2])
                                  for b in BATCHES for j in range(3)], arena, rank, world)
     launches_per_step = 2 * len(BATCHES)
-    prepare_per_step = 2 * sum(1 for b in BATCHES if b > 1)  # activation conversion ahead of batched GEMVs
+    prepare_per_step = 1 if any(b > 1 for b in BATCHES) else 0  # ONE launch converts the batched activations of a list
 
     def step(slot, batches=BATCHES):
         if tuple(batches) == tuple(BATCHES):
