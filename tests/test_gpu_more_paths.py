@@ -290,6 +290,43 @@ def test_gemv_list_converts_batched_activations_first(shared_scratch):
     assert tb.device_status() == 0
 
 
+def test_gemv_list_twelve_batched_items_and_mixed_kernels():
+    """The longest list, every item batched (twelve conversions in one launch); then a list whose items go to
+    four different kernels (pipelined Q4_K at batch 16, tensor-memory Q6_K at batch 16, integer dot-product Q8_0
+    at batch 1, SIMT for fp32 activations), each with its own slice of the scratch."""
+    entries, wants = [], []
+    for i in range(12):
+        m, n, k = (2, 4, 8, 16)[i % 4], 256 + 64 * i, (1024, 2048, 3584)[i % 3]
+        raw = oracle.make_weights("q4_k", n, k, seed=200 + i)
+        x = oracle.make_activations(m, k, seed=220 + i, dtype="bf16")
+        entries.append((to_dev(x, torch.bfloat16), to_dev(raw), "q4_k", n, k, torch.full((m, n), float("nan"), device=dev())))
+        wants.append(c_oracle.gemv(x, raw, "q4_k", n, k))
+    lst = ops.GemvList(entries)
+    for _ in range(2):
+        for e in entries:
+            e[5].fill_(float("nan"))
+        lst.launch()
+        for e, want in zip(entries, wants):
+            assert oracle.rel_frobenius(e[5].cpu().numpy(), want) < TOL
+    entries, wants = [], []
+    for i, (name, m, n, k, xdt) in enumerate((("q4_k", 16, 512, 2048, "bf16"), ("q6_k", 16, 256, 2048, "bf16"),
+                                              ("q8_0", 1, 300, 1024, "f16"), ("q4_k", 4, 128, 512, "f32"),
+                                              ("q4_k", 16, 640, 3584, "bf16"))):
+        raw = oracle.make_weights(name, n, k, seed=240 + i)
+        x = oracle.make_activations(m, k, seed=250 + i, dtype=xdt)
+        xd = to_dev(x, {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[xdt])
+        entries.append((xd, to_dev(raw), name, n, k, torch.full((m, n), float("nan"), device=dev())))
+        wants.append(c_oracle.gemv(x, raw, name, n, k))
+    lst = ops.GemvList(entries)
+    for _ in range(2):
+        for e in entries:
+            e[5].fill_(float("nan"))
+        lst.launch()
+        for e, want in zip(entries, wants):
+            assert oracle.rel_frobenius(e[5].cpu().numpy(), want) < TOL
+    assert tb.device_status() == 0
+
+
 def test_gemv_list_other_formats_fall_back():
     m, n, k = 2, 96, 512
     entries, wants = [], []
