@@ -44,6 +44,23 @@ def test_recorded_schedule_becomes_the_default_plan():
     assert tb.gemv_plan(*shape) == derived
 
 
+def test_derived_plan_counts_the_latency_of_a_split():
+    """Batch 1 at K = 4096: a K split balances the SMs on paper but its extra phase costs about 2 us, more than
+    the whole unsplit launch takes (measured 4.4 against 11.6 us at 3072 rows): the derived plan must not split.
+    Where K is long and the rows are few, it still does."""
+    schedule.clear()
+    try:
+        for n in (1024, 1536, 2048, 3072, 4096, 6144):
+            assert tb.gemv_plan("q4_k", 1, n, 4096)["k_splits"] == 1, n
+        assert tb.gemv_plan("q4_k", 1, 3584, 18944)["k_splits"] > 1
+        assert tb.gemv_plan("q4_k", 16, 3584, 18944)["k_splits"] > 1
+    finally:
+        from tensor_b200 import _native
+
+        _native._apply_shipped_schedules()
+    assert tb.gemv_plan("q4_k", 1, 3584, 18944)["k_splits"] == 3  # the shipped schedule for the benchmark's down projection
+
+
 def test_profile_round_trip(tmp_path):
     profile = schedule.Profile()
     profile.add({"op": "gemv", "format": "q4_k", "m": 1, "n": 3584, "k": 18944, "best": {"k_splits": 8, "ctas_per_sm": 2},
