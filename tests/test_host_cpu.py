@@ -24,6 +24,18 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(handle, name), name
 
 
+def test_host_constants_match_the_header():
+    """The variant ids, peer flags and list length the Python layer passes are the header's."""
+    from tensor_b200 import ops
+
+    with open(os.path.join(ROOT, "include", "tensor_b200_gguf.h")) as f:
+        defines = dict(re.findall(r"#define\s+(TB200_\w+)\s+(\d+)", f.read()))
+    for name in ("auto", "simple", "fast", "mma", "tc", "dp4a"):
+        assert ops._VARIANTS[name] == int(defines["TB200_VARIANT_" + name.upper()])
+    assert ops.PEER_WAIT == int(defines["TB200_PEER_WAIT"]) and ops.PEER_SIGNAL == int(defines["TB200_PEER_SIGNAL"])
+    assert ops.GEMV_LIST_MAX == int(defines["TB200_GEMV_LIST_MAX"])
+
+
 def test_version_and_sizes():
     l = lib()
     assert l.tb200_gguf_version() >> 16 == 1
